@@ -1,0 +1,108 @@
+// Embedding gather, RMS norm, SiLU gating and small bookkeeping kernels.
+#include "common.cuh"
+
+// x[t][:] = table[token[t]][:]   (residual stream is 32-bit in every mode)
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                             float* __restrict__ x, int width, int vocab, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  if (tok < 0 || tok >= vocab) {
+    if (threadIdx.x == 0) atomicExch(err, 1 + t);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)t * width + i] = 0.f;
+    return;
+  }
+  const T* row = table + (size_t)tok * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)t * width + i] = to_f32(row[i]);
+}
+
+LLM_EXPORT int llm_embed(const int* tokens, const void* table, int table_dtype, float* x, int rows,
+                         int width, int vocab, int* err_flag, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (table_dtype == LLM_F32)
+    embed_kernel<float><<<rows, threads, 0, stream>>>(tokens, (const float*)table, x, width, vocab, err_flag);
+  else if (table_dtype == LLM_BF16)
+    embed_kernel<bf16><<<rows, threads, 0, stream>>>(tokens, (const bf16*)table, x, width, vocab, err_flag);
+  else
+    return LLM_ERR_UNSUPPORTED;
+  return launch_status();
+}
+
+// y[r][:] = x[src(r)][:] * rsqrt(mean(x^2) + eps) * w[:]    sums and scale in 32-bit.
+// src(r) = rows_index ? rows_index[r] : r.
+template <typename TOut>
+__global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                TOut* __restrict__ y, const int* __restrict__ rows_index, int width,
+                                float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows_index ? rows_index[r] : r) * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = xr[i];
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    y[(size_t)r * width + i] = from_f32<TOut>(xr[i] * scale * w[i]);
+}
+
+LLM_EXPORT int llm_rms_norm(const float* x, const float* w, void* y, int out_dtype,
+                            const int* rows_index, int rows, int width, float eps,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  if (out_dtype == LLM_F32)
+    rms_norm_kernel<float><<<rows, threads, 0, stream>>>(x, w, (float*)y, rows_index, width, eps);
+  else if (out_dtype == LLM_BF16)
+    rms_norm_kernel<bf16><<<rows, threads, 0, stream>>>(x, w, (bf16*)y, rows_index, width, eps);
+  else
+    return LLM_ERR_UNSUPPORTED;
+  return launch_status();
+}
+
+// out[t][j] = silu(gu[t][j]) * gu[t][ff + j]   with silu(z) = z / (1 + exp(-z)), in 32-bit.
+template <typename TOut>
+__global__ void silu_mul_kernel(const float* __restrict__ gate_up, TOut* __restrict__ out,
+                                long long total, int ff) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const long long t = idx / ff;
+    const int j = (int)(idx - t * ff);
+    const float g = gate_up[t * 2 * ff + j];
+    const float u = gate_up[t * 2 * ff + ff + j];
+    out[idx] = from_f32<TOut>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+LLM_EXPORT int llm_silu_mul(const float* gate_up, void* out, int out_dtype, int rows, int ff,
+                            cudaStream_t stream) {
+  const long long total = (long long)rows * ff;
+  if (total <= 0) return 0;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (out_dtype == LLM_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>(gate_up, (float*)out, total, ff);
+  else if (out_dtype == LLM_BF16)
+    silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>(gate_up, (bf16*)out, total, ff);
+  else
+    return LLM_ERR_UNSUPPORTED;
+  return launch_status();
+}
+
+// Scatter (row, column, value) triples into a table of block ids kept on the device.
+__global__ void table_update_kernel(int* __restrict__ table, int row_stride,
+                                    const int* __restrict__ updates, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) table[(size_t)updates[3 * i] * row_stride + updates[3 * i + 1]] = updates[3 * i + 2];
+}
+
+LLM_EXPORT int llm_table_update(int* table, int row_stride, const int* updates, int n,
+                                cudaStream_t stream) {
+  if (n <= 0) return 0;
+  table_update_kernel<<<(n + 127) / 128, 128, 0, stream>>>(table, row_stride, updates, n);
+  return launch_status();
+}

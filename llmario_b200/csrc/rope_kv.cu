@@ -1,0 +1,110 @@
+// Per-head RMS norm of queries and keys, half-split rotation by absolute position, and the write
+// of keys and values into the paged cache, in one pass over the projection output.
+//   order per head: norm -> rotation -> store; values are stored as projected.
+// All arithmetic is 32-bit; rounding to the cache / activation type happens once, at the store.
+#include "common.cuh"
+
+namespace {
+// One warp per (row, head).  Heads 0..Hq-1 are queries, Hq..Hq+Hkv-1 keys, then Hkv values.
+// proj row layout: [Hq*hd | Hkv*hd | Hkv*hd] (keys and values absent when !has_kv).
+template <typename TQ, typename TC>
+__global__ void qk_norm_rope_store_kernel(
+    const float* __restrict__ proj, int proj_stride, TQ* __restrict__ q_out,
+    TC* __restrict__ k_cache, TC* __restrict__ v_cache, long long page_stride,
+    const int* __restrict__ block_table, int table_stride, const int* __restrict__ row_slot,
+    const int* __restrict__ row_pos, const float* __restrict__ q_norm_w,
+    const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq, float attn_factor,
+    int rows, int Hq, int Hkv, int hd, int rot_dim, int page_size, float eps, int has_kv,
+    int use_norm) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int heads = Hq + (has_kv ? 2 * Hkv : 0);
+  if (warp >= rows * heads) return;
+  const int t = warp / heads, h = warp % heads;
+  const float* src = proj + (size_t)t * proj_stride + (size_t)h * hd;
+  const int pos = row_pos[t];
+
+  TC* cache_dst = nullptr;
+  if (h >= Hq) {
+    const int slot = row_slot[t];
+    const int page = block_table[(size_t)slot * table_stride + pos / page_size];
+    const int in_page = pos % page_size;
+    const int kvh = (h - Hq) % Hkv;
+    TC* base = (h < Hq + Hkv) ? k_cache : v_cache;
+    cache_dst = base + (size_t)page * page_stride + ((size_t)in_page * Hkv + kvh) * hd;
+  }
+  if (h >= Hq + Hkv) {  // value: copy
+    for (int i = lane; i < hd; i += 32) cache_dst[i] = from_f32<TC>(src[i]);
+    return;
+  }
+  const bool is_q = h < Hq;
+  const float* w = is_q ? q_norm_w : k_norm_w;
+  float scale = 1.f;
+  if (use_norm) {
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+      const float v = src[i];
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    scale = 1.0f / sqrtf(ss / (float)hd + eps);
+  }
+  const int half = rot_dim / 2;
+  const float fpos = (float)pos;
+  for (int i = lane; i < half; i += 32) {
+    float a = src[i], b = src[i + half];
+    if (use_norm) {
+      a = a * scale * w[i];
+      b = b * scale * w[i + half];
+    }
+    float sn, cs;
+    sincosf(fpos * inv_freq[i], &sn, &cs);
+    sn *= attn_factor;
+    cs *= attn_factor;
+    const float ra = a * cs - b * sn, rb = a * sn + b * cs;
+    if (is_q) {
+      q_out[(size_t)t * Hq * hd + (size_t)h * hd + i] = from_f32<TQ>(ra);
+      q_out[(size_t)t * Hq * hd + (size_t)h * hd + i + half] = from_f32<TQ>(rb);
+    } else {
+      cache_dst[i] = from_f32<TC>(ra);
+      cache_dst[i + half] = from_f32<TC>(rb);
+    }
+  }
+  for (int i = rot_dim + lane; i < hd; i += 32) {  // dimensions beyond the rotated ones
+    float a = src[i];
+    if (use_norm) a = a * scale * w[i];
+    if (is_q)
+      q_out[(size_t)t * Hq * hd + (size_t)h * hd + i] = from_f32<TQ>(a);
+    else
+      cache_dst[i] = from_f32<TC>(a);
+  }
+}
+}  // namespace
+
+LLM_EXPORT int llm_qk_norm_rope_store(
+    const float* proj, int proj_stride, void* q_out, void* k_cache, void* v_cache, int dtype,
+    long long page_stride, const int* block_table, int table_stride, const int* row_slot,
+    const int* row_pos, const float* q_norm_w, const float* k_norm_w, const float* inv_freq,
+    float attn_factor, int rows, int Hq, int Hkv, int hd, int rot_dim, int page_size, float eps,
+    int has_kv, int use_norm, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (rot_dim > hd || (rot_dim & 1)) return LLM_ERR_ARGUMENT;
+  const int heads = Hq + (has_kv ? 2 * Hkv : 0);
+  const long long warps = (long long)rows * heads;
+  const int threads = 128;
+  const int blocks = (int)((warps * 32 + threads - 1) / threads);
+#define ARGS proj, proj_stride, (TQ*)q_out, (TQ*)k_cache, (TQ*)v_cache, page_stride, block_table, \
+  table_stride, row_slot, row_pos, q_norm_w, k_norm_w, inv_freq, attn_factor, rows, Hq, Hkv, hd,   \
+  rot_dim, page_size, eps, has_kv, use_norm
+  if (dtype == LLM_F32) {
+    typedef float TQ;
+    qk_norm_rope_store_kernel<float, float><<<blocks, threads, 0, stream>>>(ARGS);
+  } else if (dtype == LLM_BF16) {
+    typedef bf16 TQ;
+    qk_norm_rope_store_kernel<bf16, bf16><<<blocks, threads, 0, stream>>>(ARGS);
+  } else {
+    return LLM_ERR_UNSUPPORTED;
+  }
+#undef ARGS
+  return launch_status();
+}

@@ -1,0 +1,222 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+The contract is the reference's ``forward_batch`` (crates/engine/model/src/forward.rs:204-325):
+every entry appends its tokens to its own request at positions ``length ..``; entries may be a
+single decoded token or a portion of a prompt, in any mix; a request appears at most once; when
+the pages do not suffice the step refuses and changes nothing.  Beyond the reference, the caller
+says at which of the step's tokens it wants logits (the reference returns each entry's last).
+
+All tokens of all entries are stacked into one batch of rows; one small array of integers
+(token ids, positions, request slots, wanted rows, block-table changes) goes to the device per
+step in one copy.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import kernels
+from ..cache import CacheError, CacheFull, CacheManager
+from ..parts import Segment, StepContext, Workspace
+from .model import Model
+
+
+@dataclass
+class StepEntry:
+    request: Any
+    tokens: Sequence[int]
+    want: Sequence[int] = ()      # indices into ``tokens`` whose logits are returned
+
+
+class StepError(ValueError):
+    """A batch that breaks the step function's contract."""
+
+
+def _round4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class ModelRunner:
+    """Owns the model, its cache and the per-step device buffers."""
+
+    def __init__(self, model: Model, page_size: int = 16, n_pages: Optional[int] = None,
+                 max_requests: int = 64, max_context: Optional[int] = None,
+                 token_budget: int = 2048, cache_tokens: Optional[int] = None):
+        self.model = model
+        self.device = model.device
+        if self.device.type != "cuda":
+            raise RuntimeError("llmario_b200 runs on a CUDA device; there is no CPU path "
+                               f"(asked for {self.device})")
+        kernels.lib()   # fail now, loudly, if the kernels cannot be built or loaded
+        self.page_size = int(page_size)
+        self.max_context = int(max_context or model.spec.max_positions)
+        self.max_requests = int(max_requests)
+        self.token_budget = int(token_budget)
+        if n_pages is None:
+            tokens = cache_tokens if cache_tokens is not None else \
+                self.max_requests * self.max_context
+            n_pages = -(-int(tokens) // self.page_size)
+        needs, reads = model.cache_needs()
+        self.cache = CacheManager(needs, reads, self.page_size, int(n_pages), self.max_requests,
+                                  self.max_context)
+        self.cache.allocate_storage(model.dtype, self.device)
+        self.workspace = Workspace(self.device)
+        self._meta_dev: Optional[torch.Tensor] = None
+        self._meta_host: List[Optional[torch.Tensor]] = [None, None]
+        self._meta_event: List[Optional[torch.cuda.Event]] = [None, None]
+        self._flip = 0
+        self.counters = {"steps": 0, "rows": 0, "max_entries_in_step": 0, "refused_steps": 0}
+
+    # ------------------------------------------------------------------ requests
+    def open(self, request: Any) -> None:
+        self.cache.open(request)
+
+    def close(self, request: Any) -> None:
+        if self.cache.has(request):
+            self.cache.close(request)
+
+    def length(self, request: Any) -> int:
+        return self.cache.length(request)
+
+    def free_tokens(self) -> int:
+        return min(self.cache.free_pages(), default=0) * self.page_size
+
+    # ------------------------------------------------------------------ the step
+    def _validate(self, entries: Sequence[StepEntry]) -> int:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        rows = 0
+        vocab = self.model.vocab_size
+        for e in entries:
+            if e.request in seen:
+                raise StepError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.request!r}: an entry needs at least one token")
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise StepError(f"request {e.request!r}: token {t} outside the vocabulary "
+                                    f"of {vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"request {e.request!r}: wanted place {w} outside its "
+                                    f"{n} tokens")
+            rows += n
+        new = [e.request for e in entries if not self.cache.has(e.request)]
+        if len(new) > self.cache.free_slots():
+            raise StepError(f"{len(new)} new requests but only {self.cache.free_slots()} "
+                            f"free request slots (max_requests={self.max_requests})")
+        return rows
+
+    def _meta_buffers(self, words: int) -> Tuple[torch.Tensor, torch.Tensor, int]:
+        if self._meta_dev is None or self._meta_dev.numel() < words:
+            cap = max(4096, 2 * words)
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._meta_host = [torch.empty(cap, dtype=torch.int32, pin_memory=True)
+                               for _ in range(2)]
+            self._meta_event = [None, None]
+        i = self._flip
+        self._flip ^= 1
+        ev = self._meta_event[i]
+        if ev is not None:
+            ev.synchronize()
+        return self._meta_dev, self._meta_host[i], i
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the tokens of ``entries`` as one batch.  Returns float32 logits
+        ``[number of wanted places, vocab]`` on the device, in the order of the entries and of
+        each entry's ``want``.  Raises :class:`CacheFull` with nothing changed when the pages
+        do not suffice."""
+        rows = self._validate(entries)
+        cache = self.cache
+        opened = []
+        try:
+            for e in entries:
+                if not cache.has(e.request):
+                    cache.open(e.request)
+                    opened.append(e.request)
+            cache.reserve([(e.request, len(e.tokens)) for e in entries])
+        except (CacheFull, CacheError):
+            for r in opened:
+                cache.close(r)
+            self.counters["refused_steps"] += 1
+            raise
+
+        # ---- one array of integers for the whole step
+        segments: List[Segment] = []
+        tokens = np.empty(rows, dtype=np.int32)
+        pos = np.empty(rows, dtype=np.int32)
+        slot = np.empty(rows, dtype=np.int32)
+        want: List[int] = []
+        r0 = 0
+        for e in entries:
+            n = len(e.tokens)
+            s, p0 = cache.slot(e.request), cache.length(e.request)
+            tokens[r0:r0 + n] = np.asarray(e.tokens, dtype=np.int32)
+            pos[r0:r0 + n] = np.arange(p0, p0 + n, dtype=np.int32)
+            slot[r0:r0 + n] = s
+            want += [r0 + int(w) for w in e.want]
+            segments.append(Segment(e.request, s, r0, n, p0))
+            r0 += n
+        updates = cache.take_table_updates()
+        o_tok, o_pos, o_slot = 0, _round4(rows), 2 * _round4(rows)
+        o_want = 3 * _round4(rows)
+        o_upd = []
+        off = o_want + _round4(len(want))
+        for u in updates:
+            o_upd.append(off)
+            off += _round4(3 * len(u))
+        dev, host, which = self._meta_buffers(off)
+        h = host.numpy()
+        h[o_tok:o_tok + rows] = tokens
+        h[o_pos:o_pos + rows] = pos
+        h[o_slot:o_slot + rows] = slot
+        if want:
+            h[o_want:o_want + len(want)] = np.asarray(want, dtype=np.int32)
+        for u, o in zip(updates, o_upd):
+            if len(u):
+                h[o:o + 3 * len(u)] = u.reshape(-1)
+        dev[:off].copy_(host[:off], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._meta_event[which] = ev
+        for g, u, o in zip(cache.groups, updates, o_upd):
+            if len(u):
+                kernels.table_update(g.table, dev[o:o + 3 * len(u)], len(u))
+        fresh = cache.take_fresh_slots()
+        if fresh and cache.state:
+            idx = torch.tensor(fresh, dtype=torch.long, device=self.device)
+            for st in cache.state.values():
+                st.index_fill_(0, idx, 0)
+
+        ctx = StepContext(rows=rows, tokens=dev[o_tok:o_tok + rows],
+                          row_pos=dev[o_pos:o_pos + rows], row_slot=dev[o_slot:o_slot + rows],
+                          segments=segments, dtype=self.model.dtype, device=self.device,
+                          workspace=self.workspace, cache=cache, fresh_slots=fresh,
+                          max_pos=int(pos.max()))
+
+        # ---- the model
+        m = self.model
+        x = ctx.buffer("x", (rows, m.hidden_size), torch.float32)
+        m.embedding.forward(ctx, ctx.tokens, x)
+        for call in m.calls:
+            m.blocks[call.layer].forward(ctx, call, x)
+        for e in entries:
+            cache.advance(e.request, len(e.tokens))
+
+        n_want = len(want)
+        logits = torch.empty((n_want, m.vocab_size), dtype=torch.float32, device=self.device)
+        if n_want:
+            hsel = ctx.buffer("head.h", (n_want, m.hidden_size))
+            m.final_norm.apply(ctx, x, hsel, dev[o_want:o_want + n_want])
+            m.head.forward(ctx, hsel, logits)
+        c = self.counters
+        c["steps"] += 1
+        c["rows"] += rows
+        c["max_entries_in_step"] = max(c["max_entries_in_step"], len(entries))
+        return logits

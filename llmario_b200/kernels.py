@@ -1,0 +1,204 @@
+"""Python face of the CUDA kernels: argument checks, pointers, status codes.
+
+Each function launches one hand-written kernel of ``csrc/`` on the current CUDA stream of torch.
+There is no other implementation behind these functions: a tensor that is not on a CUDA device,
+or a library that cannot be built, is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc.build import BuildError, load_library
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = load_library()
+        _declare(_lib)
+    return _lib
+
+
+def _declare(l) -> None:
+    P, I, L, F = c_void_p, c_int, c_longlong, c_float
+    sigs = {
+        "llm_embed": [P, P, I, P, I, I, I, P, P],
+        "llm_rms_norm": [P, P, P, I, P, I, I, F, P],
+        "llm_silu_mul": [P, P, I, I, I, P],
+        "llm_table_update": [P, I, P, I, P],
+        "llm_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, I, I, P],
+        "llm_qk_norm_rope_store": [P, I, P, P, P, I, L, P, I, P, P, P, P, P, F, I, I, I, I, I, I,
+                                   F, I, I, P],
+        "llm_attention_generic": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P],
+    }
+    for name, args in sigs.items():
+        if hasattr(l, name):
+            fn = getattr(l, name)
+            fn.argtypes = args
+            fn.restype = c_int
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {t.dtype}") from None
+
+
+def _cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("llmario_b200 kernels run on a CUDA device only; got a tensor on "
+                              f"{t.device}")
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status == -1:
+        raise KernelError(f"{what}: size or dtype not supported by this kernel")
+    if status == -2:
+        raise KernelError(f"{what}: inconsistent arguments")
+    raise KernelError(f"{what}: CUDA error {status}")
+
+
+# ------------------------------------------------------------------------------------------
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+          err_flag: torch.Tensor) -> None:
+    """out[t] = table[tokens[t]] as float32; a token outside the table sets err_flag to 1 + t."""
+    _cuda(tokens, table, out, err_flag)
+    assert tokens.dtype == torch.int32 and out.dtype == torch.float32
+    assert table.is_contiguous() and out.is_contiguous()
+    rows, width = out.shape
+    _check(lib().llm_embed(_ptr(tokens), _ptr(table), _dt(table), _ptr(out), rows, width,
+                           table.shape[0], _ptr(err_flag), _stream()), "embed")
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+             rows_index: Optional[torch.Tensor] = None) -> None:
+    """out[r] = x[rows_index[r] or r] * rsqrt(mean(x^2) + eps) * weight, x and weight float32."""
+    _cuda(x, weight, out, rows_index)
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32
+    assert x.is_contiguous() and out.is_contiguous()
+    rows, width = out.shape
+    assert x.shape[1] == width and weight.numel() == width
+    _check(lib().llm_rms_norm(_ptr(x), _ptr(weight), _ptr(out), _dt(out), _ptr(rows_index), rows,
+                              width, float(eps), _stream()), "rms_norm")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t][j] = silu(gate_up[t][j]) * gate_up[t][ff + j]."""
+    _cuda(gate_up, out)
+    assert gate_up.dtype == torch.float32 and gate_up.is_contiguous() and out.is_contiguous()
+    rows, ff = out.shape
+    assert gate_up.shape == (rows, 2 * ff)
+    _check(lib().llm_silu_mul(_ptr(gate_up), _ptr(out), _dt(out), rows, ff, _stream()),
+           "silu_mul")
+
+
+def table_update(table: torch.Tensor, updates: torch.Tensor, n: int) -> None:
+    """table[u[0]][u[1]] = u[2] for the first n int32 triples of ``updates``."""
+    _cuda(table, updates)
+    assert table.dtype == torch.int32 and updates.dtype == torch.int32
+    _check(lib().llm_table_update(_ptr(table), table.stride(0), _ptr(updates), n, _stream()),
+           "table_update")
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False
+              ) -> None:
+    """out (=|+=) a @ w.T on the CUDA cores with 32-bit accumulation; a [M,K], w [N,K]."""
+    _cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().llm_gemm_simt(_ptr(a), _dt(a), _ptr(w), _dt(w), _ptr(out), _dt(out), M, N, K,
+                               a.stride(0), w.stride(0), out.stride(0), int(accumulate),
+                               _stream()), "gemm_simt")
+
+
+def qk_norm_rope_store(proj: torch.Tensor, q_out: torch.Tensor,
+                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                       page_stride: int, block_table: torch.Tensor, row_slot: torch.Tensor,
+                       row_pos: torch.Tensor, q_norm_w: Optional[torch.Tensor],
+                       k_norm_w: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                       attn_factor: float, num_heads: int, num_kv_heads: int, head_dim: int,
+                       rot_dim: int, page_size: int, eps: float) -> None:
+    """Per-head norm, rotation and stores for the rows of ``proj`` (float32,
+    [rows, (Hq + 2 Hkv) * hd], or [rows, Hq * hd] when no cache is given)."""
+    _cuda(proj, q_out, k_cache, v_cache, block_table, row_slot, row_pos, q_norm_w, k_norm_w,
+          inv_freq)
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1
+    rows = proj.shape[0]
+    has_kv = k_cache is not None
+    use_norm = q_norm_w is not None
+    if rot_dim > 0:
+        assert inv_freq is not None and inv_freq.dtype == torch.float32
+        assert inv_freq.numel() == rot_dim // 2
+    _check(lib().llm_qk_norm_rope_store(
+        _ptr(proj), proj.stride(0), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _dt(q_out),
+        page_stride, _ptr(block_table), block_table.stride(0), _ptr(row_slot), _ptr(row_pos),
+        _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq), float(attn_factor), rows, num_heads,
+        num_kv_heads, head_dim, rot_dim, page_size, float(eps), int(has_kv), int(use_norm),
+        _stream()), "qk_norm_rope_store")
+
+
+def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
+                      v_cache: torch.Tensor, page_stride: int, block_table: torch.Tensor,
+                      row_slot: torch.Tensor, row_pos: torch.Tensor, num_heads: int,
+                      num_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                      window: Optional[int]) -> None:
+    _cuda(q, out, k_cache, v_cache, block_table, row_slot, row_pos)
+    assert q.dtype == out.dtype == k_cache.dtype and q.is_contiguous() and out.is_contiguous()
+    rows = q.shape[0]
+    _check(lib().llm_attention_generic(
+        _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _dt(q), page_stride, _ptr(block_table),
+        block_table.stride(0), _ptr(row_slot), _ptr(row_pos), rows, num_heads, num_kv_heads,
+        head_dim, page_size, float(scale), int(window or 0), _stream()),
+        f"attention (head_dim {head_dim})")
+
+
+# ------------------------------------------------------------------------------------------
+# dispatch: which kernel serves which dtype and size
+# ------------------------------------------------------------------------------------------
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out (=|+=) a @ w.T with the fastest hand-written kernel that takes these operands."""
+    gemm_simt(a, w, out, accumulate)
+
+
+def gate_up_silu(ctx, h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> None:
+    """act = silu(h Wg^T) * (h Wu^T) for Wg, Wu stacked in ``w_gate_up`` ([2 ff][hidden])."""
+    rows, ff = act.shape
+    gu = ctx.buffer("ffn.gate_up", (rows, 2 * ff), torch.float32)
+    linear(h, w_gate_up, gu)
+    silu_mul(gu, act)
+
+
+def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
+              head_dim: int, scale: float, window: Optional[int]) -> None:
+    """Causal attention of every row of the step over its own request's cached keys."""
+    attention_generic(q, out, view.k, view.v, view.page_stride, view.block_table, ctx.row_slot,
+                      ctx.row_pos, num_heads, num_kv_heads, head_dim, view.page_size, scale,
+                      window)

@@ -1,0 +1,79 @@
+"""Grouped-query attention over the paged cache, with optional per-head norm of queries and
+keys and a rotary position encoding.
+
+Order of operations as in crates/engine/model/src/forward.rs:399-485: project q, k, v; norm each
+head of q and k; rotate q and k by position; store k and v in the cache; attend from the cache
+(causal, optionally only the last ``window`` keys); project the result and add it to the
+residual stream.  A call that reads another call's cache projects only q.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels
+from ..cache import PagedKV
+from ..config.spec import PartSpec
+from .base import BoundCall, StepContext, build_part, register_part, tensor_of
+from .linear import Linear
+
+
+class Attention:
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = int(spec["hidden_size"])
+        self.num_heads = int(spec["num_heads"])
+        self.num_kv_heads = int(spec["num_kv_heads"])
+        self.head_dim = int(spec["head_dim"])
+        self.scale = float(spec["scale"])
+        self.window = spec.get("window")
+        self.q_width = self.num_heads * self.head_dim
+        self.kv_width = self.num_kv_heads * self.head_dim
+        self.position = (build_part("position", spec["position"], weights, dtype, device)
+                         if spec.get("position") is not None else None)
+        qn, kn = spec.get("q_norm"), spec.get("k_norm")
+        self.q_norm = build_part("norm", qn, weights, dtype, device) if qn is not None else None
+        self.k_norm = build_part("norm", kn, weights, dtype, device) if kn is not None else None
+        if (self.q_norm is None) != (self.k_norm is None):
+            raise ValueError("q_norm and k_norm come together")
+        if self.q_norm is not None and self.q_norm.eps != self.k_norm.eps:
+            raise ValueError("q_norm and k_norm must share eps")
+        self.qkv_proj = Linear.stacked([tensor_of(spec, r, weights) for r in ("q", "k", "v")])
+        self.q_proj = Linear(self.qkv_proj.weight[:self.q_width])   # the first rows, no copy
+        self.o_proj = Linear(tensor_of(spec, "o", weights))
+
+    def cache_need(self):
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+
+    def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor) -> None:
+        rows = ctx.rows
+        view = ctx.cache.view(call.cache_entry)
+        if view is None:
+            raise RuntimeError(f"run-order entry {call.index}: attention needs a cache")
+        if call.writes_cache:
+            proj = ctx.buffer("attn.proj", (rows, self.q_width + 2 * self.kv_width), torch.float32)
+            self.qkv_proj(h, proj)
+        else:
+            proj = ctx.buffer("attn.proj", (rows, self.q_width), torch.float32)
+            self.q_proj(h, proj)
+        q = ctx.buffer("attn.q", (rows, self.q_width))
+        tables = self.position.rotary_tables() if self.position is not None else None
+        if self.position is not None and tables is None:
+            raise NotImplementedError("a position encoding that is not a rotation needs its own "
+                                      "mixer")
+        inv_freq, rot_dim, attn_factor = tables if tables else (None, 0, 1.0)
+        kernels.qk_norm_rope_store(
+            proj, q, view.k if call.writes_cache else None,
+            view.v if call.writes_cache else None, view.page_stride, view.block_table,
+            ctx.row_slot, ctx.row_pos,
+            self.q_norm.weight if self.q_norm is not None else None,
+            self.k_norm.weight if self.k_norm is not None else None,
+            inv_freq, attn_factor, self.num_heads, self.num_kv_heads, self.head_dim, rot_dim,
+            view.page_size, self.q_norm.eps if self.q_norm is not None else 0.0)
+        out = ctx.buffer("attn.out", (rows, self.q_width))
+        kernels.attention(ctx, q, out, view, self.num_heads, self.num_kv_heads, self.head_dim,
+                          self.scale, self.window)
+        self.o_proj(out, x, accumulate=True)
+
+
+register_part("mixer", "attention", Attention, replace=True)

@@ -1,0 +1,124 @@
+"""Interfaces of the parts a layer is made of, and the registries that map a part's ``kind`` to
+its implementation.
+
+Roles: ``embedding``, ``mixer``, ``feed_forward``, ``norm``, ``position``, ``block``, ``head``.
+A part is built from its :class:`PartSpec` (sizes, constants, tensor names), the dictionary of
+loaded tensors and the compute dtype; it never looks at anything else of the model.  A new kind
+is added with :func:`register_part`; nothing in the framework's files changes.
+
+Interfaces (``ctx`` is the :class:`StepContext` of the running step):
+
+* norm          ``apply(ctx, x_f32[rows, width], out[rows, width], rows_index=None)``
+* position      ``rotary_tables()`` -> (inv_freq, rot_dim, attn_factor) for a rotation that the
+                fused kernel applies, or ``None`` together with ``apply(ctx, heads_f32, n_heads)``
+* mixer         ``cache_need()`` -> PagedKV | FixedState | None;
+                ``forward(ctx, call, h[rows, hidden], x_f32[rows, hidden])`` adds its output to x
+* feed_forward  ``forward(ctx, h[rows, hidden], x_f32[rows, hidden])`` adds its output to x
+* block         ``forward(ctx, call, x_f32)``; owns the arrangement of norms, mixer, feed-forward
+* embedding     ``forward(ctx, tokens_i32[rows], x_f32[rows, hidden])``
+* head          ``forward(ctx, h[n, hidden], logits_f32[n, vocab])``
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config.spec import ConfigError, PartSpec
+
+ROLES = ("embedding", "mixer", "feed_forward", "norm", "position", "block", "head")
+_REGISTRY: Dict[str, Dict[str, type]] = {r: {} for r in ROLES}
+
+
+def register_part(role: str, kind: str, cls: type, replace: bool = False) -> None:
+    if role not in _REGISTRY:
+        raise ConfigError(f"unknown part role '{role}'; roles: {', '.join(ROLES)}")
+    if kind in _REGISTRY[role] and not replace:
+        raise ConfigError(f"{role} '{kind}' is already registered")
+    _REGISTRY[role][kind] = cls
+
+
+def unregister_part(role: str, kind: str) -> None:
+    _REGISTRY[role].pop(kind, None)
+
+
+def part_class(role: str, kind: str) -> type:
+    try:
+        return _REGISTRY[role][kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRY.get(role, {}))) or "none"
+        raise ConfigError(f"no {role} of kind '{kind}' is registered (known: {known})") from None
+
+
+def build_part(role: str, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype: torch.dtype,
+               device: torch.device):
+    return part_class(role, spec.kind)(spec, weights, dtype, device)
+
+
+def tensor_of(spec: PartSpec, role: str, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+    """The loaded tensor that ``spec`` names for ``role``."""
+    name = spec["tensors"][role][0]
+    return weights[name]
+
+
+@dataclass
+class Segment:
+    """The rows of one request in this step."""
+
+    request: Any
+    slot: int          # the request's row in the block tables and state tensors
+    row_start: int
+    rows: int
+    pos_start: int     # position of the first of these rows inside the request
+
+
+class Workspace:
+    """Named buffers that live across steps, grown on demand, so that a step allocates nothing
+    once the largest batch has been seen."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+
+    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= int(d)
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(*shape)
+
+
+@dataclass
+class StepContext:
+    """Everything a part may read about the running step."""
+
+    rows: int
+    tokens: torch.Tensor           # int32 [rows]
+    row_pos: torch.Tensor          # int32 [rows]  position of each row inside its request
+    row_slot: torch.Tensor         # int32 [rows]  request slot of each row
+    segments: List[Segment]
+    dtype: torch.dtype             # dtype of activations between parts (bfloat16 or float32)
+    device: torch.device
+    workspace: Workspace
+    cache: Any                     # CacheManager
+    fresh_slots: Sequence[int] = ()   # request slots opened since the last step
+    max_pos: int = 0               # largest position in this step
+
+    def buffer(self, name: str, shape: Sequence[int], dtype: Optional[torch.dtype] = None
+               ) -> torch.Tensor:
+        return self.workspace.get(name, shape, dtype or self.dtype)
+
+
+@dataclass
+class BoundCall:
+    """A run-order entry at run time: which cache (if any) it writes or reads."""
+
+    index: int                     # position in the run order
+    layer: int
+    writes_cache: bool
+    cache_entry: Optional[int]     # run-order entry that owns the cache this call uses

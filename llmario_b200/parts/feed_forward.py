@@ -1,0 +1,31 @@
+"""Gated feed-forward: ``y = W_down (silu(W_gate h) * (W_up h))`` with
+``silu(z) = z / (1 + exp(-z))``, no biases (crates/engine/model/src/forward.rs:500-530;
+crates/engine/cpu/src/ops.rs:83-99).  Gate and up are one product over stacked rows."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import kernels
+from ..config.spec import PartSpec
+from .base import StepContext, register_part, tensor_of
+from .linear import Linear
+
+
+class SwiGLU:
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = int(spec["hidden_size"])
+        self.ff = int(spec["intermediate_size"])
+        self.gate_up = Linear.stacked([tensor_of(spec, "gate", weights),
+                                       tensor_of(spec, "up", weights)])
+        self.down = Linear(tensor_of(spec, "down", weights))
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor) -> None:
+        rows = ctx.rows
+        act = ctx.buffer("ffn.act", (rows, self.ff))
+        kernels.gate_up_silu(ctx, h, self.gate_up.weight, act)
+        self.down(act, x, accumulate=True)
+
+
+register_part("feed_forward", "swiglu", SwiGLU, replace=True)

@@ -1,0 +1,34 @@
+"""Rotary position encoding, half-split pairing (i, i + rot_dim/2):
+``freq_i = theta^(-2i/rot_dim)``, ``angle = pos * freq_scale * freq_i``, all in 32-bit
+(crates/engine/cpu/src/ops.rs:46-66, ``RopeKind::Neox``).  The rotation itself is applied by the
+kernel that also norms the heads and writes the cache; this part owns the constants."""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..config.spec import PartSpec
+from .base import register_part
+
+
+class RotaryHalfSplit:
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.rot_dim = int(spec["rot_dim"])
+        self.theta = float(spec["theta"])
+        self.freq_scale = float(spec.get("freq_scale", 1.0))
+        self.attn_factor = float(spec.get("attn_factor", 1.0))
+        if self.rot_dim % 2:
+            raise ValueError("rot_dim must be even")
+        i = np.arange(self.rot_dim // 2, dtype=np.float32)
+        exponent = (-(np.float32(2.0) * i) / np.float32(self.rot_dim)).astype(np.float32)
+        freq = np.power(np.float32(self.theta), exponent).astype(np.float32)
+        freq = (np.float32(self.freq_scale) * freq).astype(np.float32)
+        self.inv_freq = torch.from_numpy(freq).to(device)
+
+    def rotary_tables(self) -> Optional[Tuple[torch.Tensor, int, float]]:
+        return self.inv_freq, self.rot_dim, self.attn_factor
+
+
+register_part("position", "rope_neox", RotaryHalfSplit, replace=True)
