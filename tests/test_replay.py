@@ -1,0 +1,96 @@
+"""Replay of the same requests cut in different ways (whole; most at once and the last 32
+tokens one by one; portions of changing size; mixed with other requests and so few pages that
+they are used again), in 32-bit and in bfloat16, against the plain implementation."""
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+import traces
+from util import TINY, model_dir, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run_in_process(name, dtype, steps, max_tokens, max_requests=8):
+    """Drive the engine's own step function the way bin/trace_run does."""
+    from llmario_b200.engine import Model, ModelRunner, StepEntry
+
+    model = Model.from_folder(model_dir(name, dtype), dtype, "cuda:0")
+    page = TINY[name]["page_size"]
+    n_pages = -(-max_tokens // page)
+    runner = ModelRunner(model, page_size=page, n_pages=n_pages, max_requests=max_requests,
+                         max_context=min(model.spec.max_positions, n_pages * page))
+    out = {}
+    for s in steps:
+        logits = runner.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]])
+        if logits.shape[0]:
+            out[s["step"]] = logits.cpu().numpy()
+        for rid in s["end"]:
+            runner.close(rid)
+        runner.cache.check_invariants()
+    assert not runner.cache.live_requests()
+    assert all(f == n_pages for f in runner.cache.free_pages())
+    return out, runner
+
+
+def requests_for(name, lengths, seed):
+    return {f"q{i}": random_tokens(name, n, seed + i) for i, n in enumerate(lengths)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("mode", ["whole", "bulk_then_tail", "portions"])
+def test_one_request_at_a_time(name, dtype, mode):
+    reqs = requests_for(name, (45, 97, 130), seed=7)
+    steps = getattr(traces, mode)(reqs)
+    out, _ = run_in_process(name, dtype, steps, traces.peak_tokens(steps))
+    traces.check(steps, out, reqs, name, dtype, f"{name} {dtype} {mode}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_with_page_reuse(name, dtype):
+    reqs = requests_for(name, (40, 23, 75, 7, 1, 110, 64, 33, 90), seed=11)
+    steps = traces.mixed(reqs, live=4, seed=3)
+    peak = traces.peak_tokens(steps)
+    out, runner = run_in_process(name, dtype, steps, peak)
+    traces.check(steps, out, reqs, name, dtype, f"{name} {dtype} mixed")
+    page = TINY[name]["page_size"]
+    total = sum(-(-len(t) // page) for t in reqs.values())
+    # so few pages that they are used again: more were handed out than the pool holds
+    assert runner.cache.counters["pages_allocated"] > runner.cache.groups[0].n_pages
+    assert runner.cache.counters["pages_allocated"] >= total
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype):
+    """The program itself: standard input to files, `done` lines, exit code."""
+    name = "B"
+    reqs = requests_for(name, (50, 37, 20), seed=5)
+    steps = traces.mixed(reqs, live=3, seed=1)
+    with tempfile.TemporaryDirectory() as out_dir:
+        p = subprocess.run(
+            [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model",
+             model_dir(name, dtype), "--dtype", dtype, "--out", out_dir, "--max-tokens",
+             str(traces.peak_tokens(steps))],
+            input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+            timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        done = [l for l in p.stdout.splitlines() if l.startswith("done ")]
+        assert done == [f"done {s['step']}" for s in steps]
+        vocab = TINY[name]["vocab_size"]
+        out = {}
+        for s in steps:
+            path = os.path.join(out_dir, f"{s['step']}.f32")
+            n = sum(len(e["want"]) for e in s["entries"])
+            if n:
+                out[s["step"]] = np.fromfile(path, dtype="<f4").reshape(n, vocab)
+            else:
+                assert not os.path.exists(path)
+    traces.check(steps, out, reqs, name, dtype, f"trace_run {dtype}")
