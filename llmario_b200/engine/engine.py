@@ -1,0 +1,139 @@
+"""The Python entry point: an engine that takes token ids and returns token ids.
+
+``Engine.generate`` is the analogue of the reference's ``raw-run`` (prompt ids in, generated ids
+out: crates/engine/bin/src/main.rs:459-558) on top of the continuous-batching loop of its
+server (crates/engine/server/src/engine.rs:621-710).  Option names follow the reference's
+``serve`` flags: ``context`` (--ctx), ``max_requests`` (--parallel), ``token_budget`` (--batch)
+(crates/engine/bin/src/main.rs:31-90).
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from typing import Any, Dict, Iterable, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache import CacheFull
+from ..sampling import DeviceSampler, RequestSampler, SamplingParams
+from .model import Model, parse_dtype
+from .scheduler import FINISHED, Request, Scheduler, StepPlan
+from .step import ModelRunner, StepEntry
+
+
+class Engine:
+    def __init__(self, model: Union[str, Model, None] = None, *, config=None, seed: int = 0,
+                 dtype="bfloat16", device: str = "cuda:0", page_size: int = 16,
+                 num_pages: Optional[int] = None, cache_tokens: Optional[int] = None,
+                 token_budget: int = 512, max_requests: int = 64,
+                 context: Optional[int] = None, num_layers: Optional[int] = None):
+        """``model``: a folder with config.json and model.safetensors, or a built
+        :class:`Model`; or give ``config`` (a typed configuration) and ``seed`` for random
+        weights.  ``context``: most tokens of one request; ``max_requests``: requests running at
+        once; ``token_budget``: most tokens in one step; ``num_pages`` / ``cache_tokens``: size
+        of the cache (default: room for every request slot at full context)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("llmario_b200 needs a CUDA device; there is no CPU path")
+        if isinstance(model, Model):
+            self.model = model
+        elif model is not None:
+            self.model = Model.from_folder(model, dtype, device)
+        elif config is not None:
+            self.model = Model.random(config, seed, dtype, device)
+        else:
+            raise ValueError("give a model folder, a Model, or a config for random weights")
+        spec = self.model.spec
+        ctx = int(context or spec.max_positions)
+        self.runner = ModelRunner(self.model, page_size=page_size, n_pages=num_pages,
+                                  max_requests=max_requests, max_context=ctx,
+                                  token_budget=token_budget, cache_tokens=cache_tokens)
+        self.scheduler = Scheduler(self.runner.cache, token_budget, ctx, spec.eos_token_ids)
+        self.sampler = DeviceSampler(self.model.device)
+        self._ids = itertools.count()
+        self._requests: Dict[Any, Request] = {}
+        self.timers = {"step_s": 0.0, "sample_s": 0.0}
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Any = None) -> Any:
+        params = params or SamplingParams()
+        rid = request_id if request_id is not None else f"req-{next(self._ids)}"
+        if rid in self._requests and self._requests[rid].state != FINISHED:
+            raise ValueError(f"request id {rid!r} is in use")
+        vocab = self.model.vocab_size
+        prompt = [int(t) for t in prompt]
+        for t in prompt:
+            if not 0 <= t < vocab:
+                raise ValueError(f"token {t} outside the vocabulary of {vocab}")
+        req = Request(rid, prompt, params)
+        req.sampler = RequestSampler(params, vocab)
+        for t in prompt:                       # the prompt is penalised too (sampler.rs:374-386)
+            req.sampler.accept(t)
+        self.scheduler.add(req)
+        self._requests[rid] = req
+        return rid
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> List[Request]:
+        """One iteration: plan, run the batch, sample, finish.  Returns requests that finished
+        (or failed) in this iteration."""
+        plan = self.scheduler.plan()
+        finished: List[Request] = list(plan.failed)
+        if not plan.entries:
+            return finished
+        entries = []
+        for e in plan.entries:
+            toks = e.request.tokens(e.start, e.count)
+            entries.append(StepEntry(e.request.id, toks, [e.count - 1] if e.samples else []))
+        t0 = time.perf_counter()
+        logits = self.runner.step(entries)
+        samplers = [e.request.sampler for e in plan.entries if e.samples]
+        t1 = time.perf_counter()
+        tokens = self.sampler.sample(logits, samplers) if samplers else []
+        t2 = time.perf_counter()
+        self.timers["step_s"] += t1 - t0
+        self.timers["sample_s"] += t2 - t1
+        sampled = {}
+        i = 0
+        for e in plan.entries:
+            if e.samples:
+                sampled[e.request.id] = tokens[i]
+                e.request.sampler.accept(tokens[i])
+                i += 1
+        finished += self.scheduler.complete(plan, sampled)
+        return finished
+
+    def run_until_done(self) -> List[Request]:
+        done: List[Request] = []
+        while self.has_work():
+            done += self.step()
+        return done
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None
+                 ) -> List[List[int]]:
+        """Generated token ids for every prompt (host lists in, host lists out)."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        self.run_until_done()
+        out = []
+        for rid in ids:
+            r = self._requests.pop(rid)
+            if r.error:
+                raise RuntimeError(f"request {rid!r}: {r.error}")
+            out.append(list(r.output))
+        return out
+
+    def request(self, request_id: Any) -> Request:
+        return self._requests[request_id]
+
+    def stats(self) -> Dict[str, Any]:
+        """Counters in the spirit of the reference's ``Stats`` (engine.rs:59-159)."""
+        c = self.runner.cache
+        return {**self.runner.counters, **self.scheduler.counters,
+                "cache": dict(c.counters), "free_pages": c.free_pages(),
+                "pages": [g.n_pages for g in c.groups], "running": len(self.scheduler.running),
+                "waiting": len(self.scheduler.waiting), **self.timers}

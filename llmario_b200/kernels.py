@@ -44,6 +44,9 @@ def _declare(l) -> None:
         "llm_qk_norm_rope_store": [P, I, P, P, P, I, L, P, I, P, P, P, P, P, F, I, I, I, I, I, I,
                                    F, I, I, P],
         "llm_attention_generic": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P],
+        "llm_sample": [P, L, I, I, P, P, P, P, P, P, P],
+        "llm_gemv_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, P],
+        "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
     for name, args in sigs.items():
         if hasattr(l, name):
@@ -74,8 +77,13 @@ def _cuda(*tensors: Optional[torch.Tensor]) -> None:
                               f"{t.device}")
 
 
+launches = 0   # kernels of this library launched so far (a claim that bench.py reports)
+
+
 def _check(status: int, what: str) -> None:
+    global launches
     if status == 0:
+        launches += 1
         return
     if status == -1:
         raise KernelError(f"{what}: size or dtype not supported by this kernel")
@@ -180,17 +188,67 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         f"attention (head_dim {head_dim})")
 
 
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, min_p: torch.Tensor, uniform: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """One token per row of ``logits`` (float32 [rows, vocab]): greedy where temperature <= 0,
+    else top-k, top-p, min-p, temperature, softmax and a draw with the row's uniform."""
+    _cuda(logits, temperature, top_k, top_p, min_p, uniform, out)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert uniform.dtype == torch.float64 and top_k.dtype == torch.int32
+    rows, vocab = logits.shape
+    _check(lib().llm_sample(_ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature),
+                            _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(out),
+                            _stream()), "sample")
+
+
+def apply_penalties(logits: torch.Tensor, triples: torch.Tensor, n: int, repeat: torch.Tensor,
+                    freq: torch.Tensor, presence: torch.Tensor) -> None:
+    """For the first n (row, token, count) triples adjust logits[row][token] in place."""
+    _cuda(logits, triples, repeat, freq, presence)
+    _check(lib().llm_apply_penalties(_ptr(logits), logits.stride(0), _ptr(triples), n,
+                                     _ptr(repeat), _ptr(freq), _ptr(presence), _stream()),
+           "apply_penalties")
+
+
 # ------------------------------------------------------------------------------------------
 # dispatch: which kernel serves which dtype and size
 # ------------------------------------------------------------------------------------------
+GEMV_MAX_ROWS = 8
+
+
+def _gemv_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and a.shape[0] <= GEMV_MAX_ROWS and a.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemv_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, half: int = 0
+              ) -> None:
+    """Weight-streaming product for up to 8 rows.  mode 0: out = a w^T; 1: out += a w^T
+    (float32); 2: out = silu(a wg^T) * (a wu^T) with w = [wg; wu], ``half`` rows each."""
+    _cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    _check(lib().llm_gemv_bf16(_ptr(a), _ptr(w), _ptr(out), _dt(out), M, N, K, a.stride(0),
+                               w.stride(0), out.stride(0), mode, half, _stream()), "gemv_bf16")
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out (=|+=) a @ w.T with the fastest hand-written kernel that takes these operands."""
-    gemm_simt(a, w, out, accumulate)
+    if _gemv_ok(a, w):
+        gemv_bf16(a, w, out, 1 if accumulate else 0)
+    else:
+        gemm_simt(a, w, out, accumulate)
 
 
 def gate_up_silu(ctx, h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> None:
     """act = silu(h Wg^T) * (h Wu^T) for Wg, Wu stacked in ``w_gate_up`` ([2 ff][hidden])."""
     rows, ff = act.shape
+    if _gemv_ok(h, w_gate_up):
+        gemv_bf16(h, w_gate_up, act, 2, ff)
+        return
     gu = ctx.buffer("ffn.gate_up", (rows, 2 * ff), torch.float32)
     linear(h, w_gate_up, gu)
     silu_mul(gu, act)

@@ -1,0 +1,116 @@
+"""The sampler: per-request state on the host (options, random stream, penalty window) and the
+chain itself on the device (``csrc/sampling.cu``).
+
+Order of the chain (crates/engine/decode/src/sampler.rs:234-362): penalties -> greedy? ->
+top-k -> top-p -> min-p -> temperature -> softmax -> draw.  The window holds the last
+``repeat_last_n`` tokens, prompt included (sampler.rs:374-386).
+"""
+from __future__ import annotations
+
+import os
+from collections import deque
+from typing import Deque, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels
+from .params import SamplingParams
+from .rng import Xoshiro256StarStar
+
+
+class RequestSampler:
+    """Sampling state of one request."""
+
+    def __init__(self, params: SamplingParams, vocab_size: int):
+        self.params = params
+        self.vocab_size = vocab_size
+        self.seed = params.seed if params.seed is not None else \
+            int.from_bytes(os.urandom(8), "little")
+        self.rng = Xoshiro256StarStar(self.seed)
+        self.window: Deque[int] = deque()
+        self.counts: Dict[int, int] = {}
+
+    def accept(self, token: int) -> None:
+        """A prompt or generated token enters the penalty window."""
+        n = self.params.repeat_last_n
+        if n <= 0 or not 0 <= token < self.vocab_size:
+            return
+        if len(self.window) >= n:
+            old = self.window.popleft()
+            c = self.counts[old] - 1
+            if c:
+                self.counts[old] = c
+            else:
+                del self.counts[old]
+        self.window.append(token)
+        self.counts[token] = self.counts.get(token, 0) + 1
+
+    def next_uniform(self) -> float:
+        return 0.0 if self.params.greedy else self.rng.next_f64()
+
+
+class DeviceSampler:
+    """Samples one token for each row of a logits tensor on the device."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._cap = 0
+
+    def _buffers(self, rows: int, triples: int):
+        need = max(rows, 1)
+        if need > self._cap:
+            self._cap = max(64, 2 * need)
+            c = self._cap
+            # host (pinned) and device copies of the per-row options, packed in one buffer:
+            # [temperature f32 | top_p f32 | min_p f32 | repeat f32 | freq f32 | presence f32 |
+            #  top_k i32 | pad | uniform f64]
+            self._host = torch.empty(c * 10, dtype=torch.float32, pin_memory=True)
+            self._dev = torch.empty(c * 10, dtype=torch.float32, device=self.device)
+            self._out = torch.empty(c, dtype=torch.int32, device=self.device)
+            self._out_host = torch.empty(c, dtype=torch.int32, pin_memory=True)
+        if triples:
+            if getattr(self, "_tri_cap", 0) < triples:
+                self._tri_cap = max(1024, 2 * triples)
+                self._tri_host = torch.empty(self._tri_cap * 3, dtype=torch.int32,
+                                             pin_memory=True)
+                self._tri_dev = torch.empty(self._tri_cap * 3, dtype=torch.int32,
+                                            device=self.device)
+
+    def sample(self, logits: torch.Tensor, samplers: Sequence[RequestSampler]) -> List[int]:
+        """``logits`` float32 [rows, vocab] on the device (modified in place by penalties);
+        one :class:`RequestSampler` per row.  Returns the sampled token ids."""
+        rows = logits.shape[0]
+        assert rows == len(samplers) and logits.dtype == torch.float32
+        if rows == 0:
+            return []
+        tri: List[int] = []
+        for r, s in enumerate(samplers):
+            if s.params.penalties_active:
+                for tok, cnt in s.counts.items():
+                    tri += (r, tok, cnt)
+        self._buffers(rows, len(tri) // 3)
+        c = self._cap
+        h = self._host.numpy()
+        f = h[:6 * c].reshape(6, c)
+        k = h[6 * c:7 * c].view(np.int32)
+        u = h[8 * c:10 * c].view(np.float64)
+        for r, s in enumerate(samplers):
+            p = s.params
+            f[0, r], f[1, r], f[2, r] = p.temperature, p.top_p, p.min_p
+            f[3, r], f[4, r], f[5, r] = p.repeat_penalty, p.frequency_penalty, p.presence_penalty
+            k[r] = p.top_k
+            u[r] = s.next_uniform()
+        self._dev.copy_(self._host, non_blocking=True)
+        d = self._dev
+        if tri:
+            n = len(tri) // 3
+            self._tri_host[:3 * n] = torch.tensor(tri, dtype=torch.int32)
+            self._tri_dev[:3 * n].copy_(self._tri_host[:3 * n], non_blocking=True)
+            kernels.apply_penalties(logits, self._tri_dev, n, d[3 * c:4 * c], d[4 * c:5 * c],
+                                    d[5 * c:6 * c])
+        kernels.sample(logits, d[0:c], d[6 * c:7 * c].view(torch.int32), d[c:2 * c],
+                       d[2 * c:3 * c], d[8 * c:10 * c].view(torch.float64), self._out)
+        self._out_host[:rows].copy_(self._out[:rows], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._out_host[:rows].tolist()

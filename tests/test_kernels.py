@@ -1,0 +1,226 @@
+"""Each kernel alone against a plain float32/float64 torch statement of the same operation, at
+sizes other than the engine's tiny configurations."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (scale * torch.randn(*shape, generator=g)).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("rows,width", [(1, 40), (7, 1000), (33, 4096)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm(rows, width, out_dtype):
+    from llmario_b200 import kernels
+    x, w = rnd(rows, width, scale=3.0), 1 + 0.1 * rnd(width, seed=1)
+    out = torch.empty(rows, width, dtype=out_dtype, device=DEV)
+    kernels.rms_norm(x, w, out, 1e-5)
+    xd = x.double()
+    ref = xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + 1e-5) * w.double()
+    tol = 1e-5 if out_dtype == torch.float32 else 2 ** -8
+    assert (out.double() - ref).abs().max() <= tol * ref.abs().max()
+    # with a row index: rows in another order
+    idx = torch.tensor(list(range(rows))[::-1], dtype=torch.int32, device=DEV)
+    out2 = torch.empty_like(out)
+    kernels.rms_norm(x, w, out2, 1e-5, idx)
+    assert torch.equal(out2, out.flip(0))
+
+
+@pytest.mark.parametrize("vocab,width", [(50, 24), (1000, 520)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(vocab, width, dtype):
+    from llmario_b200 import kernels
+    table = rnd(vocab, width, dtype=dtype)
+    toks = torch.tensor([0, vocab - 1, 3, 3, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, width, dtype=torch.float32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.embed(toks, table, out, err)
+    assert torch.equal(out, table[toks.long()].float())
+    assert err.item() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 50, 24), (5, 130, 100), (70, 300, 257), (130, 64, 512)])
+@pytest.mark.parametrize("dt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                (torch.bfloat16, torch.float32)])
+def test_gemm_simt(M, N, K, dt):
+    from llmario_b200 import kernels
+    a, w = rnd(M, K, dtype=dt[0]), rnd(N, K, dtype=dt[1], seed=3)
+    ref = a.double() @ w.double().t()
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    kernels.gemm_simt(a, w, out)
+    assert (out.double() - ref).abs().max() <= 1e-5 * ref.abs().max() * math.sqrt(K)
+    base = rnd(M, N, seed=9)
+    acc = base.clone()
+    kernels.gemm_simt(a, w, acc, accumulate=True)
+    assert (acc.double() - (base.double() + ref)).abs().max() <= 1e-5 * ref.abs().max() * math.sqrt(K)
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("N,K", [(6, 8), (130, 264), (1000, 4096)])
+def test_gemv_bf16(M, N, K):
+    from llmario_b200 import kernels
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=3)
+    ref = a.double() @ w.double().t()
+    tol = 1e-5 * ref.abs().max() * math.sqrt(K)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    kernels.gemv_bf16(a, w, out, 0)
+    assert (out.double() - ref).abs().max() <= tol
+    base = rnd(M, N, seed=9)
+    acc = base.clone()
+    kernels.gemv_bf16(a, w, acc, 1)
+    assert (acc.double() - (base.double() + ref)).abs().max() <= tol
+    if N % 2 == 0:
+        half = N // 2
+        act = torch.empty(M, half, dtype=torch.float32, device=DEV)
+        kernels.gemv_bf16(a, w, act, 2, half)
+        g, u = ref[:, :half], ref[:, half:]
+        want = g / (1 + torch.exp(-g)) * u
+        assert (act.double() - want).abs().max() <= 4 * tol * max(1.0, ref.abs().max().item())
+
+
+def test_silu_mul():
+    from llmario_b200 import kernels
+    gu = rnd(9, 2 * 70, scale=4.0)
+    out = torch.empty(9, 70, dtype=torch.float32, device=DEV)
+    kernels.silu_mul(gu, out)
+    g, u = gu[:, :70].double(), gu[:, 70:].double()
+    assert (out.double() - g / (1 + torch.exp(-g)) * u).abs().max() <= 1e-5
+
+
+def paged_setup(lengths, page, Hkv, hd, dtype, seed=0, n_layers_in_page=2, layer=1):
+    """A scrambled paged cache holding random keys/values for requests of the given lengths."""
+    n_pages = sum(-(-n // page) for n in lengths) + 3
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    storage = torch.zeros(n_pages, n_layers_in_page, 2, page, Hkv, hd, dtype=dtype, device=DEV)
+    maxp = max(-(-n // page) for n in lengths) + 1
+    table = torch.full((len(lengths), maxp), -1, dtype=torch.int32)
+    ks, vs = [], []
+    at = 0
+    for r, n in enumerate(lengths):
+        k = torch.randn(n, Hkv, hd, generator=g).to(dtype)
+        v = torch.randn(n, Hkv, hd, generator=g).to(dtype)
+        ks.append(k), vs.append(v)
+        for j in range(-(-n // page)):
+            p = perm[at]
+            at += 1
+            table[r, j] = p
+            m = min(page, n - j * page)
+            storage[p, layer, 0, :m] = k[j * page:j * page + m].to(DEV)
+            storage[p, layer, 1, :m] = v[j * page:j * page + m].to(DEV)
+    return storage, table.to(DEV), ks, vs
+
+
+def attention_ref(q, k, v, pos, window, scale):
+    """q [Hq, hd], k/v [S, Hkv, hd]: one query at position pos over keys lo..pos."""
+    Hq, Hkv = q.shape[0], k.shape[1]
+    lo = max(0, pos + 1 - window) if window else 0
+    out = torch.zeros_like(q, dtype=torch.float64)
+    for h in range(Hq):
+        kh = k[lo:pos + 1, h // (Hq // Hkv)].double()
+        vh = v[lo:pos + 1, h // (Hq // Hkv)].double()
+        s = (kh @ q[h].double()) * scale
+        w = torch.softmax(s, 0)
+        out[h] = w @ vh
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(4, 2, 16, 4, None), (6, 1, 48, 16, 37),
+                                                   (8, 8, 128, 8, None), (3, 3, 80, 32, 100),
+                                                   (10, 2, 256, 16, None)])
+def test_attention_generic(dtype, Hq, Hkv, hd, page, window):
+    from llmario_b200 import kernels
+    lengths = [1, 33, 150, 64, 257]
+    storage, table, ks, vs = paged_setup(lengths, page, Hkv, hd, dtype)
+    # rows: the last position of every request, plus a run of rows inside request 2
+    rows = [(r, n - 1) for r, n in enumerate(lengths)] + [(2, p) for p in range(60, 70)]
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(len(rows), Hq, hd, generator=g).to(dtype)
+    slot = torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    out = torch.empty(len(rows), Hq * hd, dtype=dtype, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    kernels.attention_generic(q.reshape(len(rows), -1).to(DEV).contiguous(), out,
+                              storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table, slot,
+                              pos, Hq, Hkv, hd, page, scale, window)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    for i, (r, p) in enumerate(rows):
+        ref = attention_ref(q[i], ks[r], vs[r], p, window, scale)
+        got = out[i].reshape(Hq, hd).double().cpu()
+        assert (got - ref).abs().max() <= tol, (i, r, p)
+
+
+def test_attention_far_key_stands_out():
+    """One key far back among hundreds is made to dominate: the output must be its value."""
+    from llmario_b200 import kernels
+    Hq, Hkv, hd, page = 4, 2, 32, 8
+    n = 700
+    storage, table, ks, vs = paged_setup([n], page, Hkv, hd, torch.float32, seed=3,
+                                         n_layers_in_page=1, layer=0)
+    q = torch.randn(1, Hq, hd)
+    far = 13
+    for h in range(Hq):
+        kvh = h // 2
+        ks[0][far, kvh] = 0
+    ks[0][far] = 40 * q[0, ::2] / q[0, ::2].norm(dim=-1, keepdim=True)   # aligned with heads 0, 2
+    p_idx, s_idx = table[0, far // page].item(), far % page
+    storage[p_idx, 0, 0, s_idx] = ks[0][far].to(DEV)
+    out = torch.empty(1, Hq * hd, dtype=torch.float32, device=DEV)
+    kernels.attention_generic(q.reshape(1, -1).to(DEV), out, storage[0, 0, 0], storage[0, 0, 1],
+                              storage.stride(0), table, torch.zeros(1, dtype=torch.int32, device=DEV),
+                              torch.tensor([n - 1], dtype=torch.int32, device=DEV), Hq, Hkv, hd,
+                              page, 1 / math.sqrt(hd), None)
+    ref = attention_ref(q[0], ks[0], vs[0], n - 1, None, 1 / math.sqrt(hd))
+    got = out.reshape(Hq, hd).double().cpu()
+    assert (got - ref).abs().max() <= 2e-5
+    for h in (0, 2):   # the heads whose query the far key was aligned with
+        assert (got[h] - vs[0][far, h // 2].double()).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,hd,page", [(4, 2, 16, 4), (5, 5, 48, 16), (8, 2, 128, 8)])
+def test_qk_norm_rope_store(dtype, Hq, Hkv, hd, page):
+    from llmario_b200 import kernels
+    rows_pos = [0, 1, 5, 17, 300, 1023]
+    T = len(rows_pos)
+    width = (Hq + 2 * Hkv) * hd
+    proj = rnd(T, width, scale=2.0)
+    qw, kw = 1 + 0.1 * rnd(hd, seed=1), 1 + 0.1 * rnd(hd, seed=2)
+    theta, eps = 12345.0, 1e-5
+    inv_freq = torch.tensor(np.power(np.float32(theta), -(np.arange(hd // 2, dtype=np.float32) * 2) / hd)
+                            .astype(np.float32), device=DEV)
+    n_pages = 1024 // page + 1
+    storage = torch.zeros(n_pages, 1, 2, page, Hkv, hd, dtype=dtype, device=DEV)
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).flip(0).reshape(1, -1).contiguous()
+    q_out = torch.empty(T, Hq * hd, dtype=dtype, device=DEV)
+    slot = torch.zeros(T, dtype=torch.int32, device=DEV)
+    pos = torch.tensor(rows_pos, dtype=torch.int32, device=DEV)
+    kernels.qk_norm_rope_store(proj, q_out, storage[0, 0, 0], storage[0, 0, 1], storage.stride(0),
+                               table, slot, pos, qw, kw, inv_freq, 1.0, Hq, Hkv, hd, hd, page, eps)
+
+    def norm_rope(x, w, p):   # x [H, hd] float64
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.double().cpu()
+        half = hd // 2
+        ang = p * (theta ** (-(torch.arange(half, dtype=torch.float64) * 2) / hd))
+        c, s = torch.cos(ang), torch.sin(ang)
+        a, b = x[:, :half], x[:, half:]
+        return torch.cat([a * c - b * s, a * s + b * c], -1)
+
+    tol = 3e-4 if dtype == torch.float32 else 3e-2   # 32-bit angle at position 1023: ~1e-4 rad
+    pc = proj.double().cpu()
+    for i, p in enumerate(rows_pos):
+        qr = norm_rope(pc[i, :Hq * hd].reshape(Hq, hd), qw, p)
+        kr = norm_rope(pc[i, Hq * hd:(Hq + Hkv) * hd].reshape(Hkv, hd), kw, p)
+        vr = pc[i, (Hq + Hkv) * hd:].reshape(Hkv, hd)
+        page_id = table[0, p // page].item()
+        assert (q_out[i].double().cpu().reshape(Hq, hd) - qr).abs().max() <= tol
+        assert (storage[page_id, 0, 0, p % page].double().cpu() - kr).abs().max() <= tol
+        assert (storage[page_id, 0, 1, p % page].double().cpu() - vr).abs().max() <= tol
