@@ -80,9 +80,13 @@ class Model:
 
     # ------------------------------------------------------------------------------------
     @classmethod
-    def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda:0") -> "Model":
+    def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda:0",
+                    spec: Optional[ModelSpec] = None) -> "Model":
+        """Build the model that ``config.json`` of the folder names.  ``spec`` replaces the
+        layout read from the configuration (another run order, other parts) while the tensors
+        still come from the folder."""
         dt = parse_dtype(dtype)
-        spec = load_spec(model_dir)
+        spec = spec if spec is not None else load_spec(model_dir)
         weights = load_weights(model_dir, spec, dt, device)
         model = cls(spec, weights, dt, device)
         weights.clear()

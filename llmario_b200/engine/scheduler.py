@@ -15,8 +15,8 @@ crate retracts a running request and recomputes it later, crates/engine/sched/sr
 148-174): first prompt portions are shortened or left out of the step; if even the decoding
 requests do not fit, the most recently admitted running request is preempted: its pages are
 given back and it returns to the head of the waiting queue with its prompt extended by what it
-has generated, to be recomputed.  A request that cannot fit even alone is failed with
-"KV cache full".
+has generated, to be recomputed once all of it fits the free pages.  A request that cannot fit
+even alone is failed with "KV cache full".
 """
 from __future__ import annotations
 
@@ -171,6 +171,13 @@ class Scheduler:
                     cache.free_slots() - self._planned_new(entries) > 0:
                 r = self.waiting[0]
                 left = r.sequence_len - r.computed
+                if r.preemptions:
+                    # a request that lost its pages comes back only when all of it fits:
+                    # otherwise it would take the pages the older requests are about to need
+                    # and be preempted again
+                    if plan.preempted or any(
+                            k > f for k, f in zip(self._pages_for(r, left + 1, False), free)):
+                        break
                 n = self._fit(r, min(left, self.token_budget - used), free, False)
                 if n <= 0:
                     break

@@ -302,9 +302,13 @@ def plain_sample(logits: Sequence[float], *, temperature: float = 1.0, top_k: in
             l[t] = np.float32(l[t] - np.float32(c * frequency_penalty + presence_penalty))
     if temperature <= 0:
         return int(np.argmax(l))  # first maximum wins (sampler.rs:37-45)
-    order = sorted(range(len(l)), key=lambda i: (-float(l[i]), i))
+    # candidates stay in id order until a filter that needs sorting runs (sampler.rs:247-301)
+    by_rank = lambda ids: sorted(ids, key=lambda i: (-float(l[i]), i))
+    order = list(range(len(l)))
+    is_sorted = False
     if 0 < top_k < len(l):
-        order = order[:top_k]
+        order = by_rank(order)[:top_k]
+        is_sorted = True
 
     def soft(ids):
         z = np.array([l[i] for i in ids], dtype=np.float32)
@@ -312,6 +316,9 @@ def plain_sample(logits: Sequence[float], *, temperature: float = 1.0, top_k: in
         return e / e.sum(dtype=np.float32)
 
     if top_p < 1.0 and len(order) > 1:
+        if not is_sorted:
+            order = by_rank(order)
+            is_sorted = True
         p = soft(order)
         cum = np.float32(0)
         last = len(order)
@@ -322,8 +329,9 @@ def plain_sample(logits: Sequence[float], *, temperature: float = 1.0, top_k: in
                 break
         order = order[:last]
     if min_p > 0 and len(order) > 1:
-        floor = np.float32(l[order[0]] + np.float32(math.log(min_p)))
-        order = [order[0]] + [i for i in order[1:] if l[i] >= floor]
+        top = max(float(l[i]) for i in order)
+        floor = np.float32(np.float32(top) + np.float32(math.log(min_p)))
+        order = [i for i in order if l[i] >= floor]
     if temperature != 1.0:
         for i in order:
             l[i] = np.float32(l[i] / np.float32(temperature))

@@ -1,0 +1,334 @@
+"""Cache manager and scheduler decisions (no GPU)."""
+import random
+
+import pytest
+
+from llmario_b200.cache import (CacheError, CacheFull, CacheManager, FixedState, PagedKV,
+                                PagePool)
+from llmario_b200.engine.scheduler import FINISHED, RUNNING, WAITING, Request, Scheduler
+from llmario_b200.sampling import SamplingParams
+
+
+def manager(n_pages=16, page=4, max_requests=4, ctx=64, window=None, layers=2, state=False):
+    needs = [PagedKV(2, 8, None)] * layers + ([PagedKV(2, 8, window)] if window else [])
+    if state:
+        needs.append(FixedState((3,)))
+    return CacheManager(needs, [None] * len(needs), page, n_pages, max_requests, ctx)
+
+
+# ------------------------------------------------------------------------------ pool
+def test_pool_all_or_nothing_and_double_free():
+    p = PagePool(4)
+    assert p.alloc(5) is None and p.free == 4
+    a = p.alloc(3)
+    assert p.free == 1 and len(set(a)) == 3
+    p.release(a[:1])
+    with pytest.raises(CacheError):
+        p.release(a[:1])         # freed twice
+    with pytest.raises(CacheError):
+        p.release([99])
+    assert p.held() == 2
+
+
+def test_freed_pages_are_used_again_oldest_first():
+    p = PagePool(3)
+    a = p.alloc(3)
+    p.release([a[1]])
+    p.release([a[0]])
+    assert p.alloc(2) == [a[1], a[0]]
+
+
+# ------------------------------------------------------------------------------ manager
+def test_grouping_by_need():
+    m = manager(window=6, layers=3)
+    assert len(m.groups) == 2
+    assert m.groups[0].entries == [0, 1, 2] and m.groups[1].entries == [3]
+    m2 = CacheManager([PagedKV(2, 8), PagedKV(2, 8), None], [None, None, 0], 4, 8, 2, 32)
+    assert m2._where[2] == m2._where[0]          # reads the first entry's cache
+    with pytest.raises(CacheError):
+        CacheManager([None, PagedKV(2, 8)], [None, 0], 4, 8, 2, 32)
+
+
+def test_reserve_refuses_and_changes_nothing():
+    m = manager(n_pages=5)
+    m.open("a"), m.open("b")
+    m.reserve([("a", 9)])
+    m.advance("a", 9)
+    m.take_table_updates()
+    before = (m.free_pages(), m.pages_of("a"), m.pages_of("b"))
+    with pytest.raises(CacheFull) as e:
+        m.reserve([("a", 4), ("b", 8)])      # a needs 1 more, b needs 2, 2 free
+    assert (e.value.needed, e.value.free) == (3, 2)
+    assert (m.free_pages(), m.pages_of("a"), m.pages_of("b")) == before
+    assert all(len(u) == 0 for u in m.take_table_updates())
+    m.reserve([("a", 3), ("b", 8)])          # a fits its pages, b takes the last two
+    assert m.free_pages() == [0]
+    m.check_invariants()
+
+
+def test_step_contract_errors():
+    m = manager(ctx=16)
+    m.open("a")
+    with pytest.raises(CacheError, match="twice"):
+        m.reserve([("a", 1), ("a", 1)])
+    with pytest.raises(CacheError, match="exceed the context"):
+        m.reserve([("a", 17)])
+    with pytest.raises(CacheError, match="unknown request"):
+        m.reserve([("zz", 1)])
+    with pytest.raises(CacheError, match="already open"):
+        m.open("a")
+    for r in "bcd":
+        m.open(r)
+    with pytest.raises(CacheError, match="no free request slot"):
+        m.open("e")
+
+
+def test_window_pages_go_back_when_passed():
+    m = manager(n_pages=8, page=4, window=6, layers=1, ctx=64)
+    full, win = 0, 1
+    m.open("a")
+    at = 0
+    for n in (5, 4, 1, 1, 1, 9, 2):
+        m.reserve([("a", n)])
+        m.advance("a", n)
+        at += n
+        pages = m.pages_of("a", win)
+        # a later query at position >= at reaches back to at - 6 + 1
+        first_needed = max(0, at - 6 + 1) // 4
+        assert all(p == -1 for p in pages[:first_needed])
+        assert all(p >= 0 for p in pages[first_needed:])
+        assert all(p >= 0 for p in m.pages_of("a", full))
+        m.check_invariants()
+    assert m.counters["window_releases"] == first_needed
+    assert m.free_pages()[win] > m.free_pages()[full]
+    m.close("a")
+    assert m.free_pages() == [8, 8]
+    m.check_invariants()
+
+
+def test_truncate_and_state_rules():
+    m = manager(n_pages=8)
+    m.open("a")
+    m.reserve([("a", 14)])
+    m.advance("a", 14)
+    m.truncate("a", 5)
+    assert m.length("a") == 5 and len(m.pages_of("a")) == 2 and m.free_pages() == [6]
+    with pytest.raises(CacheError):
+        m.truncate("a", 9)
+    s = manager(state=True)
+    s.open("a")
+    s.reserve([("a", 3)])
+    s.advance("a", 3)
+    with pytest.raises(CacheError, match="cannot be rewound"):
+        s.truncate("a", 1)
+    w = manager(window=6, layers=1)
+    w.open("a")
+    w.reserve([("a", 20)])
+    w.advance("a", 20)
+    with pytest.raises(CacheError, match="already given back"):
+        w.truncate("a", 6)
+
+
+def test_table_updates_one_per_cell():
+    m = manager(n_pages=4, max_requests=1)
+    m.open("a")
+    m.reserve([("a", 8)])
+    m.advance("a", 8)
+    first = m.pages_of("a")
+    m.close("a")
+    m.open("b")                       # same slot, pages handed out again
+    m.reserve([("b", 4)])
+    (u,) = m.take_table_updates()
+    cells = {(int(s), int(j)): int(p) for s, j, p in u}
+    assert len(cells) == len(u)       # no cell twice: any order of application is right
+    assert cells[(0, 0)] == m.pages_of("b")[0] and cells[(0, 1)] == -1
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_orders_lose_nothing(seed):
+    rng = random.Random(seed)
+    m = manager(n_pages=24, page=4, max_requests=5, ctx=40, window=7, layers=2, state=True)
+    live = {}
+    n = 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.25 and m.free_slots():
+            n += 1
+            m.open(n)
+            live[n] = 0
+        elif op < 0.8 and live:
+            chosen = rng.sample(sorted(live), rng.randint(1, len(live)))
+            growth = [(r, rng.randint(1, 9)) for r in chosen if live[r] < 30]
+            if growth:
+                try:
+                    m.reserve(growth)
+                    for r, k in growth:
+                        m.advance(r, k)
+                        live[r] += k
+                except CacheFull:
+                    pass
+        elif live:
+            r = rng.choice(sorted(live))
+            m.close(r)
+            del live[r]
+        m.check_invariants()
+        for r, length in live.items():
+            assert m.length(r) == length
+    for r in list(live):
+        m.close(r)
+    m.check_invariants()
+    assert m.free_pages() == [24, 24] and m.free_slots() == 5
+
+
+# ------------------------------------------------------------------------------ scheduler
+def req(rid, n_prompt, max_tokens=4):
+    return Request(rid, list(range(1, n_prompt + 1)), SamplingParams(temperature=0, max_tokens=max_tokens))
+
+
+def run_plan(s, plan, token=7):
+    """Pretend the step ran: grow the cache as the step function would, then complete."""
+    for e in plan.entries:
+        if not s.cache.has(e.request.id):
+            s.cache.open(e.request.id)
+    s.cache.reserve([(e.request.id, e.count) for e in plan.entries])
+    for e in plan.entries:
+        s.cache.advance(e.request.id, e.count)
+    return s.complete(plan, {e.request.id: token for e in plan.entries if e.samples})
+
+
+def test_portions_under_the_budget_then_decodes_first():
+    """The reference's rule (sched/src/lib.rs:318-326): (a,0,8), then (a,8,10) + (b,0,3)."""
+    s = Scheduler(manager(n_pages=64, ctx=64), token_budget=8)
+    a, b = req("a", 10), req("b", 3)
+    s.add(a), s.add(b)
+    p1 = s.plan()
+    assert [(e.request.id, e.start, e.count, e.samples) for e in p1.entries] == [("a", 0, 8, False)]
+    run_plan(s, p1)
+    p2 = s.plan()
+    assert [(e.request.id, e.start, e.count, e.samples) for e in p2.entries] == \
+        [("a", 8, 2, True), ("b", 0, 3, True)]
+    run_plan(s, p2)
+    c = req("c", 20)
+    s.add(c)
+    p3 = s.plan()        # decodes first, one token each, then c's first portion in what is left
+    assert [(e.request.id, e.start, e.count) for e in p3.entries] == \
+        [("a", 10, 1), ("b", 3, 1), ("c", 0, 6)]
+    assert p3.tokens == 8
+
+
+def test_finish_reasons_and_pages_come_back():
+    m = manager(n_pages=16, ctx=12)
+    s = Scheduler(m, token_budget=32, eos_token_ids=[99])
+    a, b, c = req("a", 3, max_tokens=2), req("b", 3, max_tokens=50), req("c", 9, max_tokens=50)
+    for r in (a, b, c):
+        s.add(r)
+    done = run_plan(s, s.plan())
+    assert not done
+    done = run_plan(s, s.plan())
+    assert done == [a] and a.finish_reason == "length" and a.output == [7, 7]
+    done = run_plan(s, s.plan(), token=99)     # end of sequence
+    assert {r.id for r in done} == {"b", "c"} and b.finish_reason == "stop"
+    assert m.free_pages() == [16] and not s.has_work()
+    d = req("d", 9, max_tokens=50)             # runs into the context of 12
+    s.add(d)
+    while s.has_work():
+        run_plan(s, s.plan())
+    assert d.finish_reason == "length" and d.sequence_len == 12
+    e = req("e", 3, max_tokens=3)
+    e.params.ignore_eos = True
+    s.add(e)
+    while s.has_work():
+        run_plan(s, s.plan(), token=99)
+    assert e.finish_reason == "length" and e.output == [99, 99, 99]
+
+
+def test_refuses_bad_prompts():
+    s = Scheduler(manager(ctx=16))
+    with pytest.raises(ValueError, match="empty"):
+        s.add(req("a", 0))
+    with pytest.raises(ValueError, match="does not fit the context"):
+        s.add(req("a", 16))
+
+
+def test_pages_run_out_newest_is_preempted_and_recomputed():
+    m = manager(n_pages=6, page=4, ctx=64, max_requests=4)
+    s = Scheduler(m, token_budget=64)
+    a, b = req("a", 11, max_tokens=6), req("b", 11, max_tokens=6)
+    s.add(a), s.add(b)
+    run_plan(s, s.plan())           # both prompts: 3 pages each, pool full, 12 tokens each
+    assert m.free_pages() == [0]
+    p = s.plan()                    # both decode at position 11: fits the held pages
+    assert not p.preempted and len(p.entries) == 2
+    run_plan(s, p)
+    p = s.plan()                    # position 12 needs a fourth page each: none free
+    assert p.preempted == [b] and b.state == WAITING and b.computed == 0 and b.preemptions == 1
+    assert [(e.request.id, e.count) for e in p.entries] == [("a", 1)]   # b waits: no room
+    assert s.waiting[0] is b
+    run_plan(s, p)
+    while a.state != FINISHED:
+        run_plan(s, s.plan())
+    # b comes back and recomputes prompt + what it had generated, in one portion
+    p = s.plan()
+    assert [(e.request.id, e.start, e.count, e.samples) for e in p.entries] == \
+        [("b", 0, 11 + len(b.output), True)]
+    while s.has_work():
+        run_plan(s, s.plan())
+    assert len(b.output) == 6 and m.free_pages() == [6]
+    assert s.counters["preemptions"] == 1
+    m.check_invariants()
+
+
+def test_a_request_too_large_for_the_cache_fails_alone():
+    m = manager(n_pages=3, page=4, ctx=64)
+    s = Scheduler(m, token_budget=64)
+    a = req("a", 10, max_tokens=30)
+    s.add(a)
+    run_plan(s, s.plan())
+    while s.has_work():
+        p = s.plan()
+        if p.failed:
+            break
+        run_plan(s, p)
+    assert a.state == FINISHED and a.finish_reason == "error" and "KV cache full" in a.error
+    assert m.free_pages() == [3]
+    big = req("big", 40)
+    s.add(big)
+    p = s.plan()        # the prompt is cut to what fits, then sticks: fails alone
+    while s.has_work() and not p.failed:
+        run_plan(s, p)
+        p = s.plan()
+    assert big.finish_reason == "error" and m.free_pages() == [3]
+
+
+def test_prompt_portion_shrinks_to_free_pages():
+    m = manager(n_pages=5, page=4, ctx=64)
+    s = Scheduler(m, token_budget=64)
+    a, b = req("a", 10, max_tokens=8), req("b", 30, max_tokens=2)
+    s.add(a), s.add(b)
+    p = s.plan()
+    # a takes 3 pages; b gets what is left: 2 pages = 8 tokens of its prompt
+    assert [(e.request.id, e.count) for e in p.entries] == [("a", 10), ("b", 8)]
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_random_load_finishes_everything(seed):
+    rng = random.Random(seed)
+    m = manager(n_pages=12, page=4, ctx=48, max_requests=3, window=9, layers=1)
+    s = Scheduler(m, token_budget=16)
+    reqs = [req(i, rng.randint(1, 20), max_tokens=rng.randint(1, 12)) for i in range(12)]
+    pending = list(reqs)
+    steps = 0
+    while pending or s.has_work():
+        if pending and rng.random() < 0.4:
+            s.add(pending.pop(0))
+        if s.has_work():
+            p = s.plan()
+            assert p.tokens <= 16
+            assert len({e.request.id for e in p.entries}) == len(p.entries)
+            run_plan(s, p, token=rng.randint(0, 5))
+            m.check_invariants()
+        steps += 1
+        assert steps < 5000
+    assert all(r.state == FINISHED and r.finish_reason in ("length", "stop") for r in reqs)
+    assert all(len(r.output) == r.params.max_tokens or r.sequence_len == 48 for r in reqs)
+    assert m.free_pages() == [12, 12]

@@ -1,0 +1,334 @@
+"""The engine through its entry point, the sampler on the device, the parts alone, and parts
+defined by a test."""
+import dataclasses
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen3_plain as P
+from util import TINY, assert_close, config_json, model_dir, plain_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def plain_greedy(name, dtype, prompt, n, margin):
+    """Greedy continuation by the plain implementation; also says at which steps its two best
+    logits are closer than ``margin`` (there the engine's rounding may pick the other)."""
+    seq, out, close = list(prompt), [], []
+    for _ in range(n):
+        l = plain_logits(name, dtype, seq)[-1]
+        top = np.sort(l)[-2:]
+        close.append(top[1] - top[0] <= margin * max(1.0, np.abs(l).max()))
+        out.append(int(np.argmax(l)))
+        seq.append(out[-1])
+    return out, close
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_the_entry_point(name, dtype):
+    from llmario_b200 import Engine, SamplingParams
+    eng = Engine(model_dir(name, dtype), dtype=dtype, page_size=TINY[name]["page_size"],
+                 cache_tokens=512, max_requests=4, context=256, token_budget=16)
+    prompts = [random_tokens(name, n, 40 + n) for n in (5, 11, 17)]      # the workload of config A
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8))
+    margin = 1e-4 if dtype == "float32" else 3e-2
+    for prompt, out in zip(prompts, outs):
+        assert len(out) == 8
+        want, close = plain_greedy(name, dtype, prompt, 8, margin)
+        for i, (a, b) in enumerate(zip(out, want)):
+            if close[i]:
+                break            # a near-tie: later tokens may legitimately differ
+            assert a == b, f"{name} {dtype}: token {i} is {a}, plain {b}"
+    st = eng.stats()
+    assert st["finished"] == 3 and st["free_pages"] == st["pages"]
+    assert st["max_entries_in_step"] >= 2            # requests shared steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(dtype):
+    """300 tokens one by one from an empty cache (first tokens included) against the whole."""
+    from llmario_b200.engine import Model, ModelRunner, StepEntry
+    name = "C"
+    toks = random_tokens(name, 300, 9)
+    model = Model.from_folder(model_dir(name, dtype), dtype, DEV)
+    runner = ModelRunner(model, page_size=16, n_pages=20, max_requests=2, max_context=320)
+    rows = [runner.step([StepEntry("r", [t], [0])])[0].cpu().numpy() for t in toks]
+    assert_close(np.stack(rows), plain_logits(name, dtype, toks), dtype, f"long decode {dtype}")
+
+
+def test_float32_weights_stay_float32_in_bfloat16_mode():
+    """A folder stored in 32-bit, run with --dtype bfloat16: the matrices stay 32-bit and the
+    result is closer to the plain implementation than bfloat16 weights would allow."""
+    from llmario_b200.engine import Model, ModelRunner, StepEntry
+    name = "B"
+    model = Model.from_folder(model_dir(name, "float32"), "bfloat16", DEV)
+    assert model.blocks[0].mixer.o_proj.weight.dtype == torch.float32
+    runner = ModelRunner(model, page_size=8, n_pages=16, max_requests=2, max_context=128)
+    toks = random_tokens(name, 50, 3)
+    got = runner.step([StepEntry("r", toks, list(range(50)))]).cpu().numpy()
+    assert_close(got, plain_logits(name, "float32", toks), "bfloat16", "f32 weights, bf16 mode")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_run_order_twice_and_shared_cache(dtype):
+    """The order of layers is data: a layer run twice (own cache each time) and a call that
+    reads an earlier call's cache, against the plain implementation with the same order."""
+    from llmario_b200.config import LayerCall, load_spec
+    from llmario_b200.engine import Model, ModelRunner, StepEntry
+    name = "A"
+    d = model_dir(name, dtype)
+    spec = load_spec(d)
+    order = (LayerCall(0), LayerCall(1), LayerCall(1), LayerCall(0, reads_cache_of=1))
+    model = Model.from_folder(d, dtype, DEV, spec=dataclasses.replace(spec, run_order=order))
+    runner = ModelRunner(model, page_size=4, n_pages=64, max_requests=2, max_context=128)
+    assert len(runner.cache.groups) == 1 and len(runner.cache.groups[0].entries) == 3
+    toks = random_tokens(name, 37, 4)
+    tensors, cfg = P.load(d)
+    ref = P.forward_logits(tensors, cfg, toks, schedule=[(0, None), (1, None), (1, None), (0, 1)]).numpy()
+    got = [runner.step([StepEntry("r", toks[:20], list(range(20)))]).cpu().numpy()]
+    got += [runner.step([StepEntry("r", [t], [0])]).cpu().numpy() for t in toks[20:]]
+    assert_close(np.concatenate(got), ref, dtype, f"run order {dtype}")
+
+
+# ----------------------------------------------------------------------------- sampler
+def test_device_sampler_matches_plain_chain():
+    from llmario_b200.sampling import DeviceSampler, RequestSampler, SamplingParams
+    rng = random.Random(0)
+    V = 1000
+    g = torch.Generator().manual_seed(0)
+    sampler = DeviceSampler(DEV)
+    cases = [dict(temperature=0.0), dict(temperature=1.0, top_k=0, top_p=1.0, min_p=0.0),
+             dict(temperature=0.7, top_k=0, top_p=1.0, min_p=0.0),
+             dict(temperature=0.7, top_k=40, top_p=1.0, min_p=0.0),
+             dict(temperature=1.3, top_k=5, top_p=0.8, min_p=0.0),
+             dict(temperature=1.0, top_k=0, top_p=0.9, min_p=0.0),
+             dict(temperature=0.8, top_k=0, top_p=1.0, min_p=0.1),
+             dict(),                                  # the defaults: 40 / 0.95 / 0.05
+             dict(temperature=1.0, top_k=1), dict(temperature=2.0, top_k=V + 5, top_p=0.5)]
+    for trial in range(6):
+        logits = (3.0 * torch.randn(len(cases), V, generator=g)).float()
+        logits[:, 17] = logits[:, 400] = logits.max() + 0.5        # a tie at the top
+        rs = []
+        for c in cases:
+            r = RequestSampler(SamplingParams(seed=trial * 100 + len(rs), **c), V)
+            rs.append(r)
+        twins = [P.PlainRng(r.seed) for r in rs]
+        got = sampler.sample(logits.to(DEV), rs)
+        for i, c in enumerate(cases):
+            p = SamplingParams(**c)
+            u = 0.0 if p.greedy else twins[i].next_f64()
+            want = P.plain_sample(logits[i].tolist(), temperature=p.temperature, top_k=p.top_k,
+                                  top_p=p.top_p, min_p=p.min_p, u=u)
+            assert got[i] == want, (trial, c, u)
+
+
+def test_device_sampler_penalties_and_streams():
+    from llmario_b200.sampling import DeviceSampler, RequestSampler, SamplingParams
+    V = 64
+    logits = torch.zeros(2, V)
+    logits[:, 3], logits[:, 9] = 5.0, 4.9
+    pen = RequestSampler(SamplingParams(temperature=0, repeat_penalty=1.5), V)
+    pen.accept(3)
+    plain = RequestSampler(SamplingParams(temperature=0), V)
+    assert DeviceSampler(DEV).sample(logits.to(DEV), [pen, plain]) == [9, 3]
+    freq = RequestSampler(SamplingParams(temperature=0, frequency_penalty=0.06,
+                                         presence_penalty=0.0, repeat_last_n=2), V)
+    for t in (3, 3, 3):
+        freq.accept(t)                       # window of 2: count 2 -> 5.0 - 0.12 < 4.9
+    assert list(freq.window) == [3, 3] and freq.counts == {3: 2}
+    assert DeviceSampler(DEV).sample(logits[:1].to(DEV), [freq]) == [9]
+    # a seed gives the same tokens whatever else is in the batch; frequencies follow the softmax
+    l = torch.log(torch.tensor([0.5, 0.3, 0.2] + [1e-9] * (V - 3)))[None, :]
+    params = SamplingParams(temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, seed=7)
+    a = RequestSampler(params, V)
+    alone = [DeviceSampler(DEV).sample(l.to(DEV), [a])[0] for _ in range(300)]
+    b = RequestSampler(params, V)
+    other = RequestSampler(SamplingParams(temperature=0.9, seed=1), V)
+    mixed = [DeviceSampler(DEV).sample(l.repeat(2, 1).to(DEV), [other, b])[1] for _ in range(300)]
+    assert alone == mixed
+    freqs = [alone.count(i) / 300 for i in range(3)]
+    assert abs(freqs[0] - 0.5) < 0.09 and abs(freqs[1] - 0.3) < 0.09 and abs(freqs[2] - 0.2) < 0.08
+
+
+def test_temperature_generation_is_reproducible_and_batch_independent():
+    """Config B's workload: four requests of 1/7/23/40 tokens, prompts cut at 16 beside
+    running decodes, 12 tokens at temperature 0.7 with a seed."""
+    from llmario_b200 import Engine, SamplingParams
+    name, dtype = "B", "float32"
+    prompts = [random_tokens(name, n, 70 + n) for n in (1, 7, 23, 40)]
+    params = [SamplingParams(temperature=0.7, seed=11 + i, max_tokens=12) for i in range(4)]
+
+    def run(order, budget):
+        eng = Engine(model_dir(name, dtype), dtype=dtype, page_size=8, cache_tokens=512,
+                     max_requests=4, context=128, token_budget=budget)
+        outs = eng.generate([prompts[i] for i in order], [params[i] for i in order])
+        return {i: o for i, o in zip(order, outs)}
+
+    a = run([0, 1, 2, 3], 16)
+    b = run([3, 2, 1, 0], 64)
+    alone = {i: run([i], 16)[i] for i in range(4)}
+    assert all(len(a[i]) == 12 for i in range(4))
+    assert a == alone            # same seed, same logits (to rounding) -> same tokens
+    assert a == b
+
+
+# ----------------------------------------------------------------------------- parts alone
+def test_parts_alone():
+    """Each part built from its spec and stepped by itself against the plain functions."""
+    from llmario_b200.cache import CacheManager
+    from llmario_b200.config import load_spec
+    from llmario_b200.parts import BoundCall, Segment, StepContext, Workspace, build_part
+    from llmario_b200.weights import load_weights
+    name, dtype = "C", "float32"
+    d = model_dir(name, dtype)
+    spec = load_spec(d)
+    weights = load_weights(d, spec, torch.float32, DEV)
+    tensors, cfg = P.load(d)
+    T, hidden = 23, spec.hidden_size
+    x64 = torch.randn(T, hidden, dtype=torch.float64)
+    x = x64.float().to(DEV)
+
+    norm = build_part("norm", spec.final_norm, weights, torch.float32, DEV)
+    out = torch.empty_like(x)
+    norm.apply(None, x, out)
+    ref = P.rms_norm(x64, tensors["model.norm.weight"], cfg["eps"])
+    assert (out.double().cpu() - ref).abs().max() < 1e-5
+
+    layer = spec.layers[1]                      # a layer with a window
+    mixer = build_part("mixer", layer.mixer, weights, torch.float32, DEV)
+    ffn = build_part("feed_forward", layer.feed_forward, weights, torch.float32, DEV)
+    cache = CacheManager([mixer.cache_need()], [None], 16, 8, 2, 64)
+    cache.allocate_storage(torch.float32, DEV)
+    cache.open("r")
+    cache.reserve([("r", T)])
+    (upd,) = cache.take_table_updates()
+    for s, j, p in upd:
+        cache.groups[0].table[s, j] = int(p)
+    ar = torch.arange(T, dtype=torch.int32, device=DEV)
+    ctx = StepContext(rows=T, tokens=ar, row_pos=ar, row_slot=torch.zeros_like(ar),
+                      segments=[Segment("r", 0, 0, T, 0)], dtype=torch.float32,
+                      device=torch.device(DEV), workspace=Workspace(torch.device(DEV)), cache=cache)
+    acc = torch.zeros_like(x)
+    mixer.forward(ctx, BoundCall(0, 1, True, 0), x, acc)
+    ref, _ = P.attention_mixer(x64, torch.arange(T), tensors, "model.layers.1.self_attn.", cfg,
+                               cfg["windows"][1])
+    assert cfg["windows"][1] == 21
+    assert (acc.double().cpu() - ref).abs().max() < 1e-5
+
+    acc.zero_()
+    ffn.forward(ctx, x, acc)
+    p = "model.layers.1.mlp."
+    ref = P.swiglu_ffn(x64, tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"],
+                       tensors[p + "down_proj.weight"])
+    assert (acc.double().cpu() - ref).abs().max() < 1e-5
+
+    emb = build_part("embedding", spec.embedding, weights, torch.float32, DEV)
+    toks = torch.tensor(random_tokens(name, T, 1), dtype=torch.int32, device=DEV)
+    e = torch.empty_like(x)
+    emb.forward(ctx, toks, e)
+    assert torch.equal(e.cpu(), tensors["model.embed_tokens.weight"][toks.cpu().long()].float())
+    head = build_part("head", spec.head, weights, torch.float32, DEV)
+    logits = torch.empty(T, spec.vocab_size, dtype=torch.float32, device=DEV)
+    head.forward(ctx, x, logits)
+    assert (logits.double().cpu() - P.linear(x64, tensors["lm_head.weight"])).abs().max() < 1e-4
+
+    pos = build_part("position", layer.mixer["position"], weights, torch.float32, DEV)
+    inv_freq, rot, factor = pos.rotary_tables()
+    want = cfg["theta"] ** (-(2.0 * np.arange(rot // 2)) / rot)
+    assert rot == cfg["head_dim"] and factor == 1.0
+    assert np.abs(inv_freq.cpu().numpy() / want - 1).max() < 1e-6
+
+
+# ----------------------------------------------------------------------------- a toy mixer
+class RunningMeanMixer:
+    """A mixer with a state of its own, defined here and not in the package: the state of a
+    request is the running sum of its inputs and their count; the output at a token is
+    W (mean of the inputs up to and including it)."""
+
+    def __init__(self, spec, weights, dtype, device):
+        self.hidden = spec["hidden_size"]
+        self.weight = weights[spec["tensors"]["mix"][0]].float()
+
+    def cache_need(self):
+        from llmario_b200.cache import FixedState
+        return FixedState((self.hidden + 1,), torch.float32)
+
+    def forward(self, ctx, call, h, x):
+        state = ctx.cache.state_of(call.cache_entry)
+        for seg in ctx.segments:
+            rows = h[seg.row_start:seg.row_start + seg.rows].float()
+            s = state[seg.slot]
+            sums = s[:self.hidden] + rows.cumsum(0)
+            counts = s[self.hidden] + torch.arange(1, seg.rows + 1, device=h.device)
+            x[seg.row_start:seg.row_start + seg.rows] += (sums / counts[:, None]) @ self.weight.T
+            s[:self.hidden] = sums[-1]
+            s[self.hidden] = counts[-1]
+
+
+def toy_spec(spec):
+    """Config A with the mixer of layer 1 replaced by the running-mean mixer."""
+    from llmario_b200.config import LayerSpec, PartSpec
+    hidden = spec.hidden_size
+    toy = PartSpec("running_mean", {"hidden_size": hidden,
+                                    "tensors": {"mix": ("toy.mix.weight", (hidden, hidden))}})
+    layers = list(spec.layers)
+    layers[1] = dataclasses.replace(layers[1], mixer=toy)
+    return dataclasses.replace(spec, layers=tuple(layers))
+
+
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
+    from llmario_b200.config import load_spec
+    from llmario_b200.engine import Model, ModelRunner, StepEntry
+    from llmario_b200.parts import register_part, unregister_part
+    from llmario_b200.weights import expected_tensors, random_tensors
+    register_part("mixer", "running_mean", RunningMeanMixer, replace=True)
+    try:
+        spec = toy_spec(load_spec(model_dir("A", "float32")))
+        names = expected_tensors(spec)
+        assert "toy.mix.weight" in names and "model.layers.1.self_attn.q_proj.weight" not in names
+        weights = random_tensors(spec, 5, torch.float32, DEV)
+        host = {k: v.double().cpu() for k, v in weights.items()}
+        model = Model(spec, weights, torch.float32, DEV)
+        runner = ModelRunner(model, page_size=4, n_pages=32, max_requests=3, max_context=64)
+        assert len(runner.cache.groups) == 1 and list(runner.cache.state) == [1]
+
+        def reference(tokens):
+            cfg = P.read_config(model_dir("A", "float32"))
+            xx = P.embed(host["model.embed_tokens.weight"], tokens)
+            pos = torch.arange(len(tokens))
+            xx, _ = P.decoder_layer(xx, pos, host, 0, cfg)
+            p = "model.layers.1."
+            h = P.rms_norm(xx, host[p + "input_layernorm.weight"], cfg["eps"])
+            mean = h.cumsum(0) / torch.arange(1, len(tokens) + 1)[:, None]
+            xx = xx + mean @ host["toy.mix.weight"].T
+            h = P.rms_norm(xx, host[p + "post_attention_layernorm.weight"], cfg["eps"])
+            xx = xx + P.swiglu_ffn(h, host[p + "mlp.gate_proj.weight"], host[p + "mlp.up_proj.weight"],
+                                   host[p + "mlp.down_proj.weight"])
+            return P.linear(P.rms_norm(xx, host["model.norm.weight"], cfg["eps"]),
+                            host["model.embed_tokens.weight"]).numpy()
+
+        a, b = random_tokens("A", 21, 1), random_tokens("A", 13, 2)
+        got = {"a": [], "b": []}
+        # two requests interleaved in portions: each keeps a state of its own
+        plan = [[("a", 0, 5)], [("a", 5, 3), ("b", 0, 6)], [("b", 6, 1)], [("a", 8, 13), ("b", 7, 6)]]
+        toks = {"a": a, "b": b}
+        for step in plan:
+            entries = [StepEntry(r, toks[r][s:s + n], list(range(n))) for r, s, n in step]
+            out = runner.step(entries).cpu().numpy()
+            at = 0
+            for r, s, n in step:
+                got[r].append(out[at:at + n])
+                at += n
+        assert_close(np.concatenate(got["a"]), reference(a), "float32", "toy mixer a")
+        assert_close(np.concatenate(got["b"]), reference(b), "float32", "toy mixer b")
+        # a slot that is used again starts from a zero state
+        runner.close("a"), runner.close("b")
+        out = runner.step([StepEntry("c", b, list(range(len(b))))]).cpu().numpy()
+        assert_close(out, reference(b), "float32", "toy mixer, slot used again")
+    finally:
+        unregister_part("mixer", "running_mean")
