@@ -1,0 +1,406 @@
+// Matrix product on the 5th-generation tensor cores (tcgen05) for bfloat16 operands:
+//     C[t][n] (=|+=) sum_k X[t][k] * W[n][k]          X: [T][K] activations, W: [N][K] weights
+// computed transposed, D = W X^T: a CTA owns 128 weight rows (the UMMA "M" side, one TMEM lane per
+// output feature) and a tile of BN tokens (the UMMA "N" side, one TMEM column per token).  Because
+// the weights sit on the 128-wide side, the same kernel serves a prompt portion of thousands of
+// tokens and a decode step of a few: BN goes from 16 to 256 and the weight tile is streamed once.
+//
+//   warp 0   producer: TMA loads of the W tile (128 x 64) and the X tile (BN x 64), both K-major
+//            with the 128-byte swizzle, into a ring of STAGES shared-memory stages (mbarriers)
+//   warp 1   allocates TMEM; one lane issues tcgen05.mma (128 x BN x 16 per instruction, four per
+//            stage) and frees stages with tcgen05.commit
+//   warps 2-5  epilogue: tcgen05.ld of the 32 TMEM lanes of their quarter, then coalesced stores
+//
+// Epilogues: store bfloat16 / float32, add into a float32 residual stream, or the gated
+// activation silu(g) * u with 64 gate rows and their 64 up rows in one 128-row tile.  With
+// gridDim.z > 1 the K range is split and the partial sums are added with float atomics.
+//
+// Every wait on an mbarrier is bounded; when a bound runs out the kernel records where in
+// *status, drains the loads it still has in flight, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_M = 128;       // weight rows per CTA
+constexpr int TILE_K = 64;        // bf16 elements per stage row: 128 bytes, one swizzle span
+constexpr int UMMA_K = 16;
+constexpr long long WAIT_CYCLES = 4000000000LL;
+
+enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_GATED = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// Bounded wait for the phase with the given parity: polls without blocking and gives up after
+// WAIT_CYCLES clock cycles (about two seconds).  Returns false when the bound ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  long long start = 0;
+  for (uint32_t i = 0;; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (i == 64) start = clock64();
+    if (i > 64) {
+      __nanosleep(32);
+      if ((i & 255u) == 0 && clock64() - start > WAIT_CYCLES) return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, both operands K-major bf16, accumulate in float32
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Shared-memory matrix descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of eight
+// rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BN>
+constexpr uint32_t instr_desc() {
+  // float32 accumulator, bf16 A and B, both K-major, N = BN, M = 128
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct alignas(1024) SharedStorage {
+  uint8_t a[STAGES][TILE_M * TILE_K * 2];
+  uint8_t b[STAGES][BN * TILE_K * 2 < 1024 ? 1024 : BN * TILE_K * 2];
+  float gate_exchange[64][17];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+};
+
+// grid: (feature tiles, token tiles, K splits).  Features per tile: 128, or 64 when gated.
+template <int BN, int STAGES, int EPI, typename TC>
+__global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+    TC* __restrict__ C, int ldc, int T, int N, int K, int half, int* __restrict__ status) {
+  extern __shared__ uint8_t raw[];
+  auto& sm = *reinterpret_cast<SharedStorage<BN, STAGES>*>(
+      (reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int feat_per_tile = EPI == EPI_GATED ? 64 : TILE_M;
+  const int n0 = blockIdx.x * feat_per_tile;
+  const int t0 = blockIdx.y * BN;
+  const int kblocks = (K + TILE_K - 1) / TILE_K;
+  const int per_split = (kblocks + gridDim.z - 1) / gridDim.z;
+  const int kb_begin = blockIdx.z * per_split;
+  const int kb_end = min(kblocks, kb_begin + per_split);
+  const int nkb = kb_end - kb_begin;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t STAGE_BYTES = TILE_M * TILE_K * 2 + BN * TILE_K * 2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    mbar_init(&sm.acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (nkb > 0) {
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------------- producer
+      int issued = 0;
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t round = i / STAGES;
+        ok = mbar_wait(&sm.empty[s], (round & 1) ^ 1);
+        if (!ok) { atomicExch(status, 1); break; }
+        mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+        const int k = (kb_begin + i) * TILE_K;
+        if (EPI == EPI_GATED) {
+          tma_load_2d(sm.a[s], &map_w, k, n0, &sm.full[s]);
+          tma_load_2d(sm.a[s] + 64 * TILE_K * 2, &map_w, k, half + n0, &sm.full[s]);
+        } else {
+          tma_load_2d(sm.a[s], &map_w, k, n0, &sm.full[s]);
+        }
+        tma_load_2d(sm.b[s], &map_x, k, t0, &sm.full[s]);
+        issued = i + 1;
+      }
+      if (!ok) {
+        // drain: the loads already issued must land before this CTA's shared memory is given up
+        for (int i = max(0, issued - STAGES); i < issued; ++i)
+          mbar_wait(&sm.full[i % STAGES], (i / STAGES) & 1);
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc = instr_desc<BN>();
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        ok = mbar_wait(&sm.full[s], (i / STAGES) & 1);
+        if (!ok) { atomicExch(status, 2); break; }
+        tc_fence_after();
+        const uint64_t da = smem_desc(smem_u32(sm.a[s]));
+        const uint64_t db = smem_desc(smem_u32(sm.b[s]));
+#pragma unroll
+        for (int k = 0; k < TILE_K / UMMA_K; ++k)
+          tc_mma(tmem, da + (uint64_t)(k * UMMA_K * 2 >> 4), db + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
+                 (i > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&sm.empty[s]);   // frees the stage when these MMAs have read it
+      }
+      tc_commit(&sm.acc_full);     // arrives when every MMA above has completed
+    } else if (warp >= 2) {
+      // ---------------------------------------------------------------- epilogue
+      const int q = warp & 3;                 // TMEM lane quarter this warp may read
+      const int row = q * 32 + lane;          // row of the 128-row tile
+      const bool ok = mbar_wait(&sm.acc_full, 0);
+      if (!ok && lane == 0) atomicExch(status, 3);
+      tc_fence_after();
+      if (ok) {
+        const bool split = gridDim.z > 1;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t v[16];
+          tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+          tmem_ld_wait();
+          if (EPI == EPI_GATED) {
+            // rows 0..63 hold gate, rows 64..127 the matching up values: hand them over
+            if (q >= 2) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) sm.gate_exchange[row - 64][j] = __uint_as_float(v[j]);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (q < 2) {
+              const int n = n0 + row;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int t = t0 + c + j;
+                if (t < T && n < half) {
+                  const float g = __uint_as_float(v[j]), u = sm.gate_exchange[row][j];
+                  C[(size_t)t * ldc + n] = from_f32<TC>(g / (1.0f + __expf(-g)) * u);
+                }
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          } else {
+            const int n = n0 + row;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c + j;
+              if (t < T && n < N) {
+                TC* dst = C + (size_t)t * ldc + n;
+                const float a = __uint_as_float(v[j]);
+                if (EPI == EPI_ACCUM || split) {
+                  if (split) atomicAdd(reinterpret_cast<float*>(dst), a);
+                  else *dst = from_f32<TC>(to_f32(*dst) + a);
+                } else {
+                  *dst = from_f32<TC>(a);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side: tensor maps (made once per matrix and cached) and launch
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long rows, cols, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    h ^= std::hash<long long>()(k.rows * 1315423911LL + k.cols * 2654435761LL + k.ld * 97 + k.box_rows) +
+         0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+// A [rows][cols] bf16 matrix with row stride ld (elements), tiled in boxes of box_rows x 64.
+bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiled enc = encoder();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+template <int BN, int STAGES, int EPI, typename TC>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K, int half,
+           int splits, int* status, cudaStream_t stream) {
+  auto kernel = gemm_tcgen05_kernel<BN, STAGES, EPI, TC>;
+  constexpr int smem = (int)sizeof(SharedStorage<BN, STAGES>) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int feat = EPI == EPI_GATED ? 64 : TILE_M;
+  const int limit = EPI == EPI_GATED ? half : N;
+  dim3 grid((limit + feat - 1) / feat, (T + BN - 1) / BN, splits);
+  kernel<<<grid, 192, smem, stream>>>(mw, mx, C, ldc, T, N, K, half, status);
+  return launch_status();
+}
+
+template <int EPI, typename TC>
+int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K,
+             int half, int splits, int* status, cudaStream_t stream) {
+  switch (bn) {
+    case 16: return launch<16, 6, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
+    case 32: return launch<32, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
+    case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
+    case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
+    case 256: return launch<256, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
+  }
+  return LLM_ERR_UNSUPPORTED;
+}
+}  // namespace
+
+// X [T][K] and W [N][K] bfloat16 with 16-byte aligned rows (K, lda, ldw multiples of 8).
+//   mode 0: C = X W^T (c_dtype bf16 or f32; with splits > 1: f32 and C zeroed by the caller)
+//   mode 1: C += X W^T (f32)
+//   mode 2: W = [gate; up] with `half` rows each, C[t][n] = silu(gate) * up, n < half
+// bn: token tile, one of 16, 32, 64, 128, 256.  status: device int, set non-zero when a wait
+// inside the kernel gave up.
+LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
+                                int lda, int ldw, int ldc, int mode, int half, int bn, int splits,
+                                int* status, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return LLM_ERR_UNSUPPORTED;
+  if (((uintptr_t)X | (uintptr_t)W) & 15) return LLM_ERR_UNSUPPORTED;
+  if (splits < 1) return LLM_ERR_ARGUMENT;
+  const int kblocks = (K + TILE_K - 1) / TILE_K;
+  if (splits > kblocks) splits = kblocks;
+  // no split may be empty
+  while (splits > 1 && (splits - 1) * ((kblocks + splits - 1) / splits) >= kblocks) --splits;
+  CUtensorMap mw, mx;
+  if (!tensor_map(W, N, K, ldw, mode == 2 ? 64 : TILE_M, &mw)) return LLM_ERR_UNSUPPORTED;
+  if (!tensor_map(X, T, K, lda, bn, &mx)) return LLM_ERR_UNSUPPORTED;
+  if (mode == 0) {
+    if (c_dtype == LLM_F32)
+      return dispatch<EPI_STORE, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, splits, status, stream);
+    if (c_dtype == LLM_BF16 && splits == 1)
+      return dispatch<EPI_STORE, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, half, 1, status, stream);
+    return LLM_ERR_UNSUPPORTED;
+  }
+  if (mode == 1) {
+    if (c_dtype != LLM_F32) return LLM_ERR_UNSUPPORTED;
+    return dispatch<EPI_ACCUM, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, splits, status, stream);
+  }
+  if (mode == 2) {
+    if (N != 2 * half) return LLM_ERR_ARGUMENT;
+    if (c_dtype == LLM_BF16)
+      return dispatch<EPI_GATED, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, half, 1, status, stream);
+    if (c_dtype == LLM_F32)
+      return dispatch<EPI_GATED, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, 1, status, stream);
+    return LLM_ERR_UNSUPPORTED;
+  }
+  return LLM_ERR_ARGUMENT;
+}

@@ -46,6 +46,7 @@ def _declare(l) -> None:
         "llm_attention_generic": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P],
         "llm_sample": [P, L, I, I, P, P, P, P, P, P, P],
         "llm_gemv_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, P],
+        "llm_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
     for name, args in sigs.items():
@@ -233,6 +234,56 @@ def gemv_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, ha
     N = w.shape[0]
     _check(lib().llm_gemv_bf16(_ptr(a), _ptr(w), _ptr(out), _dt(out), M, N, K, a.stride(0),
                                w.stride(0), out.stride(0), mode, half, _stream()), "gemv_bf16")
+
+
+_tc_status = {}
+
+
+def tc_status(device) -> torch.Tensor:
+    """The device word in which the tensor-core kernels record a wait that gave up."""
+    key = torch.device(device).index or 0
+    if key not in _tc_status:
+        _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_status[key]
+
+
+def check_tc_status(device) -> None:
+    """Raise if a tensor-core kernel gave up waiting (synchronises the device)."""
+    st = _tc_status.get(torch.device(device).index or 0)
+    if st is not None:
+        code = int(st.item())
+        if code:
+            st.zero_()
+            raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (role {code})")
+
+
+def token_tile(rows: int) -> int:
+    for bn in (16, 32, 64, 128):
+        if rows <= bn:
+            return bn
+    return 128
+
+
+def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1
+            and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, half: int = 0,
+                 bn: Optional[int] = None, splits: int = 1) -> None:
+    """Tensor-core product of bfloat16 operands.  mode 0: out = a w^T (bfloat16 or float32);
+    1: out += a w^T (float32); 2: out = silu(a wg^T) * (a wu^T), w = [wg; wu] of ``half`` rows
+    each.  ``bn``: token tile (16..256); ``splits`` > 1 splits K and adds partial sums with
+    atomics (mode 0 then needs ``out`` float32 and zeroed)."""
+    _cuda(a, w, out)
+    T, K = a.shape
+    N = w.shape[0]
+    assert out.stride(1) == 1
+    bn = bn or token_tile(T)
+    _check(lib().llm_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(out), _dt(out), T, N, K, a.stride(0),
+                                  w.stride(0), out.stride(0), mode, half, bn, splits,
+                                  _ptr(tc_status(a.device)), _stream()), "gemm_tcgen05")
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

@@ -224,3 +224,52 @@ def test_qk_norm_rope_store(dtype, Hq, Hkv, hd, page):
         assert (q_out[i].double().cpu().reshape(Hq, hd) - qr).abs().max() <= tol
         assert (storage[page_id, 0, 0, p % page].double().cpu() - kr).abs().max() <= tol
         assert (storage[page_id, 0, 1, p % page].double().cpu() - vr).abs().max() <= tol
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 128, 64), (16, 256, 128), (5, 200, 72), (40, 384, 4096),
+                                   (130, 130, 264), (300, 1000, 512), (64, 4096, 12288)])
+def test_gemm_tcgen05(T, N, K):
+    from llmario_b200 import kernels
+    a, w = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=3)
+    ref = a.double() @ w.double().t()
+    tol = 2e-5 * float(ref.abs().max()) * math.sqrt(K) + 1e-6
+    out = torch.full((T, N), 7.0, dtype=torch.float32, device=DEV)
+    kernels.gemm_tcgen05(a, w, out, 0)
+    kernels.check_tc_status(DEV)
+    assert (out.double() - ref).abs().max() <= tol
+    outb = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tcgen05(a, w, outb, 0)
+    assert (outb.double() - ref).abs().max() <= 2 ** -8 * float(ref.abs().max()) + tol
+    base = rnd(T, N, seed=9)
+    acc = base.clone()
+    kernels.gemm_tcgen05(a, w, acc, 1)
+    assert (acc.double() - (base.double() + ref)).abs().max() <= tol
+    for bn in (16, 64, 256):           # every token tile gives the same product
+        o2 = torch.empty(T, N, dtype=torch.float32, device=DEV)
+        kernels.gemm_tcgen05(a, w, o2, 0, bn=bn)
+        assert (o2.double() - ref).abs().max() <= tol, bn
+    if K >= 256:                       # K split in three, partial sums added
+        acc = base.clone()
+        kernels.gemm_tcgen05(a, w, acc, 1, splits=3)
+        assert (acc.double() - (base.double() + ref)).abs().max() <= tol
+        z = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+        kernels.gemm_tcgen05(a, w, z, 0, splits=2)
+        assert (z.double() - ref).abs().max() <= tol
+    kernels.check_tc_status(DEV)
+
+
+@pytest.mark.parametrize("T,ff,K", [(3, 64, 64), (20, 200, 136), (150, 1000, 512)])
+def test_gemm_tcgen05_gated(T, ff, K):
+    from llmario_b200 import kernels
+    a, w = rnd(T, K, dtype=torch.bfloat16), rnd(2 * ff, K, dtype=torch.bfloat16, seed=3, scale=0.3)
+    ref = a.double() @ w.double().t()
+    g, u = ref[:, :ff], ref[:, ff:]
+    want = g / (1 + torch.exp(-g)) * u
+    act = torch.empty(T, ff, dtype=torch.float32, device=DEV)
+    kernels.gemm_tcgen05(a, w, act, 2, ff)
+    kernels.check_tc_status(DEV)
+    tol = 1e-4 * max(1.0, float(want.abs().max())) * math.sqrt(K)
+    assert (act.double() - want).abs().max() <= tol
+    actb = torch.empty(T, ff, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tcgen05(a, w, actb, 2, ff)
+    assert (actb.double() - want).abs().max() <= 2 ** -8 * float(want.abs().max()) + tol
