@@ -364,7 +364,7 @@ int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ld
 }  // namespace
 
 // X [T][K] and W [N][K] bfloat16 with 16-byte aligned rows (K, lda, ldw multiples of 8).
-//   mode 0: C = X W^T (c_dtype bf16 or f32; with splits > 1: f32 and C zeroed by the caller)
+//   mode 0: C = X W^T (c_dtype bf16 or f32; with splits > 1: f32, zeroed here first)
 //   mode 1: C += X W^T (f32)
 //   mode 2: W = [gate; up] with `half` rows each, C[t][n] = silu(gate) * up, n < half
 // bn: token tile, one of 16, 32, 64, 128, 256.  status: device int, set non-zero when a wait
@@ -384,6 +384,10 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dty
   if (!tensor_map(W, N, K, ldw, mode == 2 ? 64 : TILE_M, &mw)) return LLM_ERR_UNSUPPORTED;
   if (!tensor_map(X, T, K, lda, bn, &mx)) return LLM_ERR_UNSUPPORTED;
   if (mode == 0) {
+    if (c_dtype == LLM_F32 && splits > 1) {   // partial sums are added into zeros
+      cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, T, stream);
+      if (e != cudaSuccess) return (int)e;
+    }
     if (c_dtype == LLM_F32)
       return dispatch<EPI_STORE, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, splits, status, stream);
     if (c_dtype == LLM_BF16 && splits == 1)
