@@ -1,0 +1,338 @@
+// Paged causal attention for bfloat16 with tensor cores: prompt portions and decode rows.
+//
+// A work item is a run of consecutive tokens of one request (a whole short portion, a slice of
+// a long one, or a single decode token).  A CTA takes one item and one KV head; its rows are
+// (token, query head of the group) pairs, so the K and V of the group are read once for all of
+// its query heads.  Keys are walked in tiles aligned to absolute positions; K and V tiles come
+// from the pages named by the block table through cp.async into swizzled shared memory, two
+// stages deep.  S = Q K^T and O += P V run on mma.sync m16n8k16 with 32-bit accumulators; the
+// softmax keeps a running maximum and sum per row in 32-bit (exp2 of scores pre-multiplied by
+// log2 e).  A mask hides keys after the query, keys before the window and keys of other tiles'
+// padding.  With splits > 1 the key range of an item is cut across blockIdx.z: every part
+// writes an unnormalised sum with its maximum and weight to scratch memory and a second kernel
+// merges them.
+//
+// Head sizes 32, 64 and 128; any number of heads and groups (the rows of a CTA are 16 per warp,
+// a group larger than that is refused by the host and served by the generic kernel).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* p) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* p) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// chunk (16 bytes) c of row r inside a tile with CPR chunks per row
+template <int CPR> __device__ __forceinline__ int swizzle(int r, int c) {
+  return CPR >= 8 ? (c ^ (r & 7)) : (c ^ ((r >> 1) & 3));
+}
+
+struct Item { int row_start, tokens, slot, pos_start; };
+
+template <int HD, int WARPS, int KT>
+__global__ void __launch_bounds__(WARPS * 32) flash_paged_kernel(
+    const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_o,
+    float* __restrict__ part_ml, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+    long long page_stride, const int* __restrict__ block_table, int table_stride,
+    const int* __restrict__ items, const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+    int Hq, int Hkv, int page_size, float scale_log2, int window, int splits) {
+  constexpr int CPR = HD / 8;            // 16-byte chunks per key row
+  constexpr int KS = HD / 16;            // k-steps of Q K^T
+  constexpr int NT = KT / 8;             // key n-tiles of S
+  constexpr int DT = HD / 8;             // dim n-tiles of O
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  bf16* ks = reinterpret_cast<bf16*>(smem_raw);               // [2][KT][HD]
+  bf16* vs = ks + 2 * KT * HD;                                 // [2][KT][HD]
+
+  // without a list of items every row of the step is an item of one token
+  const Item it = items ? reinterpret_cast<const Item*>(items)[blockIdx.x]
+                        : Item{(int)blockIdx.x, 1, row_slot[blockIdx.x], row_pos[blockIdx.x]};
+  const int kvh = blockIdx.y, z = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int rows_valid = it.tokens * G;
+  const int hi = it.pos_start + it.tokens - 1;
+  const int lo = (window > 0 && it.pos_start + 1 > window) ? it.pos_start + 1 - window : 0;
+  const int tile_first = lo / KT, tile_last = hi / KT;
+  const int ntiles = tile_last - tile_first + 1;
+  const int per = (ntiles + splits - 1) / splits;
+  const int tb0 = tile_first + z * per;
+  const int tb1 = min(tile_last + 1, tb0 + per);
+  const int* table = block_table + (size_t)it.slot * table_stride;
+
+  // this thread's two rows: r0 = warp*16 + g, r1 = r0 + 8
+  int rtok[2], rhead[2], rpos[2], rlo[2];
+  bool rvalid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + g + 8 * i;
+    rvalid[i] = r < rows_valid;
+    rtok[i] = rvalid[i] ? r / G : 0;
+    rhead[i] = kvh * G + (rvalid[i] ? r % G : 0);
+    rpos[i] = it.pos_start + rtok[i];
+    rlo[i] = (window > 0 && rpos[i] + 1 > window) ? rpos[i] + 1 - window : 0;
+  }
+
+  // Q fragments, kept for the whole kernel
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int k = 0; k < KS; ++k) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const bf16* src = q + ((size_t)(it.row_start + rtok[i]) * Hq + rhead[i]) * HD + k * 16 + 2 * t;
+      qf[k][i] = rvalid[i] ? *reinterpret_cast<const uint32_t*>(src) : 0u;
+      qf[k][i + 2] = rvalid[i] ? *reinterpret_cast<const uint32_t*>(src + 8) : 0u;
+    }
+  }
+
+  float o[DT][4];
+#pragma unroll
+  for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  auto load_tile = [&](int tb, int stage) {
+    bf16* kd = ks + stage * KT * HD;
+    bf16* vd = vs + stage * KT * HD;
+    for (int id = threadIdx.x; id < KT * CPR; id += WARPS * 32) {
+      const int j = id / CPR, c = id % CPR;
+      const int p = tb * KT + j;
+      const bool valid = p >= lo && p <= hi;
+      long long off = 0;
+      if (valid) {
+        const int page = table[p / page_size];
+        off = (long long)page * page_stride + ((long long)(p % page_size) * Hkv + kvh) * HD + c * 8;
+      }
+      const int dst = j * HD + swizzle<CPR>(j, c) * 8;
+      cp_async16(kd + dst, k_cache + off, valid);
+      cp_async16(vd + dst, v_cache + off, valid);
+    }
+  };
+
+  if (tb0 < tb1) load_tile(tb0, 0);
+  cp_async_commit();
+  for (int tb = tb0; tb < tb1; ++tb) {
+    const int stage = (tb - tb0) & 1;
+    if (tb + 1 < tb1) load_tile(tb + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const bf16* kt = ks + stage * KT * HD;
+    const bf16* vt = vs + stage * KT * HD;
+
+    if (warp * 16 < rows_valid) {
+      // ---- S = Q K^T
+      float s[NT][4];
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int k2 = 0; k2 < KS / 2; ++k2) {
+          uint32_t b[4];
+          const int row = n * 8 + (lane & 7), chunk = k2 * 4 + (lane >> 3);
+          ldmatrix_x4(b, kt + row * HD + swizzle<CPR>(row, chunk) * 8);
+          mma_bf16(s[n], qf[2 * k2], b[0], b[1]);
+          mma_bf16(s[n], qf[2 * k2 + 1], b[2], b[3]);
+        }
+      }
+      // ---- mask, running maximum, exponentials
+      const int base = tb * KT;
+      float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int p = base + n * 8 + 2 * t + (e & 1);
+          const bool vis = rvalid[i] && p <= rpos[i] && p >= rlo[i];
+          s[n][e] = vis ? s[n][e] * scale_log2 : -INFINITY;
+          tmax[i] = fmaxf(tmax[i], s[n][e]);
+        }
+      float corr[2], muse[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
+        tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
+        const float mnew = fmaxf(m[i], tmax[i]);
+        muse[i] = mnew == -INFINITY ? 0.f : mnew;
+        corr[i] = exp2f(m[i] - muse[i]);   // m = -inf gives 0
+        m[i] = mnew;
+        l[i] *= corr[i];
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pexp = exp2f(s[n][e] - muse[e >> 1]);
+          s[n][e] = pexp;
+          l[e >> 1] += pexp;
+        }
+#pragma unroll
+      for (int d = 0; d < DT; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[0];
+        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+      }
+      // ---- O += P V
+#pragma unroll
+      for (int kk = 0; kk < KT / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int d2 = 0; d2 < DT / 2; ++d2) {
+          uint32_t b[4];
+          const int mi = lane >> 3;
+          const int row = kk * 16 + (mi & 1) * 8 + (lane & 7), chunk = d2 * 2 + (mi >> 1);
+          ldmatrix_x4_trans(b, vt + row * HD + swizzle<CPR>(row, chunk) * 8);
+          mma_bf16(o[2 * d2], a, b[0], b[1]);
+          mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // ---- finish: the row sums are spread over the four threads of a row
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!rvalid[i]) continue;
+    const size_t rowhead = (size_t)(it.row_start + rtok[i]) * Hq + rhead[i];
+    if (splits == 1) {
+      const float inv = 1.0f / l[i];
+      bf16* dst = out + rowhead * HD;
+#pragma unroll
+      for (int d = 0; d < DT; ++d)
+        *reinterpret_cast<uint32_t*>(dst + d * 8 + 2 * t) =
+            pack_bf16(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+    } else {
+      float* dst = part_o + (rowhead * splits + z) * HD;
+#pragma unroll
+      for (int d = 0; d < DT; ++d)
+        *reinterpret_cast<float2*>(dst + d * 8 + 2 * t) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+      if (t == 0) {
+        part_ml[(rowhead * splits + z) * 2] = m[i];
+        part_ml[(rowhead * splits + z) * 2 + 1] = l[i];
+      }
+    }
+  }
+}
+
+// out[row][head] = sum_z 2^(m_z - m*) o_z / sum_z 2^(m_z - m*) l_z   over the parts of a row
+template <int HD>
+__global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                             bf16* __restrict__ out, const int* __restrict__ rows, int Hq, int splits) {
+  const size_t rowhead = (size_t)(rows ? rows[blockIdx.x] : (int)blockIdx.x) * Hq + blockIdx.y;
+  float mstar = -INFINITY;
+  for (int z = 0; z < splits; ++z) mstar = fmaxf(mstar, part_ml[(rowhead * splits + z) * 2]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f, lsum = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = part_ml[(rowhead * splits + z) * 2];
+      const float w = mz == -INFINITY ? 0.f : exp2f(mz - mstar);
+      acc += w * part_o[(rowhead * splits + z) * HD + d];
+      lsum += w * part_ml[(rowhead * splits + z) * 2 + 1];
+    }
+    out[rowhead * HD + d] = __float2bfloat16_rn(acc / lsum);
+  }
+}
+
+template <int HD, int WARPS, int KT>
+int launch(const bf16* q, bf16* out, float* part_o, float* part_ml, const bf16* kc, const bf16* vc,
+           long long page_stride, const int* table, int table_stride, const int* items,
+           const int* row_slot, const int* row_pos, int n_items, int Hq, int Hkv, int page_size,
+           float scale, int window, int splits, cudaStream_t s) {
+  auto kernel = flash_paged_kernel<HD, WARPS, KT>;
+  constexpr int smem = 4 * KT * HD * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(n_items, Hkv, splits);
+  kernel<<<grid, WARPS * 32, smem, s>>>(q, out, part_o, part_ml, kc, vc, page_stride, table, table_stride,
+                                       items, row_slot, row_pos, Hq, Hkv, page_size,
+                                       scale * 1.4426950408889634f, window, splits);
+  return launch_status();
+}
+}  // namespace
+
+// items: n_items x (first row, tokens, request slot, first position) int32 on the device; when
+// null, every one of the n_items rows is an item of one token described by row_slot / row_pos.
+// rows_per_cta 16: one warp per CTA (decode rows and very short portions, tokens * group <= 16);
+// rows_per_cta 64: four warps (tokens * group <= 64).  splits > 1 needs part_o
+// [rows*Hq*splits*hd] and part_ml [rows*Hq*splits*2] float scratch and is followed by
+// llm_attention_merge over the same rows.
+LLM_EXPORT int llm_attention_flash(const void* q, void* out, float* part_o, float* part_ml,
+                                   const void* k_cache, const void* v_cache, long long page_stride,
+                                   const int* block_table, int table_stride, const int* items,
+                                   const int* row_slot, const int* row_pos, int n_items,
+                                   int rows_per_cta, int Hq, int Hkv, int hd,
+                                   int page_size, float scale, int window, int splits,
+                                   cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv || splits < 1) return LLM_ERR_ARGUMENT;
+  if (splits > 1 && (!part_o || !part_ml)) return LLM_ERR_ARGUMENT;
+#define GO(HD, W, KT)                                                                                 \
+  return launch<HD, W, KT>((const bf16*)q, (bf16*)out, part_o, part_ml, (const bf16*)k_cache,          \
+                           (const bf16*)v_cache, page_stride, block_table, table_stride, items, row_slot, \
+                           row_pos, n_items,                                                          \
+                           Hq, Hkv, page_size, scale, window, splits, stream)
+  if (rows_per_cta == 16) {
+    if (hd == 128) GO(128, 1, 32);
+    if (hd == 64) GO(64, 1, 32);
+    if (hd == 32) GO(32, 1, 32);
+  } else if (rows_per_cta == 64) {
+    if (hd == 128) GO(128, 4, 64);
+    if (hd == 64) GO(64, 4, 64);
+    if (hd == 32) GO(32, 4, 64);
+  }
+#undef GO
+  return LLM_ERR_UNSUPPORTED;
+}
+
+LLM_EXPORT int llm_attention_merge(const float* part_o, const float* part_ml, void* out,
+                                   const int* rows, int n_rows, int Hq, int hd, int splits,
+                                   cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  dim3 grid(n_rows, Hq);
+  if (hd == 128) merge_kernel<128><<<grid, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, rows, Hq, splits);
+  else if (hd == 64) merge_kernel<64><<<grid, 64, 0, stream>>>(part_o, part_ml, (bf16*)out, rows, Hq, splits);
+  else if (hd == 32) merge_kernel<32><<<grid, 32, 0, stream>>>(part_o, part_ml, (bf16*)out, rows, Hq, splits);
+  else return LLM_ERR_UNSUPPORTED;
+  return launch_status();
+}

@@ -273,3 +273,62 @@ def test_gemm_tcgen05_gated(T, ff, K):
     actb = torch.empty(T, ff, dtype=torch.bfloat16, device=DEV)
     kernels.gemm_tcgen05(a, w, actb, 2, ff)
     assert (actb.double() - want).abs().max() <= 2 ** -8 * float(want.abs().max()) + tol
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (6, 3, 64, 8, 50),
+                                                   (4, 4, 32, 4, None), (16, 1, 128, 16, 200),
+                                                   (3, 1, 64, 32, None)])
+def test_attention_flash(Hq, Hkv, hd, page, window):
+    """The tensor-core kernel in its three uses: one-token items with the keys split and
+    merged, short portions in one warp, long portions in four warps."""
+    from llmario_b200 import kernels
+    dtype = torch.bfloat16
+    G = Hq // Hkv
+    lengths = [1, 33, 150, 64, 700, 385]
+    storage, table, ks, vs = paged_setup(lengths, page, Hkv, hd, dtype)
+    scale = 1 / math.sqrt(hd)
+    g = torch.Generator().manual_seed(5)
+
+    def check(rows, out, q, tol=2e-2):
+        for i, (r, p) in enumerate(rows):
+            ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
+            got = out[i].reshape(Hq, hd).double().cpu()
+            assert (got - ref).abs().max() <= tol, (i, r, p, (got - ref).abs().max())
+
+    # 1. decode rows: the last position of every request, keys split in 1, 3 and 5 parts
+    rows = [(r, n - 1) for r, n in enumerate(lengths)]
+    q = torch.randn(len(rows), Hq, hd, generator=g).to(dtype)
+    qd = q.reshape(len(rows), -1).to(DEV).contiguous()
+    slot = torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    for splits in (1, 3, 5):
+        out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
+        po = torch.empty(len(rows) * Hq * splits * hd, dtype=torch.float32, device=DEV)
+        pml = torch.empty(len(rows) * Hq * splits * 2, dtype=torch.float32, device=DEV)
+        kernels.attention_flash(qd, out, storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table,
+                                None, len(rows), 16, Hq, Hkv, hd, page, scale, window, splits,
+                                po, pml, slot, pos)
+        if splits > 1:
+            kernels.attention_merge(po, pml, out, None, len(rows), Hq, hd, splits)
+        check(rows, out, q)
+    # 2. portions: the tail of request 4 as items of changing length, small and large
+    small_cap, large_cap = max(1, 16 // G), max(1, 64 // G)
+    start = 700 - 150
+    sizes, at = [], start
+    for n in [1, small_cap, large_cap, 2, large_cap, 3, large_cap]:
+        n = min(n, 700 - at)
+        if n > 0:
+            sizes.append((at, n))
+            at += n
+    rows = [(4, p) for p in range(start, at)]
+    q = torch.randn(len(rows), Hq, hd, generator=g).to(dtype)
+    qd = q.reshape(len(rows), -1).to(DEV).contiguous()
+    out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
+    for cap, rpc in ((small_cap, 16), (large_cap, 64)):
+        items = [(p0 - start, n, 4, p0) for p0, n in sizes if (n <= small_cap) == (rpc == 16)]
+        if not items:
+            continue
+        dev = torch.tensor(items, dtype=torch.int32, device=DEV).reshape(-1)
+        kernels.attention_flash(qd, out, storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table,
+                                dev, len(items), rpc, Hq, Hkv, hd, page, scale, window)
+    check(rows, out, q)
