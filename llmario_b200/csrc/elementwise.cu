@@ -100,6 +100,24 @@ __global__ void table_update_kernel(int* __restrict__ table, int row_stride,
   if (i < n) table[(size_t)updates[3 * i] * row_stride + updates[3 * i + 1]] = updates[3 * i + 2];
 }
 
+// The same with the number of triples read from device memory (at most max_n), so that the
+// launch itself does not change from step to step.
+__global__ void table_update_counted_kernel(int* __restrict__ table, int row_stride,
+                                            const int* __restrict__ updates,
+                                            const int* __restrict__ count, int max_n) {
+  const int n = min(*count, max_n);
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    table[(size_t)updates[3 * i] * row_stride + updates[3 * i + 1]] = updates[3 * i + 2];
+}
+
+LLM_EXPORT int llm_table_update_counted(int* table, int row_stride, const int* updates,
+                                        const int* count, int max_n, cudaStream_t stream) {
+  if (max_n <= 0) return 0;
+  const int blocks = (max_n + 127) / 128 < 8 ? (max_n + 127) / 128 : 8;
+  table_update_counted_kernel<<<blocks, 128, 0, stream>>>(table, row_stride, updates, count, max_n);
+  return launch_status();
+}
+
 LLM_EXPORT int llm_table_update(int* table, int row_stride, const int* updates, int n,
                                 cudaStream_t stream) {
   if (n <= 0) return 0;

@@ -39,12 +39,17 @@ def _round4(n: int) -> int:
     return (n + 3) & ~3
 
 
+HEADER = 16                    # first words of the integer array: block-table changes per group
+GRAPH_UPDATES_PER_ROW = 4      # room for block-table changes per row in a recorded step
+
+
 class ModelRunner:
     """Owns the model, its cache and the per-step device buffers."""
 
     def __init__(self, model: Model, page_size: int = 16, n_pages: Optional[int] = None,
                  max_requests: int = 64, max_context: Optional[int] = None,
-                 token_budget: int = 2048, cache_tokens: Optional[int] = None):
+                 token_budget: int = 2048, cache_tokens: Optional[int] = None,
+                 use_graphs: bool = True):
         self.model = model
         self.device = model.device
         if self.device.type != "cuda":
@@ -68,7 +73,12 @@ class ModelRunner:
         self._meta_host: List[Optional[torch.Tensor]] = [None, None]
         self._meta_event: List[Optional[torch.cuda.Event]] = [None, None]
         self._flip = 0
-        self.counters = {"steps": 0, "rows": 0, "max_entries_in_step": 0, "refused_steps": 0}
+        self._meta_generation = 0
+        self.use_graphs = bool(use_graphs) and len(self.cache.groups) <= HEADER
+        self._graphs: Dict[Any, Any] = {}
+        self._graph_seen: Dict[Any, Any] = {}
+        self.counters = {"steps": 0, "rows": 0, "max_entries_in_step": 0, "refused_steps": 0,
+                         "graphs_recorded": 0, "graph_replays": 0}
 
     # ------------------------------------------------------------------ requests
     def open(self, request: Any) -> None:
@@ -120,6 +130,7 @@ class ModelRunner:
             self._meta_host = [torch.empty(cap, dtype=torch.int32, pin_memory=True)
                                for _ in range(2)]
             self._meta_event = [None, None]
+            self._meta_generation += 1
         i = self._flip
         self._flip ^= 1
         ev = self._meta_event[i]
@@ -164,20 +175,37 @@ class ModelRunner:
             segments.append(Segment(e.request, s, r0, n, p0))
             r0 += n
         updates = cache.take_table_updates()
-        o_tok, o_pos, o_slot = 0, _round4(rows), 2 * _round4(rows)
-        o_want = 3 * _round4(rows)
+        n_want = len(want)
+        max_pos = int(pos.max())
+
+        # A step of single tokens has the same launches every time: it is recorded once as a
+        # CUDA graph per (rows, wanted rows, context bucket) and replayed.  Its layout of the
+        # integer array is fixed, with room for a bounded number of block-table changes.
+        graph_key = None
+        if self.use_graphs and rows == len(entries) and not cache.state and \
+                all(len(u) <= GRAPH_UPDATES_PER_ROW * rows for u in updates):
+            bucket = 1 << max(7, max_pos.bit_length())
+            graph_key = (rows, n_want, bucket)
+        upd_cap = [GRAPH_UPDATES_PER_ROW * rows if graph_key else len(u) for u in updates]
+
+        o_tok = HEADER
+        o_pos, o_slot, o_want = o_tok + _round4(rows), o_tok + 2 * _round4(rows), \
+            o_tok + 3 * _round4(rows)
         o_upd = []
-        off = o_want + _round4(len(want))
-        for u in updates:
+        off = o_want + _round4(n_want)
+        for cap in upd_cap:
             o_upd.append(off)
-            off += _round4(3 * len(u))
+            off += _round4(3 * cap)
         dev, host, which = self._meta_buffers(off)
         h = host.numpy()
+        h[:HEADER] = 0
+        for gi, u in enumerate(updates):
+            h[gi] = len(u)
         h[o_tok:o_tok + rows] = tokens
         h[o_pos:o_pos + rows] = pos
         h[o_slot:o_slot + rows] = slot
         if want:
-            h[o_want:o_want + len(want)] = np.asarray(want, dtype=np.int32)
+            h[o_want:o_want + n_want] = np.asarray(want, dtype=np.int32)
         for u, o in zip(updates, o_upd):
             if len(u):
                 h[o:o + 3 * len(u)] = u.reshape(-1)
@@ -185,9 +213,6 @@ class ModelRunner:
         ev = torch.cuda.Event()
         ev.record()
         self._meta_event[which] = ev
-        for g, u, o in zip(cache.groups, updates, o_upd):
-            if len(u):
-                kernels.table_update(g.table, dev[o:o + 3 * len(u)], len(u))
         fresh = cache.take_fresh_slots()
         if fresh and cache.state:
             idx = torch.tensor(fresh, dtype=torch.long, device=self.device)
@@ -198,25 +223,68 @@ class ModelRunner:
                           row_pos=dev[o_pos:o_pos + rows], row_slot=dev[o_slot:o_slot + rows],
                           segments=segments, dtype=self.model.dtype, device=self.device,
                           workspace=self.workspace, cache=cache, fresh_slots=fresh,
-                          max_pos=int(pos.max()))
+                          max_pos=(graph_key[2] - 1) if graph_key else max_pos)
+        want_dev = dev[o_want:o_want + n_want]
 
-        # ---- the model
-        m = self.model
-        x = ctx.buffer("x", (rows, m.hidden_size), torch.float32)
-        m.embedding.forward(ctx, ctx.tokens, x)
-        for call in m.calls:
-            m.blocks[call.layer].forward(ctx, call, x)
+        def forward() -> torch.Tensor:
+            for gi, (g, o, cap) in enumerate(zip(cache.groups, o_upd, upd_cap)):
+                if graph_key:
+                    kernels.table_update_counted(g.table, dev[o:o + 3 * cap], dev[gi:gi + 1], cap)
+                elif cap:
+                    kernels.table_update(g.table, dev[o:o + 3 * cap], cap)
+            return self._forward(ctx, want_dev, n_want)
+
+        if graph_key is None:
+            logits = forward()
+        else:
+            logits = self._graph_step(graph_key, forward)
         for e in entries:
             cache.advance(e.request, len(e.tokens))
-
-        n_want = len(want)
-        logits = torch.empty((n_want, m.vocab_size), dtype=torch.float32, device=self.device)
-        if n_want:
-            hsel = ctx.buffer("head.h", (n_want, m.hidden_size))
-            m.final_norm.apply(ctx, x, hsel, dev[o_want:o_want + n_want])
-            m.head.forward(ctx, hsel, logits)
         c = self.counters
         c["steps"] += 1
         c["rows"] += rows
         c["max_entries_in_step"] = max(c["max_entries_in_step"], len(entries))
         return logits
+
+    def _forward(self, ctx: StepContext, want_dev: torch.Tensor, n_want: int) -> torch.Tensor:
+        """Embedding, every layer call of the run order, final norm and head at the wanted
+        rows.  Returns a view of a workspace buffer: read it before the next step."""
+        m = self.model
+        x = ctx.buffer("x", (ctx.rows, m.hidden_size), torch.float32)
+        m.embedding.forward(ctx, ctx.tokens, x)
+        for call in m.calls:
+            m.blocks[call.layer].forward(ctx, call, x)
+        logits = ctx.buffer("logits", (n_want, m.vocab_size), torch.float32)
+        if n_want:
+            hsel = ctx.buffer("head.h", (n_want, m.hidden_size))
+            m.final_norm.apply(ctx, x, hsel, want_dev)
+            m.head.forward(ctx, hsel, logits)
+        return logits
+
+    def _graph_step(self, key, forward) -> torch.Tensor:
+        """Run ``forward`` eagerly the first time a key is seen, record it the second time,
+        replay the recording from then on.  A recording is dropped when a workspace buffer or
+        the integer array has moved since."""
+        gen = (self.workspace.generation, self._meta_generation)
+        rec = self._graphs.get(key)
+        if rec is not None and rec[0] == gen:
+            rec[1].replay()
+            self.counters["graph_replays"] += 1
+            kernels.launches += rec[3]       # the kernels of this library inside the recording
+            return rec[2]
+        if self._graph_seen.get(key) != gen:
+            self._graph_seen[key] = gen          # warm: sizes every buffer, loads every kernel
+            out = forward()
+            if (self.workspace.generation, self._meta_generation) != gen:
+                self._graph_seen[key] = (self.workspace.generation, self._meta_generation)
+            return out
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = kernels.launches
+        with torch.cuda.graph(graph):
+            out = forward()
+        recorded = kernels.launches - before
+        self._graphs[key] = (gen, graph, out, recorded)
+        self.counters["graphs_recorded"] += 1
+        graph.replay()
+        return out

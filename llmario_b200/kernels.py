@@ -40,6 +40,7 @@ def _declare(l) -> None:
         "llm_rms_norm": [P, P, P, I, P, I, I, F, P],
         "llm_silu_mul": [P, P, I, I, I, P],
         "llm_table_update": [P, I, P, I, P],
+        "llm_table_update_counted": [P, I, P, P, I, P],
         "llm_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, I, I, P],
         "llm_qk_norm_rope_store": [P, I, P, P, P, I, L, P, I, P, P, P, P, P, F, I, I, I, I, I, I,
                                    F, I, I, P],
@@ -135,6 +136,15 @@ def table_update(table: torch.Tensor, updates: torch.Tensor, n: int) -> None:
     assert table.dtype == torch.int32 and updates.dtype == torch.int32
     _check(lib().llm_table_update(_ptr(table), table.stride(0), _ptr(updates), n, _stream()),
            "table_update")
+
+
+def table_update_counted(table: torch.Tensor, updates: torch.Tensor, count: torch.Tensor,
+                         max_n: int) -> None:
+    """As :func:`table_update`, the number of triples read from ``count[0]`` on the device."""
+    _cuda(table, updates, count)
+    assert table.dtype == torch.int32 and updates.dtype == torch.int32
+    _check(lib().llm_table_update_counted(_ptr(table), table.stride(0), _ptr(updates),
+                                          _ptr(count), max_n, _stream()), "table_update")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False

@@ -80,6 +80,7 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.generation = 0     # grows whenever a buffer moves: recorded launches are stale then
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -90,6 +91,7 @@ class Workspace:
         if buf is None or buf.numel() < n:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.generation += 1
         return buf[:n].view(*shape)
 
 
