@@ -336,3 +336,80 @@ LLM_EXPORT int llm_attention_merge(const float* part_o, const float* part_ml, vo
   else return LLM_ERR_UNSUPPORTED;
   return launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention with built-in scratch memory (declared in no_alloc.h).
+//
+// llm_attention_flash with split keys needs two float buffers that its caller allocates.  Some
+// callers of this library cannot allocate device memory at the moment they need attention: an
+// engine whose memory planner handed out every byte of the GPU before the first token (the
+// reference plans every byte before it loads a model, crates/engine/plan), a serving loop that
+// may not take the device-wide stall a cudaMalloc can cause, or a host that keeps all CUDA
+// allocation inside another framework's pool and forbids it elsewhere.  For them this one entry
+// point keeps its partial sums in a fixed array that is part of the library image: every GPU
+// that loads the library carries these 8 MiB until the process exits.
+//
+// * Limit: rows * Hq * splits * (hd + 2) floats must fit NO_ALLOC_SCRATCH_FLOATS (2 Mi floats);
+//   a larger request returns LLM_ERR_TOO_LARGE and launches nothing.
+// * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+//   that device current) and remembers it.  Make that first call outside any stream capture.
+// * It calls no cudaMalloc, cudaFree or other allocating routine.
+// * All calls share the one array and it keeps what the last call left.  Nothing in it has to
+//   start at zero: every (row, head, part) cell that the merge reads is written by the first
+//   kernel of the same call, parts without keys included.  Two calls that overlap on the GPU
+//   (different streams) race on it: order them.
+// ------------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_no_alloc_scratch[NO_ALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_scratch_address[MAX_DEVICES] = {nullptr};
+
+// The array's name is a host-side handle, not a device pointer: a kernel must be given the
+// address that the runtime reports for the current device.
+int scratch_address(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= MAX_DEVICES) return LLM_ERR_UNSUPPORTED;
+  if (!g_scratch_address[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_no_alloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_scratch_address[dev] = p;
+  }
+  *out = g_scratch_address[dev];
+  return 0;
+}
+}  // namespace
+
+LLM_EXPORT int llm_attention_decode_no_alloc(const void* q, void* out, const void* k_cache,
+                                             const void* v_cache, long long page_stride,
+                                             const int* block_table, int table_stride,
+                                             const int* row_slot, const int* row_pos, int rows,
+                                             int Hq, int Hkv, int hd, int page_size, float scale,
+                                             int window, int splits, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv || splits < 1 || hd <= 0) return LLM_ERR_ARGUMENT;
+  const long long need = (long long)rows * Hq * splits * (hd + 2);
+  if (need > (long long)NO_ALLOC_SCRATCH_FLOATS) return LLM_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int st = scratch_address(&scratch);
+  if (st != 0) return st;
+  float* part_o = scratch;                                        // [rows*Hq*splits][hd]
+  float* part_ml = scratch + (size_t)rows * Hq * splits * hd;     // [rows*Hq*splits][2]
+  int r;
+#define GO(HD)                                                                                        \
+  r = launch<HD, 1, 32>((const bf16*)q, (bf16*)out, part_o, part_ml, (const bf16*)k_cache,             \
+                        (const bf16*)v_cache, page_stride, block_table, table_stride, nullptr, row_slot, \
+                        row_pos, rows, Hq, Hkv, page_size, scale, window, splits, stream)
+  if (hd == 128) GO(128);
+  else if (hd == 64) GO(64);
+  else if (hd == 32) GO(32);
+  else return LLM_ERR_UNSUPPORTED;
+#undef GO
+  if (r != 0 || splits == 1) return r;
+  return llm_attention_merge(part_o, part_ml, out, nullptr, rows, Hq, hd, splits, stream);
+}
