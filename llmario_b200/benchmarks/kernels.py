@@ -1,0 +1,153 @@
+"""Time one kernel of the library on given sizes with CUDA events.
+
+    python -m llmario_b200.benchmarks.kernels gemm --rows 8 --out 24576 --in 4096 --mode gated
+    python -m llmario_b200.benchmarks.kernels attention --batch 8 --context 1024
+    python -m llmario_b200.benchmarks.kernels prefill-attention --tokens 2048
+
+Between timed launches a buffer larger than the L2 cache is overwritten unless ``--no-flush`` is
+given.  Prints the median time, the bytes or flops it stands for, and the rate.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+from .. import kernels
+
+DEV = "cuda:0"
+
+
+def timed(fn, reps: int, flush) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def cmd_gemm(a) -> None:
+    T, N, K = a.rows, a.out, getattr(a, "in")
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (0.02 * torch.randn(N, K, device=DEV)).bfloat16()
+    flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    if a.mode == "gated":
+        out = torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
+        fn = lambda: kernels.gemm_tcgen05(x, w, out, 2, N // 2, bn=a.tile)
+    elif a.mode == "accumulate":
+        out = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+        fn = lambda: kernels.gemm_tcgen05(x, w, out, 1, bn=a.tile, splits=a.splits)
+    elif a.mode == "gemv":
+        out = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+        fn = lambda: kernels.gemv_bf16(x, w, out, 0)
+    elif a.mode == "simt":
+        out = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+        fn = lambda: kernels.gemm_simt(x, w, out)
+    else:
+        out = torch.empty(T, N, dtype=torch.float32 if a.f32 else torch.bfloat16, device=DEV)
+        fn = lambda: kernels.gemm_tcgen05(x, w, out, 0, bn=a.tile, splits=a.splits)
+    ms = timed(fn, a.reps, flush)
+    kernels.check_tc_status(DEV)
+    print(f"gemm {a.mode} rows={T} out={N} in={K} tile={a.tile} splits={a.splits}: "
+          f"{ms * 1e3:.1f} us, weights {N * K * 2 / ms / 1e6:.0f} GB/s, "
+          f"{2.0 * T * N * K / ms / 1e9:.1f} TFLOP/s")
+
+
+def _paged(batch: int, context: int, Hkv: int, hd: int, page: int):
+    pages_per = -(-context // page)
+    n_pages = batch * pages_per
+    storage = torch.randn(n_pages, 1, 2, page, Hkv, hd, device=DEV).bfloat16()
+    perm = torch.randperm(n_pages, device=DEV).to(torch.int32)
+    return storage, perm.reshape(batch, pages_per).contiguous()
+
+
+def cmd_attention(a) -> None:
+    B, S, Hq, Hkv, hd, page = a.batch, a.context, a.heads, a.kv_heads, a.head_dim, a.page_size
+    storage, table = _paged(B, S, Hkv, hd, page)
+    q = torch.randn(B, Hq * hd, device=DEV).bfloat16()
+    out = torch.empty_like(q)
+    slot = torch.arange(B, dtype=torch.int32, device=DEV)
+    pos = torch.full((B,), S - 1, dtype=torch.int32, device=DEV)
+    splits = a.splits or kernels.decode_splits(B, Hkv, S)
+    po = torch.empty(B * Hq * splits * hd, dtype=torch.float32, device=DEV)
+    pml = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=DEV)
+    flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+
+    def fn():
+        kernels.attention_flash(q, out, storage[0, 0, 0], storage[0, 0, 1], storage.stride(0), table,
+                                None, B, 16, Hq, Hkv, hd, page, hd ** -0.5, None, splits, po, pml,
+                                slot, pos)
+        if splits > 1:
+            kernels.attention_merge(po, pml, out, None, B, Hq, hd, splits)
+
+    ms = timed(fn, a.reps, flush)
+    nbytes = B * S * Hkv * hd * 2 * 2
+    print(f"decode attention batch={B} context={S} heads={Hq}/{Hkv} hd={hd} splits={splits}: "
+          f"{ms * 1e3:.1f} us, cache {nbytes / ms / 1e6:.0f} GB/s")
+
+
+def cmd_prefill_attention(a) -> None:
+    T, Hq, Hkv, hd, page = a.tokens, a.heads, a.kv_heads, a.head_dim, a.page_size
+    storage, table = _paged(1, T, Hkv, hd, page)
+    q = torch.randn(T, Hq * hd, device=DEV).bfloat16()
+    out = torch.empty_like(q)
+    cap = max(1, 64 // (Hq // Hkv))
+    items = torch.tensor([[s, min(cap, T - s), 0, s] for s in range(0, T, cap)],
+                         dtype=torch.int32, device=DEV).reshape(-1)
+    n = items.numel() // 4
+    fn = lambda: kernels.attention_flash(q, out, storage[0, 0, 0], storage[0, 0, 1],
+                                         storage.stride(0), table, items, n, 64, Hq, Hkv, hd,
+                                         page, hd ** -0.5, None)
+    ms = timed(fn, a.reps, None)
+    flops = 2.0 * T * T * Hq * hd          # causal: half of QK^T and PV
+    print(f"prefill attention tokens={T} heads={Hq}/{Hkv} hd={hd}: {ms * 1e3:.1f} us, "
+          f"{flops / ms / 1e9:.1f} TFLOP/s (causal flops)")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--rows", type=int, default=8)
+    g.add_argument("--out", type=int, default=4096)
+    g.add_argument("--in", type=int, default=4096)
+    g.add_argument("--mode", default="store", choices=["store", "accumulate", "gated", "gemv", "simt"])
+    g.add_argument("--tile", type=int, default=None)
+    g.add_argument("--splits", type=int, default=1)
+    g.add_argument("--f32", action="store_true")
+    g.set_defaults(fn=cmd_gemm)
+    d = sub.add_parser("attention")
+    d.add_argument("--batch", type=int, default=8)
+    d.add_argument("--context", type=int, default=1024)
+    d.add_argument("--splits", type=int, default=0)
+    d.set_defaults(fn=cmd_attention)
+    p = sub.add_parser("prefill-attention")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.set_defaults(fn=cmd_prefill_attention)
+    for s in (g, d, p):
+        s.add_argument("--reps", type=int, default=20)
+        s.add_argument("--no-flush", action="store_true")
+    for s in (d, p):
+        s.add_argument("--heads", type=int, default=32)
+        s.add_argument("--kv-heads", type=int, default=8)
+        s.add_argument("--head-dim", type=int, default=128)
+        s.add_argument("--page-size", type=int, default=16)
+    a = ap.parse_args(argv)
+    a.fn(a)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

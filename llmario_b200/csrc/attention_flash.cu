@@ -67,6 +67,8 @@ __global__ void __launch_bounds__(WARPS * 32) flash_paged_kernel(
   constexpr int NT = KT / 8;             // key n-tiles of S
   constexpr int DT = HD / 8;             // dim n-tiles of O
   extern __shared__ __align__(128) uint8_t smem_raw[];
+  pdl_trigger();
+  pdl_wait();
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);               // [2][KT][HD]
   bf16* vs = ks + 2 * KT * HD;                                 // [2][KT][HD]
 
@@ -255,6 +257,8 @@ __global__ void __launch_bounds__(WARPS * 32) flash_paged_kernel(
 template <int HD>
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                              bf16* __restrict__ out, const int* __restrict__ rows, int Hq, int splits) {
+  pdl_trigger();
+  pdl_wait();
   const size_t rowhead = (size_t)(rows ? rows[blockIdx.x] : (int)blockIdx.x) * Hq + blockIdx.y;
   float mstar = -INFINITY;
   for (int z = 0; z < splits; ++z) mstar = fmaxf(mstar, part_ml[(rowhead * splits + z) * 2]);
@@ -284,10 +288,9 @@ int launch(const bf16* q, bf16* out, float* part_o, float* part_ml, const bf16* 
     configured = true;
   }
   dim3 grid(n_items, Hkv, splits);
-  kernel<<<grid, WARPS * 32, smem, s>>>(q, out, part_o, part_ml, kc, vc, page_stride, table, table_stride,
-                                       items, row_slot, row_pos, Hq, Hkv, page_size,
-                                       scale * 1.4426950408889634f, window, splits);
-  return launch_status();
+  return launch_pdl(kernel, grid, WARPS * 32, smem, s, q, out, part_o, part_ml, kc, vc, page_stride, table,
+                    table_stride, items, row_slot, row_pos, Hq, Hkv, page_size,
+                    scale * 1.4426950408889634f, window, splits);
 }
 }  // namespace
 
@@ -330,11 +333,10 @@ LLM_EXPORT int llm_attention_merge(const float* part_o, const float* part_ml, vo
                                    cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   dim3 grid(n_rows, Hq);
-  if (hd == 128) merge_kernel<128><<<grid, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, rows, Hq, splits);
-  else if (hd == 64) merge_kernel<64><<<grid, 64, 0, stream>>>(part_o, part_ml, (bf16*)out, rows, Hq, splits);
-  else if (hd == 32) merge_kernel<32><<<grid, 32, 0, stream>>>(part_o, part_ml, (bf16*)out, rows, Hq, splits);
-  else return LLM_ERR_UNSUPPORTED;
-  return launch_status();
+  if (hd == 128) return launch_pdl(merge_kernel<128>, grid, 128, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits);
+  if (hd == 64) return launch_pdl(merge_kernel<64>, grid, 64, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits);
+  if (hd == 32) return launch_pdl(merge_kernel<32>, grid, 32, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits);
+  return LLM_ERR_UNSUPPORTED;
 }
 
 // ------------------------------------------------------------------------------------------------

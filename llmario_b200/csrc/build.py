@@ -128,6 +128,13 @@ def build_library(verbose: bool = True, extra_flags: Sequence[str] = ()) -> str:
     _run([nvcc, "-shared", *ARCH_FLAGS, "-o", tmp, *objs, "-lcudart_static", "-ldl", "-lrt",
           "-lpthread"], "linking")
     os.replace(tmp, lib)
+    keep = {os.path.basename(lib)} | {os.path.basename(o) for o in objs}
+    for f in os.listdir(out_dir):           # objects and libraries of older sources
+        if f.endswith((".so", ".o")) and f not in keep:
+            try:
+                os.remove(os.path.join(out_dir, f))
+            except OSError:
+                pass
     if verbose:
         _say(f"built {os.path.basename(lib)} in {time.time() - t0:.0f} s")
     return lib

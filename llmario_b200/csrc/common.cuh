@@ -51,3 +51,29 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch.  A kernel that starts with pdl_trigger() lets the next kernel
+// of the stream be scheduled as soon as all of its own blocks have started; that next kernel may
+// do work that does not depend on earlier kernels (fetching weights, setting up barriers) and
+// must call pdl_wait() before it touches anything an earlier kernel wrote or still reads.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_llm_pdl;   // 1: launch with the programmatic-serialization attribute (llm_set_pdl)
+
+// Launch a kernel that calls pdl_wait() itself.
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_llm_pdl ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

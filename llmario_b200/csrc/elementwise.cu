@@ -1,10 +1,15 @@
 // Embedding gather, RMS norm, SiLU gating and small bookkeeping kernels.
 #include "common.cuh"
 
+int g_llm_pdl = 1;
+LLM_EXPORT void llm_set_pdl(int on) { g_llm_pdl = on ? 1 : 0; }
+
 // x[t][:] = table[token[t]][:]   (residual stream is 32-bit in every mode)
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ x, int width, int vocab, int* __restrict__ err) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int tok = tokens[t];
   if (tok < 0 || tok >= vocab) {
@@ -21,12 +26,10 @@ LLM_EXPORT int llm_embed(const int* tokens, const void* table, int table_dtype, 
   if (rows <= 0) return 0;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == LLM_F32)
-    embed_kernel<float><<<rows, threads, 0, stream>>>(tokens, (const float*)table, x, width, vocab, err_flag);
-  else if (table_dtype == LLM_BF16)
-    embed_kernel<bf16><<<rows, threads, 0, stream>>>(tokens, (const bf16*)table, x, width, vocab, err_flag);
-  else
-    return LLM_ERR_UNSUPPORTED;
-  return launch_status();
+    return launch_pdl(embed_kernel<float>, rows, threads, 0, stream, tokens, (const float*)table, x, width, vocab, err_flag);
+  if (table_dtype == LLM_BF16)
+    return launch_pdl(embed_kernel<bf16>, rows, threads, 0, stream, tokens, (const bf16*)table, x, width, vocab, err_flag);
+  return LLM_ERR_UNSUPPORTED;
 }
 
 // y[r][:] = x[src(r)][:] * rsqrt(mean(x^2) + eps) * w[:]    sums and scale in 32-bit.
@@ -36,6 +39,8 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
                                 TOut* __restrict__ y, const int* __restrict__ rows_index, int width,
                                 float eps) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows_index ? rows_index[r] : r) * width;
   float ss = 0.f;
@@ -55,12 +60,10 @@ LLM_EXPORT int llm_rms_norm(const float* x, const float* w, void* y, int out_dty
   if (rows <= 0) return 0;
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   if (out_dtype == LLM_F32)
-    rms_norm_kernel<float><<<rows, threads, 0, stream>>>(x, w, (float*)y, rows_index, width, eps);
-  else if (out_dtype == LLM_BF16)
-    rms_norm_kernel<bf16><<<rows, threads, 0, stream>>>(x, w, (bf16*)y, rows_index, width, eps);
-  else
-    return LLM_ERR_UNSUPPORTED;
-  return launch_status();
+    return launch_pdl(rms_norm_kernel<float>, rows, threads, 0, stream, x, w, (float*)y, rows_index, width, eps);
+  if (out_dtype == LLM_BF16)
+    return launch_pdl(rms_norm_kernel<bf16>, rows, threads, 0, stream, x, w, (bf16*)y, rows_index, width, eps);
+  return LLM_ERR_UNSUPPORTED;
 }
 
 // out[t][j] = silu(gu[t][j]) * gu[t][ff + j]   with silu(z) = z / (1 + exp(-z)), in 32-bit.
@@ -105,6 +108,8 @@ __global__ void table_update_kernel(int* __restrict__ table, int row_stride,
 __global__ void table_update_counted_kernel(int* __restrict__ table, int row_stride,
                                             const int* __restrict__ updates,
                                             const int* __restrict__ count, int max_n) {
+  pdl_trigger();
+  pdl_wait();
   const int n = min(*count, max_n);
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
     table[(size_t)updates[3 * i] * row_stride + updates[3 * i + 1]] = updates[3 * i + 2];
@@ -114,8 +119,7 @@ LLM_EXPORT int llm_table_update_counted(int* table, int row_stride, const int* u
                                         const int* count, int max_n, cudaStream_t stream) {
   if (max_n <= 0) return 0;
   const int blocks = (max_n + 127) / 128 < 8 ? (max_n + 127) / 128 : 8;
-  table_update_counted_kernel<<<blocks, 128, 0, stream>>>(table, row_stride, updates, count, max_n);
-  return launch_status();
+  return launch_pdl(table_update_counted_kernel, blocks, 128, 0, stream, table, row_stride, updates, count, max_n);
 }
 
 LLM_EXPORT int llm_table_update(int* table, int row_stride, const int* updates, int n,
@@ -123,4 +127,22 @@ LLM_EXPORT int llm_table_update(int* table, int row_stride, const int* updates, 
   if (n <= 0) return 0;
   table_update_kernel<<<(n + 127) / 128, 128, 0, stream>>>(table, row_stride, updates, n);
   return launch_status();
+}
+
+// Clear a [rows][cols] float matrix with row stride ld (a kernel rather than a memset, so that it
+// can take part in programmatic dependent launch).
+__global__ void zero_f32_kernel(float* __restrict__ p, int rows, int cols, int ld) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = (long long)rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x)
+    p[(i / cols) * ld + (i % cols)] = 0.f;
+}
+
+int llm_zero_f32(float* p, int rows, int cols, int ld, cudaStream_t stream) {
+  const long long total = (long long)rows * cols;
+  if (total <= 0) return 0;
+  const int blocks = (int)((total + 1023) / 1024 < 592 ? (total + 1023) / 1024 : 592);
+  return launch_pdl(zero_f32_kernel, blocks, 256, 0, stream, p, rows, cols, ld);
 }

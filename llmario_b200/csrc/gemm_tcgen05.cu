@@ -24,6 +24,8 @@
 
 #include "common.cuh"
 
+int llm_zero_f32(float* p, int rows, int cols, int ld, cudaStream_t stream);   // elementwise.cu
+
 namespace {
 
 constexpr int TILE_M = 128;       // weight rows per CTA
@@ -128,6 +130,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
   extern __shared__ uint8_t raw[];
   auto& sm = *reinterpret_cast<SharedStorage<BN, STAGES>*>(
       (reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int feat_per_tile = EPI == EPI_GATED ? 64 : TILE_M;
   const int n0 = blockIdx.x * feat_per_tile;
@@ -163,22 +166,31 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
   if (nkb > 0) {
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- producer
-      int issued = 0;
-      bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
+      // The weights do not depend on any earlier kernel: the first ring of weight tiles is
+      // requested at once, the activation tiles only after the earlier kernels are done.
+      auto load_w = [&](int i) {
         const int s = i % STAGES;
-        const uint32_t round = i / STAGES;
-        ok = mbar_wait(&sm.empty[s], (round & 1) ^ 1);
-        if (!ok) { atomicExch(status, 1); break; }
         mbar_expect_tx(&sm.full[s], STAGE_BYTES);
         const int k = (kb_begin + i) * TILE_K;
-        if (EPI == EPI_GATED) {
-          tma_load_2d(sm.a[s], &map_w, k, n0, &sm.full[s]);
-          tma_load_2d(sm.a[s] + 64 * TILE_K * 2, &map_w, k, half + n0, &sm.full[s]);
-        } else {
-          tma_load_2d(sm.a[s], &map_w, k, n0, &sm.full[s]);
-        }
-        tma_load_2d(sm.b[s], &map_x, k, t0, &sm.full[s]);
+        tma_load_2d(sm.a[s], &map_w, k, n0, &sm.full[s]);
+        if (EPI == EPI_GATED) tma_load_2d(sm.a[s] + 64 * TILE_K * 2, &map_w, k, half + n0, &sm.full[s]);
+      };
+      auto load_x = [&](int i) {
+        const int s = i % STAGES;
+        tma_load_2d(sm.b[s], &map_x, (kb_begin + i) * TILE_K, t0, &sm.full[s]);
+      };
+      const int head = min(nkb, STAGES);
+      for (int i = 0; i < head; ++i) load_w(i);
+      pdl_wait();
+      for (int i = 0; i < head; ++i) load_x(i);
+      int issued = head;
+      bool ok = true;
+      for (int i = head; i < nkb; ++i) {
+        const int s = i % STAGES;
+        ok = mbar_wait(&sm.empty[s], ((i / STAGES) & 1) ^ 1);
+        if (!ok) { atomicExch(status, 1); break; }
+        load_w(i);
+        load_x(i);
         issued = i + 1;
       }
       if (!ok) {
@@ -208,6 +220,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
       // ---------------------------------------------------------------- epilogue
       const int q = warp & 3;                 // TMEM lane quarter this warp may read
       const int row = q * 32 + lane;          // row of the 128-row tile
+      pdl_wait();   // the output may still be read or written by earlier kernels
       const bool ok = mbar_wait(&sm.acc_full, 0);
       if (!ok && lane == 0) atomicExch(status, 3);
       tc_fence_after();
@@ -345,16 +358,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, 
   const int feat = EPI == EPI_GATED ? 64 : TILE_M;
   const int limit = EPI == EPI_GATED ? half : N;
   dim3 grid((limit + feat - 1) / feat, (T + BN - 1) / BN, splits);
-  kernel<<<grid, 192, smem, stream>>>(mw, mx, C, ldc, T, N, K, half, status);
-  return launch_status();
+  return launch_pdl(kernel, grid, 192, smem, stream, mw, mx, C, ldc, T, N, K, half, status);
 }
 
 template <int EPI, typename TC>
 int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K,
              int half, int splits, int* status, cudaStream_t stream) {
   switch (bn) {
-    case 16: return launch<16, 6, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
-    case 32: return launch<32, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
+    case 16: return launch<16, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
+    case 32: return launch<32, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
     case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
     case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
     case 256: return launch<256, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
@@ -385,8 +397,8 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dty
   if (!tensor_map(X, T, K, lda, bn, &mx)) return LLM_ERR_UNSUPPORTED;
   if (mode == 0) {
     if (c_dtype == LLM_F32 && splits > 1) {   // partial sums are added into zeros
-      cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, T, stream);
-      if (e != cudaSuccess) return (int)e;
+      const int z = llm_zero_f32((float*)C, T, N, ldc, stream);
+      if (z != 0) return z;
     }
     if (c_dtype == LLM_F32)
       return dispatch<EPI_STORE, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, splits, status, stream);

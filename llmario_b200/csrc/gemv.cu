@@ -28,6 +28,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const bf16* __restrict
                                                           const bf16* __restrict__ W,
                                                           TC* __restrict__ C, int N, int K, int lda,
                                                           int ldw, int ldc, int half) {
+  pdl_trigger();
+  pdl_wait();
   const int warp = blockIdx.x * WARPS + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   // gated: this warp owns ROWS/2 outputs: gate rows n0.., up rows half + n0..
@@ -103,7 +105,7 @@ void launch_m(const bf16* A, const bf16* W, TC* C, int N, int K, int lda, int ld
   const int limit = MODE == 2 ? half : N;
   const int warps = (limit + outs - 1) / outs;
   const int blocks = (warps + WARPS - 1) / WARPS;
-  gemv_kernel<M, TC, MODE><<<blocks, WARPS * 32, 0, s>>>(A, W, C, N, K, lda, ldw, ldc, half);
+  (void)launch_pdl(gemv_kernel<M, TC, MODE>, blocks, WARPS * 32, 0, s, A, W, C, N, K, lda, ldw, ldc, half);
 }
 
 template <typename TC, int MODE>

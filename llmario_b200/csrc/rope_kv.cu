@@ -16,6 +16,8 @@ __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq, float attn_factor,
     int rows, int Hq, int Hkv, int hd, int rot_dim, int page_size, float eps, int has_kv,
     int use_norm) {
+  pdl_trigger();
+  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int heads = Hq + (has_kv ? 2 * Hkv : 0);
@@ -98,13 +100,11 @@ LLM_EXPORT int llm_qk_norm_rope_store(
   rot_dim, page_size, eps, has_kv, use_norm
   if (dtype == LLM_F32) {
     typedef float TQ;
-    qk_norm_rope_store_kernel<float, float><<<blocks, threads, 0, stream>>>(ARGS);
+    return launch_pdl(qk_norm_rope_store_kernel<float, float>, blocks, threads, 0, stream, ARGS);
   } else if (dtype == LLM_BF16) {
     typedef bf16 TQ;
-    qk_norm_rope_store_kernel<bf16, bf16><<<blocks, threads, 0, stream>>>(ARGS);
-  } else {
-    return LLM_ERR_UNSUPPORTED;
+    return launch_pdl(qk_norm_rope_store_kernel<bf16, bf16>, blocks, threads, 0, stream, ARGS);
   }
 #undef ARGS
-  return launch_status();
+  return LLM_ERR_UNSUPPORTED;
 }

@@ -304,21 +304,19 @@ SM_COUNT = 148
 def k_splits(rows: int, out_features: int, in_features: int) -> int:
     """How many ways to split K so that a product with few output tiles still fills the GPU."""
     tiles = -(-out_features // 128) * -(-rows // token_tile(rows))
-    if tiles >= 120:
+    if tiles >= 2 * SM_COUNT - 40:
         return 1
-    return max(1, min(8, round(SM_COUNT / tiles), in_features // 512))
+    # two CTAs fit an SM: aim at one full wave of 2 * SM_COUNT CTAs, at least 256 of K each
+    return max(1, min(16, round(2 * SM_COUNT / tiles), in_features // 256))
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out (=|+=) a @ w.T with the fastest hand-written kernel that takes these operands:
-    tensor cores for bfloat16, a streaming kernel for one or two rows against a large matrix,
-    the CUDA-core kernel for everything else (32-bit operands, unaligned sizes)."""
+    tensor cores for bfloat16 (they fetch weights ahead of the kernel before them), the
+    CUDA-core kernels for everything else (32-bit operands, unaligned sizes)."""
     if _tc_ok(a, w):
         rows, k = a.shape
         n = w.shape[0]
-        if rows <= 2 and n * k >= (1 << 26) and _gemv_ok(a, w):
-            gemv_bf16(a, w, out, 1 if accumulate else 0)
-            return
         splits = k_splits(rows, n, k) if out.dtype == torch.float32 else 1
         gemm_tcgen05(a, w, out, 1 if accumulate else 0, splits=splits)
     elif _gemv_ok(a, w):
@@ -331,10 +329,7 @@ def gate_up_silu(ctx, h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tenso
     """act = silu(h Wg^T) * (h Wu^T) for Wg, Wu stacked in ``w_gate_up`` ([2 ff][hidden])."""
     rows, ff = act.shape
     if _tc_ok(h, w_gate_up):
-        if rows <= 2 and _gemv_ok(h, w_gate_up):
-            gemv_bf16(h, w_gate_up, act, 2, ff)
-        else:
-            gemm_tcgen05(h, w_gate_up, act, 2, ff)
+        gemm_tcgen05(h, w_gate_up, act, 2, ff)
         return
     if _gemv_ok(h, w_gate_up):
         gemv_bf16(h, w_gate_up, act, 2, ff)
