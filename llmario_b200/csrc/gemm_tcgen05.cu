@@ -12,8 +12,10 @@
 //   warps 2-5  epilogue: tcgen05.ld of the 32 TMEM lanes of their quarter, then coalesced stores
 //
 // Epilogues: store bfloat16 / float32, add into a float32 residual stream, or the gated
-// activation silu(g) * u with 64 gate rows and their 64 up rows in one 128-row tile.  With
-// gridDim.z > 1 the K range is split and the partial sums are added with float atomics.
+// activation silu(g) * u with 64 gate rows and their 64 up rows interleaved in one 128-row tile.
+// The finished tile is laid out in shared memory and leaves through one TMA store, or one TMA
+// add-reduction for the residual add and for the partial sums of a split K range (gridDim.z > 1);
+// an output whose rows are not 16-byte multiples is written with plain stores and atomics.
 //
 // Every wait on an mbarrier is bounded; when a bound runs out the kernel records where in
 // *status, drains the loads it still has in flight, frees its TMEM and returns.
@@ -115,7 +117,6 @@ template <int BN, int STAGES>
 struct alignas(1024) SharedStorage {
   uint8_t a[STAGES][TILE_M * TILE_K * 2];
   uint8_t b[STAGES][BN * TILE_K * 2 < 1024 ? 1024 : BN * TILE_K * 2];
-  float gate_exchange[64][17];
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t acc_full;
@@ -126,7 +127,8 @@ struct alignas(1024) SharedStorage {
 template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-    TC* __restrict__ C, int ldc, int T, int N, int K, int half, int* __restrict__ status) {
+    const __grid_constant__ CUtensorMap map_c, int tma_out, TC* __restrict__ C, int ldc, int T, int N,
+    int K, int half, int* __restrict__ status) {
   extern __shared__ uint8_t raw[];
   auto& sm = *reinterpret_cast<SharedStorage<BN, STAGES>*>(
       (reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -172,8 +174,16 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
         const int s = i % STAGES;
         mbar_expect_tx(&sm.full[s], STAGE_BYTES);
         const int k = (kb_begin + i) * TILE_K;
-        tma_load_2d(sm.a[s], &map_w, k, n0, &sm.full[s]);
-        if (EPI == EPI_GATED) tma_load_2d(sm.a[s] + 64 * TILE_K * 2, &map_w, k, half + n0, &sm.full[s]);
+        if (EPI == EPI_GATED) {
+          // 16 gate rows, their 16 up rows, the next 16 gate rows, ...: every 32-lane quarter of
+          // the accumulator then holds gate and up of the same 16 features
+#pragma unroll
+          for (int b = 0; b < 8; ++b)
+            tma_load_2d(sm.a[s] + b * 16 * TILE_K * 2, &map_w, k, ((b & 1) ? half : 0) + n0 + (b >> 1) * 16,
+                        &sm.full[s]);
+        } else {
+          tma_load_2d(sm.a[s], &map_w, k, n0, &sm.full[s]);
+        }
       };
       auto load_x = [&](int i) {
         const int s = i % STAGES;
@@ -226,38 +236,41 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
       tc_fence_after();
       if (ok) {
         const bool split = gridDim.z > 1;
+        // With a tensor map for the output the tile is laid out in shared memory as
+        // [token][feature] (the pipeline stages are free by now) and written by one TMA store,
+        // or added by one TMA reduction (residual add, partial sums of a K split).
+        constexpr int FEAT = EPI == EPI_GATED ? 64 : TILE_M;
+        TC* stage_out = reinterpret_cast<TC*>(&sm.a[0][0]);
 #pragma unroll 1
         for (int c = 0; c < BN; c += 16) {
           uint32_t v[16];
           tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
           tmem_ld_wait();
           if (EPI == EPI_GATED) {
-            // rows 0..63 hold gate, rows 64..127 the matching up values: hand them over
-            if (q >= 2) {
+            // lanes 0..15 hold gate of feature q*16 + lane, lanes 16..31 the matching up values
+            const int f = q * 16 + (lane & 15);
+            const int n = n0 + f;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) sm.gate_exchange[row - 64][j] = __uint_as_float(v[j]);
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (q < 2) {
-              const int n = n0 + row;
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
+            for (int j = 0; j < 16; ++j) {
+              const float mine = __uint_as_float(v[j]);
+              const float u = __shfl_down_sync(0xffffffffu, mine, 16);
+              if (lane < 16) {
                 const int t = t0 + c + j;
-                if (t < T && n < half) {
-                  const float g = __uint_as_float(v[j]), u = sm.gate_exchange[row][j];
-                  C[(size_t)t * ldc + n] = from_f32<TC>(g / (1.0f + __expf(-g)) * u);
-                }
+                const TC a = from_f32<TC>(mine / (1.0f + __expf(-mine)) * u);
+                if (tma_out) stage_out[(c + j) * FEAT + f] = a;
+                else if (t < T && n < half) C[(size_t)t * ldc + n] = a;
               }
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
           } else {
             const int n = n0 + row;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = t0 + c + j;
-              if (t < T && n < N) {
+              const float a = __uint_as_float(v[j]);
+              if (tma_out) {
+                stage_out[(c + j) * FEAT + row] = from_f32<TC>(a);
+              } else if (t < T && n < N) {
                 TC* dst = C + (size_t)t * ldc + n;
-                const float a = __uint_as_float(v[j]);
                 if (EPI == EPI_ACCUM || split) {
                   if (split) atomicAdd(reinterpret_cast<float*>(dst), a);
                   else *dst = from_f32<TC>(to_f32(*dst) + a);
@@ -266,6 +279,21 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
                 }
               }
             }
+          }
+        }
+        if (tma_out) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (warp == 2 && lane == 0) {
+            const uint32_t src = smem_u32(stage_out);
+            if (EPI == EPI_ACCUM || split)
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&map_c), "r"(src), "r"(n0), "r"(t0) : "memory");
+            else
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&map_c), "r"(src), "r"(n0), "r"(t0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           }
         }
       }
@@ -302,25 +330,29 @@ EncodeTiled encoder() {
 struct MapKey {
   const void* ptr;
   long long rows, cols, ld;
-  int box_rows;
+  int box_rows, box_cols, kind;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+           box_cols == o.box_cols && kind == o.kind;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     size_t h = std::hash<const void*>()(k.ptr);
-    h ^= std::hash<long long>()(k.rows * 1315423911LL + k.cols * 2654435761LL + k.ld * 97 + k.box_rows) +
+    h ^= std::hash<long long>()(k.rows * 1315423911LL + k.cols * 2654435761LL + k.ld * 97 + k.box_rows * 31 +
+                                k.box_cols * 7 + k.kind) +
          0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2);
     return h;
   }
 };
 
-// A [rows][cols] bf16 matrix with row stride ld (elements), tiled in boxes of box_rows x 64.
-bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+// A [rows][cols] matrix with row stride ld (elements), tiled in boxes of box_rows x box_cols.
+// kind 0: bf16 operand, 128-byte swizzle; kind 1: bf16 output, no swizzle; kind 2: f32 output.
+bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols,
+                int kind, CUtensorMap* out) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
-  MapKey key{ptr, rows, cols, ld, box_rows};
+  MapKey key{ptr, rows, cols, ld, box_rows, box_cols, kind};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -329,14 +361,16 @@ bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, i
   }
   EncodeTiled enc = encoder();
   if (!enc) return false;
+  const int esize = kind == 2 ? 4 : 2;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1, 1};
   CUtensorMap m;
-  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = enc(&m, kind == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                   const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, m);
@@ -347,6 +381,13 @@ bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, i
 template <int BN, int STAGES, int EPI, typename TC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K, int half,
            int splits, int* status, cudaStream_t stream) {
+  // the output goes through TMA when its rows are 16-byte multiples on a 16-byte aligned base
+  CUtensorMap mc = mw;
+  int tma_out = 0;
+  const int out_cols = EPI == EPI_GATED ? half : N;
+  if (((uintptr_t)C & 15) == 0 && ((size_t)ldc * sizeof(TC)) % 16 == 0 &&
+      tensor_map(C, T, out_cols, ldc, BN, EPI == EPI_GATED ? 64 : TILE_M, sizeof(TC) == 4 ? 2 : 1, &mc))
+    tma_out = 1;
   auto kernel = gemm_tcgen05_kernel<BN, STAGES, EPI, TC>;
   constexpr int smem = (int)sizeof(SharedStorage<BN, STAGES>) + 1024;
   static bool configured = false;
@@ -358,7 +399,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, 
   const int feat = EPI == EPI_GATED ? 64 : TILE_M;
   const int limit = EPI == EPI_GATED ? half : N;
   dim3 grid((limit + feat - 1) / feat, (T + BN - 1) / BN, splits);
-  return launch_pdl(kernel, grid, 192, smem, stream, mw, mx, C, ldc, T, N, K, half, status);
+  return launch_pdl(kernel, grid, 192, smem, stream, mw, mx, mc, tma_out, C, ldc, T, N, K, half, status);
 }
 
 template <int EPI, typename TC>
@@ -393,8 +434,8 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dty
   // no split may be empty
   while (splits > 1 && (splits - 1) * ((kblocks + splits - 1) / splits) >= kblocks) --splits;
   CUtensorMap mw, mx;
-  if (!tensor_map(W, N, K, ldw, mode == 2 ? 64 : TILE_M, &mw)) return LLM_ERR_UNSUPPORTED;
-  if (!tensor_map(X, T, K, lda, bn, &mx)) return LLM_ERR_UNSUPPORTED;
+  if (!tensor_map(W, N, K, ldw, mode == 2 ? 16 : TILE_M, TILE_K, 0, &mw)) return LLM_ERR_UNSUPPORTED;
+  if (!tensor_map(X, T, K, lda, bn, TILE_K, 0, &mx)) return LLM_ERR_UNSUPPORTED;
   if (mode == 0) {
     if (c_dtype == LLM_F32 && splits > 1) {   // partial sums are added into zeros
       const int z = llm_zero_f32((float*)C, T, N, ldc, stream);
