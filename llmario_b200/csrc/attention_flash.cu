@@ -43,6 +43,11 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float fast_exp2(float x) {   // 2^x, -inf gives 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -56,7 +61,7 @@ template <int CPR> __device__ __forceinline__ int swizzle(int r, int c) {
 struct Item { int row_start, tokens, slot, pos_start; };
 
 template <int HD, int WARPS, int KT>
-__global__ void __launch_bounds__(WARPS * 32) flash_paged_kernel(
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 6) flash_paged_kernel(
     const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_o,
     float* __restrict__ part_ml, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     long long page_stride, const int* __restrict__ block_table, int table_stride,
@@ -119,21 +124,41 @@ __global__ void __launch_bounds__(WARPS * 32) flash_paged_kernel(
   for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+  // A tile is filled page by page: one look-up in the block table per page, then the rows of
+  // that page (consecutive positions, Hkv * HD elements apart) in 16-byte pieces, two rows per
+  // warp instruction.  Rows outside the item's key range are cleared: their scores are masked,
+  // but their values must be finite.
   auto load_tile = [&](int tb, int stage) {
     bf16* kd = ks + stage * KT * HD;
     bf16* vd = vs + stage * KT * HD;
-    for (int id = threadIdx.x; id < KT * CPR; id += WARPS * 32) {
-      const int j = id / CPR, c = id % CPR;
-      const int p = tb * KT + j;
-      const bool valid = p >= lo && p <= hi;
-      long long off = 0;
-      if (valid) {
-        const int page = table[p / page_size];
-        off = (long long)page * page_stride + ((long long)(p % page_size) * Hkv + kvh) * HD + c * 8;
+    const int base = tb * KT;
+    const int first = max(lo, base), last = min(hi, base + KT - 1);
+    if (first > base || last < base + KT - 1) {
+      for (int id = threadIdx.x; id < KT * CPR; id += WARPS * 32) {
+        const int j = id / CPR, c = id % CPR;
+        if (base + j < first || base + j > last) {
+          const int dst = j * HD + swizzle<CPR>(j, c) * 8;
+          *reinterpret_cast<uint4*>(kd + dst) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(vd + dst) = make_uint4(0, 0, 0, 0);
+        }
       }
-      const int dst = j * HD + swizzle<CPR>(j, c) * 8;
-      cp_async16(kd + dst, k_cache + off, valid);
-      cp_async16(vd + dst, v_cache + off, valid);
+    }
+    for (int p0 = first; p0 <= last;) {
+      const int pg = p0 / page_size;
+      const int in_page = p0 - pg * page_size;
+      const int run = min(page_size - in_page, last - p0 + 1);
+      const long long off = (long long)table[pg] * page_stride + ((long long)in_page * Hkv + kvh) * HD;
+      const bf16* ksrc = k_cache + off;
+      const bf16* vsrc = v_cache + off;
+      const int j0 = p0 - base;
+      for (int id = threadIdx.x; id < run * CPR; id += WARPS * 32) {
+        const int j = id / CPR, c = id % CPR;
+        const int src = j * Hkv * HD + c * 8;
+        const int dst = (j0 + j) * HD + swizzle<CPR>(j0 + j, c) * 8;
+        cp_async16(kd + dst, ksrc + src, true);
+        cp_async16(vd + dst, vsrc + src, true);
+      }
+      p0 += run;
     }
   };
 
@@ -152,30 +177,50 @@ __global__ void __launch_bounds__(WARPS * 32) flash_paged_kernel(
       // ---- S = Q K^T
       float s[NT][4];
 #pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      // one ldmatrix feeds two key tiles at one k-step, so that consecutive MMAs write
+      // different accumulators
 #pragma unroll
-        for (int k2 = 0; k2 < KS / 2; ++k2) {
+      for (int k = 0; k < KS; ++k) {
+#pragma unroll
+        for (int n2 = 0; n2 < NT / 2; ++n2) {
           uint32_t b[4];
-          const int row = n * 8 + (lane & 7), chunk = k2 * 4 + (lane >> 3);
+          const int mi = lane >> 3;
+          const int row = (2 * n2 + (mi >> 1)) * 8 + (lane & 7), chunk = 2 * k + (mi & 1);
           ldmatrix_x4(b, kt + row * HD + swizzle<CPR>(row, chunk) * 8);
-          mma_bf16(s[n], qf[2 * k2], b[0], b[1]);
-          mma_bf16(s[n], qf[2 * k2 + 1], b[2], b[3]);
+          mma_bf16(s[2 * n2], qf[k], b[0], b[1]);
+          mma_bf16(s[2 * n2 + 1], qf[k], b[2], b[3]);
         }
       }
       // ---- mask, running maximum, exponentials
       const int base = tb * KT;
+      const bool upper = warp * 16 + 8 < rows_valid;   // rows g + 8 of this warp hold queries
+      // a tile that every row of this warp sees completely needs no mask
+      const int wr0 = warp * 16, wr1 = min(rows_valid, wr0 + 16) - 1;
+      const int min_pos = it.pos_start + wr0 / G, max_pos = it.pos_start + wr1 / G;
+      const bool interior = base + KT - 1 <= min_pos &&
+                            (window <= 0 || base >= max_pos + 1 - window) && wr1 - wr0 == 15;
       float tmax[2] = {-INFINITY, -INFINITY};
+      if (interior) {
 #pragma unroll
-      for (int n = 0; n < NT; ++n)
+        for (int n = 0; n < NT; ++n)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = e >> 1;
-          const int p = base + n * 8 + 2 * t + (e & 1);
-          const bool vis = rvalid[i] && p <= rpos[i] && p >= rlo[i];
-          s[n][e] = vis ? s[n][e] * scale_log2 : -INFINITY;
-          tmax[i] = fmaxf(tmax[i], s[n][e]);
-        }
+          for (int e = 0; e < 4; ++e) {
+            s[n][e] *= scale_log2;
+            tmax[e >> 1] = fmaxf(tmax[e >> 1], s[n][e]);
+          }
+      } else {
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = e >> 1;
+            const int p = base + n * 8 + 2 * t + (e & 1);
+            const bool vis = rvalid[i] && p <= rpos[i] && p >= rlo[i];
+            s[n][e] = vis ? s[n][e] * scale_log2 : -INFINITY;
+            tmax[i] = fmaxf(tmax[i], s[n][e]);
+          }
+      }
       float corr[2], muse[2];
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
@@ -183,7 +228,7 @@ __global__ void __launch_bounds__(WARPS * 32) flash_paged_kernel(
         tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
         const float mnew = fmaxf(m[i], tmax[i]);
         muse[i] = mnew == -INFINITY ? 0.f : mnew;
-        corr[i] = exp2f(m[i] - muse[i]);   // m = -inf gives 0
+        corr[i] = fast_exp2(m[i] - muse[i]);   // m = -inf gives 0
         m[i] = mnew;
         l[i] *= corr[i];
       }
@@ -191,14 +236,16 @@ __global__ void __launch_bounds__(WARPS * 32) flash_paged_kernel(
       for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float pexp = exp2f(s[n][e] - muse[e >> 1]);
+          const float pexp = (e < 2 || upper) ? fast_exp2(s[n][e] - muse[e >> 1]) : 0.f;
           s[n][e] = pexp;
           l[e >> 1] += pexp;
         }
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-      for (int d = 0; d < DT; ++d) {
-        o[d][0] *= corr[0]; o[d][1] *= corr[0];
-        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+        for (int d = 0; d < DT; ++d) {
+          o[d][0] *= corr[0]; o[d][1] *= corr[0];
+          o[d][2] *= corr[1]; o[d][3] *= corr[1];
+        }
       }
       // ---- O += P V
 #pragma unroll

@@ -50,6 +50,41 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// ---- mbarriers (shared by the kernels that move data with the TMA unit)
+constexpr long long WAIT_CYCLES = 4000000000LL;   // bound of every wait: about two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// Bounded wait for the phase with the given parity: polls without blocking and gives up after
+// WAIT_CYCLES clock cycles (about two seconds).  Returns false when the bound ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  long long start = 0;
+  for (uint32_t i = 0;; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (i == 64) start = clock64();
+    if (i > 64) {
+      __nanosleep(32);
+      if ((i & 255u) == 0 && clock64() - start > WAIT_CYCLES) return false;
+    }
+  }
+}
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Programmatic dependent launch.  A kernel that starts with pdl_trigger() lets the next kernel
