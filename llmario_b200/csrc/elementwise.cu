@@ -54,10 +54,67 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
     y[(size_t)r * width + i] = from_f32<TOut>(xr[i] * scale * w[i]);
 }
 
+// The same for widths that are multiples of four and at most 256 * 4 * VEC_MAX: the row is read
+// once with 16-byte loads and kept in registers between the sum and the scaling.
+constexpr int VEC_MAX = 8;
+template <typename TOut>
+__global__ void __launch_bounds__(256) rms_norm_vec_kernel(const float* __restrict__ x,
+                                                           const float* __restrict__ w, TOut* __restrict__ y,
+                                                           const int* __restrict__ rows_index, int width,
+                                                           float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows_index ? rows_index[r] : r) * width);
+  const float4* wr = reinterpret_cast<const float4*>(w);
+  const int n4 = width >> 2;
+  float4 v[VEC_MAX];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VEC_MAX; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < n4) {
+      v[k] = xr[i];
+      ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+  for (int k = 0; k < VEC_MAX; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < n4) {
+      const float4 g = wr[i];
+      const float a = v[k].x * scale * g.x, b = v[k].y * scale * g.y, c = v[k].z * scale * g.z,
+                  d = v[k].w * scale * g.w;
+      TOut* dst = y + (size_t)r * width + 4 * i;
+      if (sizeof(TOut) == 4) {
+        *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst) = packed;
+      }
+    }
+  }
+}
+
 LLM_EXPORT int llm_rms_norm(const float* x, const float* w, void* y, int out_dtype,
                             const int* rows_index, int rows, int width, float eps,
                             cudaStream_t stream) {
   if (rows <= 0) return 0;
+  const bool vec = width % 4 == 0 && width <= 256 * 4 * VEC_MAX &&
+                   (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0;
+  if (vec) {
+    if (out_dtype == LLM_F32)
+      return launch_pdl(rms_norm_vec_kernel<float>, rows, 256, 0, stream, x, w, (float*)y, rows_index, width, eps);
+    if (out_dtype == LLM_BF16)
+      return launch_pdl(rms_norm_vec_kernel<bf16>, rows, 256, 0, stream, x, w, (bf16*)y, rows_index, width, eps);
+    return LLM_ERR_UNSUPPORTED;
+  }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   if (out_dtype == LLM_F32)
     return launch_pdl(rms_norm_kernel<float>, rows, threads, 0, stream, x, w, (float*)y, rows_index, width, eps);

@@ -13,9 +13,9 @@ __global__ void qk_norm_rope_store_kernel(
     TC* __restrict__ k_cache, TC* __restrict__ v_cache, long long page_stride,
     const int* __restrict__ block_table, int table_stride, const int* __restrict__ row_slot,
     const int* __restrict__ row_pos, const float* __restrict__ q_norm_w,
-    const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq, float attn_factor,
-    int rows, int Hq, int Hkv, int hd, int rot_dim, int page_size, float eps, int has_kv,
-    int use_norm) {
+    const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
+    const float2* __restrict__ cos_sin, float attn_factor, int rows, int Hq, int Hkv, int hd, int rot_dim,
+    int page_size, float eps, int has_kv, int use_norm) {
   pdl_trigger();
   pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -60,9 +60,15 @@ __global__ void qk_norm_rope_store_kernel(
       b = b * scale * w[i + half];
     }
     float sn, cs;
-    sincosf(fpos * inv_freq[i], &sn, &cs);
-    sn *= attn_factor;
-    cs *= attn_factor;
+    if (cos_sin) {      // made once per step for all heads and layers
+      const float2 t2 = cos_sin[(size_t)t * half + i];
+      cs = t2.x;
+      sn = t2.y;
+    } else {
+      sincosf(fpos * inv_freq[i], &sn, &cs);
+      sn *= attn_factor;
+      cs *= attn_factor;
+    }
     const float ra = a * cs - b * sn, rb = a * sn + b * cs;
     if (is_q) {
       q_out[(size_t)t * Hq * hd + (size_t)h * hd + i] = from_f32<TQ>(ra);
@@ -87,8 +93,8 @@ LLM_EXPORT int llm_qk_norm_rope_store(
     const float* proj, int proj_stride, void* q_out, void* k_cache, void* v_cache, int dtype,
     long long page_stride, const int* block_table, int table_stride, const int* row_slot,
     const int* row_pos, const float* q_norm_w, const float* k_norm_w, const float* inv_freq,
-    float attn_factor, int rows, int Hq, int Hkv, int hd, int rot_dim, int page_size, float eps,
-    int has_kv, int use_norm, cudaStream_t stream) {
+    const float* cos_sin, float attn_factor, int rows, int Hq, int Hkv, int hd, int rot_dim,
+    int page_size, float eps, int has_kv, int use_norm, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (rot_dim > hd || (rot_dim & 1)) return LLM_ERR_ARGUMENT;
   const int heads = Hq + (has_kv ? 2 * Hkv : 0);
@@ -96,8 +102,8 @@ LLM_EXPORT int llm_qk_norm_rope_store(
   const int threads = 128;
   const int blocks = (int)((warps * 32 + threads - 1) / threads);
 #define ARGS proj, proj_stride, (TQ*)q_out, (TQ*)k_cache, (TQ*)v_cache, page_stride, block_table, \
-  table_stride, row_slot, row_pos, q_norm_w, k_norm_w, inv_freq, attn_factor, rows, Hq, Hkv, hd,   \
-  rot_dim, page_size, eps, has_kv, use_norm
+  table_stride, row_slot, row_pos, q_norm_w, k_norm_w, inv_freq, (const float2*)cos_sin, attn_factor, \
+  rows, Hq, Hkv, hd, rot_dim, page_size, eps, has_kv, use_norm
   if (dtype == LLM_F32) {
     typedef float TQ;
     return launch_pdl(qk_norm_rope_store_kernel<float, float>, blocks, threads, 0, stream, ARGS);
@@ -107,4 +113,28 @@ LLM_EXPORT int llm_qk_norm_rope_store(
   }
 #undef ARGS
   return LLM_ERR_UNSUPPORTED;
+}
+
+namespace {
+// cos_sin[t][i] = attn_factor * (cos, sin)(pos[t] * inv_freq[i]): the angles of a step, in 32-bit,
+// computed once and shared by every head of every layer that uses this rotation.
+__global__ void rope_table_kernel(const int* __restrict__ row_pos, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ cos_sin, int rows, int half, float attn_factor) {
+  pdl_trigger();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * half) return;
+  const int t = idx / half, i = idx % half;
+  float sn, cs;
+  sincosf((float)row_pos[t] * inv_freq[i], &sn, &cs);
+  cos_sin[idx] = make_float2(cs * attn_factor, sn * attn_factor);
+}
+}  // namespace
+
+LLM_EXPORT int llm_rope_table(const int* row_pos, const float* inv_freq, float* cos_sin, int rows,
+                              int half, float attn_factor, cudaStream_t stream) {
+  const int total = rows * half;
+  if (total <= 0) return 0;
+  return launch_pdl(rope_table_kernel, (total + 255) / 256, 256, 0, stream, row_pos, inv_freq,
+                    (float2*)cos_sin, rows, half, attn_factor);
 }

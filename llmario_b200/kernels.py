@@ -42,8 +42,9 @@ def _declare(l) -> None:
         "llm_table_update": [P, I, P, I, P],
         "llm_table_update_counted": [P, I, P, P, I, P],
         "llm_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, I, I, P],
-        "llm_qk_norm_rope_store": [P, I, P, P, P, I, L, P, I, P, P, P, P, P, F, I, I, I, I, I, I,
-                                   F, I, I, P],
+        "llm_qk_norm_rope_store": [P, I, P, P, P, I, L, P, I, P, P, P, P, P, P, F, I, I, I, I, I,
+                                   I, F, I, I, P],
+        "llm_rope_table": [P, P, P, I, I, F, P],
         "llm_attention_generic": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P],
         "llm_sample": [P, L, I, I, P, P, P, P, P, P, P],
         "llm_gemv_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, P],
@@ -166,7 +167,8 @@ def qk_norm_rope_store(proj: torch.Tensor, q_out: torch.Tensor,
                        row_pos: torch.Tensor, q_norm_w: Optional[torch.Tensor],
                        k_norm_w: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
                        attn_factor: float, num_heads: int, num_kv_heads: int, head_dim: int,
-                       rot_dim: int, page_size: int, eps: float) -> None:
+                       rot_dim: int, page_size: int, eps: float,
+                       cos_sin: Optional[torch.Tensor] = None) -> None:
     """Per-head norm, rotation and stores for the rows of ``proj`` (float32,
     [rows, (Hq + 2 Hkv) * hd], or [rows, Hq * hd] when no cache is given)."""
     _cuda(proj, q_out, k_cache, v_cache, block_table, row_slot, row_pos, q_norm_w, k_norm_w,
@@ -181,9 +183,20 @@ def qk_norm_rope_store(proj: torch.Tensor, q_out: torch.Tensor,
     _check(lib().llm_qk_norm_rope_store(
         _ptr(proj), proj.stride(0), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _dt(q_out),
         page_stride, _ptr(block_table), block_table.stride(0), _ptr(row_slot), _ptr(row_pos),
-        _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq), float(attn_factor), rows, num_heads,
+        _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq), _ptr(cos_sin), float(attn_factor), rows,
+        num_heads,
         num_kv_heads, head_dim, rot_dim, page_size, float(eps), int(has_kv), int(use_norm),
         _stream()), "qk_norm_rope_store")
+
+
+def rope_table(row_pos: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor,
+               attn_factor: float) -> None:
+    """out[t][i] = attn_factor * (cos, sin)(row_pos[t] * inv_freq[i]), float32 [rows, half, 2]."""
+    _cuda(row_pos, inv_freq, out)
+    rows, half = out.shape[0], out.shape[1]
+    assert out.dtype == torch.float32 and out.is_contiguous() and inv_freq.numel() == half
+    _check(lib().llm_rope_table(_ptr(row_pos), _ptr(inv_freq), _ptr(out), rows, half,
+                                float(attn_factor), _stream()), "rope_table")
 
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,

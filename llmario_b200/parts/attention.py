@@ -62,6 +62,8 @@ class Attention:
             raise NotImplementedError("a position encoding that is not a rotation needs its own "
                                       "mixer")
         inv_freq, rot_dim, attn_factor = tables if tables else (None, 0, 1.0)
+        angles = self.position.step_angles(ctx) if tables and hasattr(self.position, "step_angles") \
+            else None
         kernels.qk_norm_rope_store(
             proj, q, view.k if call.writes_cache else None,
             view.v if call.writes_cache else None, view.page_stride, view.block_table,
@@ -69,7 +71,7 @@ class Attention:
             self.q_norm.weight if self.q_norm is not None else None,
             self.k_norm.weight if self.k_norm is not None else None,
             inv_freq, attn_factor, self.num_heads, self.num_kv_heads, self.head_dim, rot_dim,
-            view.page_size, self.q_norm.eps if self.q_norm is not None else 0.0)
+            view.page_size, self.q_norm.eps if self.q_norm is not None else 0.0, angles)
         out = ctx.buffer("attn.out", (rows, self.q_width))
         kernels.attention(ctx, q, out, view, self.num_heads, self.num_kv_heads, self.head_dim,
                           self.scale, self.window)

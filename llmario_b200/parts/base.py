@@ -127,6 +127,7 @@ class StepContext:
     max_pos: int = 0               # largest position in this step
 
     plans: Dict[int, AttentionPlan] = field(default_factory=dict)
+    shared: Dict[Any, Any] = field(default_factory=dict)   # what parts compute once per step
 
     def buffer(self, name: str, shape: Sequence[int], dtype: Optional[torch.dtype] = None
                ) -> torch.Tensor:

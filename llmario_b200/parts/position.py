@@ -30,5 +30,18 @@ class RotaryHalfSplit:
     def rotary_tables(self) -> Optional[Tuple[torch.Tensor, int, float]]:
         return self.inv_freq, self.rot_dim, self.attn_factor
 
+    def step_angles(self, ctx) -> torch.Tensor:
+        """cos and sin of every row's angles, float32 [rows, rot_dim / 2, 2]: made once per
+        step and shared by all layers whose rotation has the same constants."""
+        key = ("rope", self.rot_dim, self.theta, self.freq_scale, self.attn_factor)
+        table = ctx.shared.get(key)
+        if table is None:
+            from .. import kernels
+            table = ctx.buffer("rope.%d.%r.%r" % (self.rot_dim, self.theta, self.freq_scale),
+                               (ctx.rows, self.rot_dim // 2, 2), torch.float32)
+            kernels.rope_table(ctx.row_pos, self.inv_freq, table, self.attn_factor)
+            ctx.shared[key] = table
+        return table
+
 
 register_part("position", "rope_neox", RotaryHalfSplit, replace=True)
