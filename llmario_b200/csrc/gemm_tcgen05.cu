@@ -26,59 +26,15 @@
 
 #include "common.cuh"
 
+#include "tcgen05.cuh"
+
 int llm_zero_f32(float* p, int rows, int cols, int ld, cudaStream_t stream);   // elementwise.cu
+int llm_gemm_tcgen05_persistent(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
+                                int lda, int ldw, int ldc, int mode, int half, int* status,
+                                cudaStream_t stream);                        // gemm_tcgen05_persistent.cu
 
 namespace {
 
-constexpr int TILE_M = 128;       // weight rows per CTA
-constexpr int TILE_K = 64;        // bf16 elements per stage row: 128 bytes, one swizzle span
-constexpr int UMMA_K = 16;
-
-enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_GATED = 2 };
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]^T, both operands K-major bf16, accumulate in float32
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Shared-memory matrix descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of eight
-// rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-template <int BN>
-constexpr uint32_t instr_desc() {
-  // float32 accumulator, bf16 A and B, both K-major, N = BN, M = 128
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
-}
 
 template <int BN, int STAGES>
 struct alignas(1024) SharedStorage {
@@ -315,8 +271,10 @@ struct MapKeyHash {
 
 // A [rows][cols] matrix with row stride ld (elements), tiled in boxes of box_rows x box_cols.
 // kind 0: bf16 operand, 128-byte swizzle; kind 1: bf16 output, no swizzle; kind 2: f32 output.
-bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols,
-                int kind, CUtensorMap* out) {
+}  // namespace
+
+bool llm_tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols,
+                    int kind, CUtensorMap* out) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
   MapKey key{ptr, rows, cols, ld, box_rows, box_cols, kind};
@@ -345,6 +303,8 @@ bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, i
   return true;
 }
 
+namespace {
+
 template <int BN, int STAGES, int EPI, typename TC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K, int half,
            int splits, int* status, cudaStream_t stream) {
@@ -353,7 +313,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, 
   int tma_out = 0;
   const int out_cols = EPI == EPI_GATED ? half : N;
   if (((uintptr_t)C & 15) == 0 && ((size_t)ldc * sizeof(TC)) % 16 == 0 &&
-      tensor_map(C, T, out_cols, ldc, BN, EPI == EPI_GATED ? 64 : TILE_M, sizeof(TC) == 4 ? 2 : 1, &mc))
+      llm_tensor_map(C, T, out_cols, ldc, BN, EPI == EPI_GATED ? 64 : TILE_M, sizeof(TC) == 4 ? 2 : 1, &mc))
     tma_out = 1;
   auto kernel = gemm_tcgen05_kernel<BN, STAGES, EPI, TC>;
   constexpr int smem = (int)sizeof(SharedStorage<BN, STAGES>) + 1024;
@@ -377,7 +337,6 @@ int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ld
     case 32: return launch<32, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
     case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
     case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
-    case 256: return launch<256, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
   }
   return LLM_ERR_UNSUPPORTED;
 }
@@ -387,7 +346,7 @@ int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ld
 //   mode 0: C = X W^T (c_dtype bf16 or f32; with splits > 1: f32, zeroed here first)
 //   mode 1: C += X W^T (f32)
 //   mode 2: W = [gate; up] with `half` rows each, C[t][n] = silu(gate) * up, n < half
-// bn: token tile, one of 16, 32, 64, 128, 256.  status: device int, set non-zero when a wait
+// bn: token tile, one of 16, 32, 64, 128, or 256 for the persistent kernel.  status: device int, set non-zero when a wait
 // inside the kernel gave up.
 LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
                                 int lda, int ldw, int ldc, int mode, int half, int bn, int splits,
@@ -396,13 +355,23 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dty
   if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return LLM_ERR_UNSUPPORTED;
   if (((uintptr_t)X | (uintptr_t)W) & 15) return LLM_ERR_UNSUPPORTED;
   if (splits < 1) return LLM_ERR_ARGUMENT;
+  if (bn == 256) {
+    // many rows: the persistent kernel (tiles of 256 tokens, epilogue overlapped with the next
+    // tile); if the output cannot be written by TMA, the one-tile kernel with 128 tokens
+    if (splits == 1) {
+      const int r = llm_gemm_tcgen05_persistent(X, W, C, c_dtype, T, N, K, lda, ldw, ldc, mode, half, status,
+                                                stream);
+      if (r != LLM_ERR_UNSUPPORTED) return r;
+    }
+    bn = 128;
+  }
   const int kblocks = (K + TILE_K - 1) / TILE_K;
   if (splits > kblocks) splits = kblocks;
   // no split may be empty
   while (splits > 1 && (splits - 1) * ((kblocks + splits - 1) / splits) >= kblocks) --splits;
   CUtensorMap mw, mx;
-  if (!tensor_map(W, N, K, ldw, mode == 2 ? 16 : TILE_M, TILE_K, 0, &mw)) return LLM_ERR_UNSUPPORTED;
-  if (!tensor_map(X, T, K, lda, bn, TILE_K, 0, &mx)) return LLM_ERR_UNSUPPORTED;
+  if (!llm_tensor_map(W, N, K, ldw, mode == 2 ? 16 : TILE_M, TILE_K, 0, &mw)) return LLM_ERR_UNSUPPORTED;
+  if (!llm_tensor_map(X, T, K, lda, bn, TILE_K, 0, &mx)) return LLM_ERR_UNSUPPORTED;
   if (mode == 0) {
     if (c_dtype == LLM_F32 && splits > 1) {   // partial sums are added into zeros
       const int z = llm_zero_f32((float*)C, T, N, ldc, stream);

@@ -283,10 +283,12 @@ def check_tc_status(device) -> None:
 
 
 def token_tile(rows: int) -> int:
+    """Tokens per tile of the tensor-core product: the smallest tile that holds the rows, 256
+    (the persistent kernel) once there are enough rows to fill the GPU with such tiles."""
     for bn in (16, 32, 64, 128):
         if rows <= bn:
             return bn
-    return 128
+    return 256 if rows >= 512 else 128
 
 
 def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:

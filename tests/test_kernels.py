@@ -227,7 +227,8 @@ def test_qk_norm_rope_store(dtype, Hq, Hkv, hd, page):
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 128, 64), (16, 256, 128), (5, 200, 72), (40, 384, 4096),
-                                   (130, 130, 264), (300, 1000, 512), (64, 4096, 12288)])
+                                   (130, 130, 264), (300, 1000, 512), (64, 4096, 12288),
+                                   (700, 384, 520), (1100, 130, 72)])
 def test_gemm_tcgen05(T, N, K):
     from llmario_b200 import kernels
     a, w = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=3)
@@ -258,7 +259,8 @@ def test_gemm_tcgen05(T, N, K):
     kernels.check_tc_status(DEV)
 
 
-@pytest.mark.parametrize("T,ff,K", [(3, 64, 64), (20, 200, 136), (150, 1000, 512)])
+@pytest.mark.parametrize("T,ff,K", [(3, 64, 64), (20, 200, 136), (150, 1000, 512),
+                                    (600, 200, 136), (1030, 72, 64)])
 def test_gemm_tcgen05_gated(T, ff, K):
     from llmario_b200 import kernels
     a, w = rnd(T, K, dtype=torch.bfloat16), rnd(2 * ff, K, dtype=torch.bfloat16, seed=3, scale=0.3)
