@@ -86,9 +86,14 @@ def cmd_attention(a) -> None:
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
 
     def fn():
-        kernels.attention_flash(q, out, storage[0, 0, 0], storage[0, 0, 1], storage.stride(0), table,
-                                None, B, 16, Hq, Hkv, hd, page, hd ** -0.5, None, splits, po, pml,
-                                slot, pos)
+        if a.row_major:
+            kernels.attention_flash(q, out, storage[0, 0, 0], storage[0, 0, 1], storage.stride(0),
+                                    table, None, B, 16, Hq, Hkv, hd, page, hd ** -0.5, None, splits,
+                                    po, pml, slot, pos)
+        else:
+            kernels.attention_decode(q, out, storage[0, 0, 0], storage[0, 0, 1], storage.stride(0),
+                                     table, None, B, Hq, Hkv, hd, page, hd ** -0.5, None, splits,
+                                     po, pml, slot, pos)
         if splits > 1:
             kernels.attention_merge(po, pml, out, None, B, Hq, hd, splits)
 
@@ -132,6 +137,8 @@ def main(argv=None) -> int:
     d.add_argument("--batch", type=int, default=8)
     d.add_argument("--context", type=int, default=1024)
     d.add_argument("--splits", type=int, default=0)
+    d.add_argument("--row-major", action="store_true",
+                   help="the 16-row kernel of attention_flash.cu instead of the decode kernel")
     d.set_defaults(fn=cmd_attention)
     p = sub.add_parser("prefill-attention")
     p.add_argument("--tokens", type=int, default=2048)

@@ -51,6 +51,7 @@ def _declare(l) -> None:
         "llm_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "llm_attention_flash": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "llm_attention_merge": [P, P, P, P, I, I, I, I, P],
+        "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
     for name, args in sigs.items():
@@ -378,6 +379,25 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         float(scale), int(window or 0), splits, _stream()), f"attention_flash (head_dim {head_dim})")
 
 
+def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
+                     v_cache: torch.Tensor, page_stride: int, block_table: torch.Tensor,
+                     items: Optional[torch.Tensor], n_items: int, num_heads: int,
+                     num_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                     window: Optional[int], splits: int = 1,
+                     part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                     row_slot: Optional[torch.Tensor] = None,
+                     row_pos: Optional[torch.Tensor] = None) -> None:
+    """Decode form of the tensor-core attention: items of at most eight (token, head of the
+    group) pairs, keys on the M side of the tile.  Arguments as :func:`attention_flash`."""
+    _cuda(q, out, k_cache, v_cache, block_table, items, part_o, part_ml, row_slot, row_pos)
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    _check(lib().llm_attention_decode(
+        _ptr(q), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(k_cache), _ptr(v_cache),
+        page_stride, _ptr(block_table), block_table.stride(0), _ptr(items), _ptr(row_slot),
+        _ptr(row_pos), n_items, num_heads, num_kv_heads, head_dim, page_size, float(scale),
+        int(window or 0), splits, _stream()), f"attention_decode (head_dim {head_dim})")
+
+
 def attention_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor,
                     rows: Optional[torch.Tensor], n_rows: int, num_heads: int, head_dim: int,
                     splits: int) -> None:
@@ -395,8 +415,8 @@ def decode_splits(n_items: int, num_kv_heads: int, max_len: int) -> int:
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
               head_dim: int, scale: float, window: Optional[int]) -> None:
     """Causal attention of every row of the step over its own request's cached keys.
-    bfloat16 with a head size the tensor-core kernel has: decode rows and short portions go to
-    its one-warp form (keys split across CTAs), longer portions to its four-warp form.
+    bfloat16 with a head size the tensor-core kernels have: decode rows and very short portions
+    go to the decode kernel (keys split across CTAs), longer portions to the four-warp kernel.
     Everything else (32-bit, other head sizes, very large groups) runs the generic kernel."""
     group = num_heads // num_kv_heads
     if q.dtype != torch.bfloat16 or head_dim not in FLASH_HEAD_DIMS or group > 16:
@@ -409,20 +429,23 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
     if plan.n_small:
         reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
         splits = decode_splits(plan.n_small, num_kv_heads, reach) if plan.small_single else 1
+        part_o = part_ml = None
         if splits > 1:
             part_o = ctx.buffer("attn.part_o", (ctx.rows * num_heads * splits * head_dim,),
                                 torch.float32)
             part_ml = ctx.buffer("attn.part_ml", (ctx.rows * num_heads * splits * 2,),
                                  torch.float32)
+        if group <= 8:      # at most eight (token, head) pairs per item: keys on the M side
+            attention_decode(q, out, *common, plan.small, plan.n_small, num_heads, num_kv_heads,
+                             head_dim, view.page_size, scale, window, splits, part_o, part_ml,
+                             ctx.row_slot, ctx.row_pos)
+        else:
             attention_flash(q, out, *common, plan.small, plan.n_small, 16, num_heads,
                             num_kv_heads, head_dim, view.page_size, scale, window, splits,
                             part_o, part_ml, ctx.row_slot, ctx.row_pos)
+        if splits > 1:
             attention_merge(part_o, part_ml, out, plan.small_rows, plan.n_small, num_heads,
                             head_dim, splits)
-        else:
-            attention_flash(q, out, *common, plan.small, plan.n_small, 16, num_heads,
-                            num_kv_heads, head_dim, view.page_size, scale, window,
-                            row_slot=ctx.row_slot, row_pos=ctx.row_pos)
     if plan.n_large:
         attention_flash(q, out, *common, plan.large, plan.n_large, 64, num_heads, num_kv_heads,
                         head_dim, view.page_size, scale, window)

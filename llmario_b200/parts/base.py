@@ -134,11 +134,14 @@ class StepContext:
         return self.workspace.get(name, shape, dtype or self.dtype)
 
     def attention_plan(self, group: int) -> AttentionPlan:
-        """Work items for attention kernels whose CTAs hold ``group`` query heads per token."""
+        """Work items for attention kernels whose CTAs hold ``group`` query heads per token:
+        small items have at most 8 (token, head) pairs (16 for a group above 8), large ones at
+        most 64."""
         plan = self.plans.get(group)
         if plan is not None:
             return plan
-        small_cap, large_cap = max(1, 16 // group), max(1, 64 // group)
+        small_cap = max(1, (8 if group <= 8 else 16) // group)
+        large_cap = max(1, 64 // group)
         if all(s.rows == 1 for s in self.segments):
             plan = AttentionPlan(n_small=self.rows, small_single=True)   # rows describe themselves
         else:

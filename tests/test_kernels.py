@@ -334,3 +334,58 @@ def test_attention_flash(Hq, Hkv, hd, page, window):
         kernels.attention_flash(qd, out, storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table,
                                 dev, len(items), rpc, Hq, Hkv, hd, page, scale, window)
     check(rows, out, q)
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (6, 3, 64, 8, 50),
+                                                   (4, 4, 32, 4, None), (8, 1, 128, 16, 200),
+                                                   (3, 1, 64, 32, None), (32, 8, 128, 16, None)])
+def test_attention_decode(Hq, Hkv, hd, page, window):
+    """The decode kernel (keys on the M side): one-token items with the keys split and merged,
+    and items of a few tokens (at most eight token-head pairs)."""
+    from llmario_b200 import kernels
+    dtype = torch.bfloat16
+    G = Hq // Hkv
+    lengths = [1, 33, 150, 64, 700, 385]
+    storage, table, ks, vs = paged_setup(lengths, page, Hkv, hd, dtype)
+    scale = 1 / math.sqrt(hd)
+    g = torch.Generator().manual_seed(5)
+    common = (storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table)
+
+    def check(rows, out, q, tol=2e-2):
+        for i, (r, p) in enumerate(rows):
+            ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
+            got = out[i].reshape(Hq, hd).double().cpu()
+            assert (got - ref).abs().max() <= tol, (i, r, p, (got - ref).abs().max())
+
+    rows = [(r, n - 1) for r, n in enumerate(lengths)]
+    q = torch.randn(len(rows), Hq, hd, generator=g).to(dtype)
+    qd = q.reshape(len(rows), -1).to(DEV).contiguous()
+    slot = torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    for splits in (1, 3, 5):
+        out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
+        po = torch.empty(len(rows) * Hq * splits * hd, dtype=torch.float32, device=DEV)
+        pml = torch.empty(len(rows) * Hq * splits * 2, dtype=torch.float32, device=DEV)
+        kernels.attention_decode(qd, out, *common, None, len(rows), Hq, Hkv, hd, page, scale, window,
+                                 splits, po, pml, slot, pos)
+        if splits > 1:
+            kernels.attention_merge(po, pml, out, None, len(rows), Hq, hd, splits)
+        check(rows, out, q)
+    cap = 8 // G
+    if cap >= 2:       # items of several tokens: every pair has its own causal limit
+        start = 700 - 41
+        sizes, at = [], start
+        for n in [cap, 1, cap, cap - 1 or 1] * 20:
+            n = min(n, 700 - at)
+            if n <= 0:
+                break
+            sizes.append((at, n))
+            at += n
+        rows = [(4, p) for p in range(start, at)]
+        q = torch.randn(len(rows), Hq, hd, generator=g).to(dtype)
+        qd = q.reshape(len(rows), -1).to(DEV).contiguous()
+        out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
+        items = torch.tensor([(p0 - start, n, 4, p0) for p0, n in sizes], dtype=torch.int32,
+                             device=DEV).reshape(-1)
+        kernels.attention_decode(qd, out, *common, items, len(sizes), Hq, Hkv, hd, page, scale, window)
+        check(rows, out, q)
