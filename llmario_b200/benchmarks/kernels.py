@@ -68,7 +68,7 @@ def cmd_gemm(a) -> None:
 def _paged(batch: int, context: int, Hkv: int, hd: int, page: int):
     pages_per = -(-context // page)
     n_pages = batch * pages_per
-    storage = torch.randn(n_pages, 1, 2, page, Hkv, hd, device=DEV).bfloat16()
+    storage = torch.randn(n_pages, 1, 2, Hkv, page, hd, device=DEV).bfloat16()
     perm = torch.randperm(n_pages, device=DEV).to(torch.int32)
     return storage, perm.reshape(batch, pages_per).contiguous()
 

@@ -8,7 +8,7 @@ What the reference does (crates/engine/kv/src/lib.rs:36-176; crates/engine/model
 key, layers that keep a window of them, and layers with a fixed-size recurrent state.
 
 Here layers with the same need share a *group*: one pool of pages, one device tensor
-``[page][cache slot of the group][K|V][position in page][kv head][head dim]`` and one block
+``[page][cache slot of the group][K|V][kv head][position in page][head dim]`` and one block
 table.  A group whose layers only look back ``window`` keys gives a page back as soon as every
 key in it is out of reach of any later query.  Fixed-size state lives in one tensor per
 run-order entry, indexed by the request's slot.
@@ -95,7 +95,7 @@ class _Group:
     n_pages: int
     entries: List[int] = field(default_factory=list)   # run-order entries stored here
     pool: PagePool = None                               # type: ignore[assignment]
-    storage: Optional[torch.Tensor] = None              # [page, slot, 2, page_size, Hkv, hd]
+    storage: Optional[torch.Tensor] = None              # [page, slot, 2, Hkv, page_size, hd]
     table: Optional[torch.Tensor] = None                # device int32 [requests, pages/request]
     # (request slot, page index) -> page id, changes not yet sent to the device table
     updates: Dict[Tuple[int, int], int] = field(default_factory=dict)
@@ -111,6 +111,8 @@ class CacheView:
     block_table: torch.Tensor
     page_size: int
     group: int
+    storage: Optional[torch.Tensor] = None   # the group's whole tensor, for kernels that tile it
+    slot: int = 0                            # this call's cache slot inside the group
 
 
 class _Request:
@@ -176,8 +178,10 @@ class CacheManager:
         self.device, self.dtype = torch.device(device), dtype
         for g in self.groups:
             n = g.need
-            g.storage = torch.zeros((g.n_pages, len(g.entries), 2, self.page_size,
-                                     n.num_kv_heads, n.head_dim), dtype=dtype, device=device)
+            # per KV head the positions of a page lie one after the other: a kernel that serves
+            # one KV head reads page_size * head_dim contiguous elements per page
+            g.storage = torch.zeros((g.n_pages, len(g.entries), 2, n.num_kv_heads,
+                                     self.page_size, n.head_dim), dtype=dtype, device=device)
             g.table = torch.full((self.max_requests, self.pages_per_request), -1,
                                  dtype=torch.int32, device=device)
         for i, need in self._state_need.items():
@@ -199,7 +203,7 @@ class CacheManager:
         g = self.groups[gi]
         st = g.storage
         return CacheView(st[0, slot, 0], st[0, slot, 1], st.stride(0), g.table, self.page_size,
-                         gi)
+                         gi, st, slot)
 
     def state_of(self, entry: int) -> Optional[torch.Tensor]:
         return self.state.get(entry)

@@ -107,13 +107,13 @@ __global__ void __launch_bounds__(32, 6) flash_decode_kernel(
       const int pg = p0 / page_size;
       const int in_page = p0 - pg * page_size;
       const int run = min(page_size - in_page, last - p0 + 1);
-      const long long off = (long long)table[pg] * page_stride + ((long long)in_page * Hkv + kvh) * HD;
+      const long long off = (long long)table[pg] * page_stride + ((long long)kvh * page_size + in_page) * HD;
       const bf16* ksrc = k_cache + off;
       const bf16* vsrc = v_cache + off;
       const int j0 = p0 - base;
       for (int id = lane; id < run * CPR; id += 32) {
         const int j = id / CPR, c = id % CPR;
-        const int src = j * Hkv * HD + c * 8;
+        const int src = j * HD + c * 8;
         const int dst = (j0 + j) * HD + swizzle<CPR>(j0 + j, c) * 8;
         cp_async16(kd + dst, ksrc + src, true);
         cp_async16(vd + dst, vsrc + src, true);

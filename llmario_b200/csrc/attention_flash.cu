@@ -83,8 +83,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 6) flash_paged_ke
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   // A tile is filled page by page: one look-up in the block table per page, then the rows of
-  // that page (consecutive positions, Hkv * HD elements apart) in 16-byte pieces, two rows per
-  // warp instruction.  Rows outside the item's key range are cleared: their scores are masked,
+  // that page and KV head (consecutive positions, contiguous) in 16-byte pieces.  Rows outside the item's key range are cleared: their scores are masked,
   // but their values must be finite.
   auto load_tile = [&](int tb, int stage) {
     bf16* kd = ks + stage * KT * HD;
@@ -105,13 +104,13 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 6) flash_paged_ke
       const int pg = p0 / page_size;
       const int in_page = p0 - pg * page_size;
       const int run = min(page_size - in_page, last - p0 + 1);
-      const long long off = (long long)table[pg] * page_stride + ((long long)in_page * Hkv + kvh) * HD;
+      const long long off = (long long)table[pg] * page_stride + ((long long)kvh * page_size + in_page) * HD;
       const bf16* ksrc = k_cache + off;
       const bf16* vsrc = v_cache + off;
       const int j0 = p0 - base;
       for (int id = threadIdx.x; id < run * CPR; id += WARPS * 32) {
         const int j = id / CPR, c = id % CPR;
-        const int src = j * Hkv * HD + c * 8;
+        const int src = j * HD + c * 8;
         const int dst = (j0 + j) * HD + swizzle<CPR>(j0 + j, c) * 8;
         cp_async16(kd + dst, ksrc + src, true);
         cp_async16(vd + dst, vsrc + src, true);

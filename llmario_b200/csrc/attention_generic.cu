@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
     float s = -INFINITY;
     if (valid) {
       const int page = table[p / page_size];
-      off = (long long)page * page_stride + ((long long)(p % page_size) * Hkv + kvh) * hd;
+      off = (long long)page * page_stride + ((long long)kvh * page_size + p % page_size) * hd;
       const T* kr = k_cache + off;
       float d = 0.f;
       for (int i = 0; i < hd; i += 8) {

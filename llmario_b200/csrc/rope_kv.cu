@@ -1,5 +1,6 @@
 // Per-head RMS norm of queries and keys, half-split rotation by absolute position, and the write
-// of keys and values into the paged cache, in one pass over the projection output.
+// of keys and values into the paged cache (a page holds, per KV head, its positions one after
+// the other), in one pass over the projection output.
 //   order per head: norm -> rotation -> store; values are stored as projected.
 // All arithmetic is 32-bit; rounding to the cache / activation type happens once, at the store.
 #include "common.cuh"
@@ -33,7 +34,7 @@ __global__ void qk_norm_rope_store_kernel(
     const int in_page = pos % page_size;
     const int kvh = (h - Hq) % Hkv;
     TC* base = (h < Hq + Hkv) ? k_cache : v_cache;
-    cache_dst = base + (size_t)page * page_stride + ((size_t)in_page * Hkv + kvh) * hd;
+    cache_dst = base + (size_t)page * page_stride + ((size_t)kvh * page_size + in_page) * hd;
   }
   if (h >= Hq + Hkv) {  // value: copy
     for (int i = lane; i < hd; i += 32) cache_dst[i] = from_f32<TC>(src[i]);

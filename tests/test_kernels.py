@@ -99,7 +99,7 @@ def paged_setup(lengths, page, Hkv, hd, dtype, seed=0, n_layers_in_page=2, layer
     n_pages = sum(-(-n // page) for n in lengths) + 3
     g = torch.Generator().manual_seed(seed)
     perm = torch.randperm(n_pages, generator=g).tolist()
-    storage = torch.zeros(n_pages, n_layers_in_page, 2, page, Hkv, hd, dtype=dtype, device=DEV)
+    storage = torch.zeros(n_pages, n_layers_in_page, 2, Hkv, page, hd, dtype=dtype, device=DEV)
     maxp = max(-(-n // page) for n in lengths) + 1
     table = torch.full((len(lengths), maxp), -1, dtype=torch.int32)
     ks, vs = [], []
@@ -113,8 +113,8 @@ def paged_setup(lengths, page, Hkv, hd, dtype, seed=0, n_layers_in_page=2, layer
             at += 1
             table[r, j] = p
             m = min(page, n - j * page)
-            storage[p, layer, 0, :m] = k[j * page:j * page + m].to(DEV)
-            storage[p, layer, 1, :m] = v[j * page:j * page + m].to(DEV)
+            storage[p, layer, 0, :, :m] = k[j * page:j * page + m].transpose(0, 1).to(DEV)
+            storage[p, layer, 1, :, :m] = v[j * page:j * page + m].transpose(0, 1).to(DEV)
     return storage, table.to(DEV), ks, vs
 
 
@@ -172,7 +172,7 @@ def test_attention_far_key_stands_out():
         ks[0][far, kvh] = 0
     ks[0][far] = 40 * q[0, ::2] / q[0, ::2].norm(dim=-1, keepdim=True)   # aligned with heads 0, 2
     p_idx, s_idx = table[0, far // page].item(), far % page
-    storage[p_idx, 0, 0, s_idx] = ks[0][far].to(DEV)
+    storage[p_idx, 0, 0, :, s_idx] = ks[0][far].to(DEV)
     out = torch.empty(1, Hq * hd, dtype=torch.float32, device=DEV)
     kernels.attention_generic(q.reshape(1, -1).to(DEV), out, storage[0, 0, 0], storage[0, 0, 1],
                               storage.stride(0), table, torch.zeros(1, dtype=torch.int32, device=DEV),
@@ -198,7 +198,7 @@ def test_qk_norm_rope_store(dtype, Hq, Hkv, hd, page):
     inv_freq = torch.tensor(np.power(np.float32(theta), -(np.arange(hd // 2, dtype=np.float32) * 2) / hd)
                             .astype(np.float32), device=DEV)
     n_pages = 1024 // page + 1
-    storage = torch.zeros(n_pages, 1, 2, page, Hkv, hd, dtype=dtype, device=DEV)
+    storage = torch.zeros(n_pages, 1, 2, Hkv, page, hd, dtype=dtype, device=DEV)
     table = torch.arange(n_pages, dtype=torch.int32, device=DEV).flip(0).reshape(1, -1).contiguous()
     q_out = torch.empty(T, Hq * hd, dtype=dtype, device=DEV)
     slot = torch.zeros(T, dtype=torch.int32, device=DEV)
@@ -222,8 +222,8 @@ def test_qk_norm_rope_store(dtype, Hq, Hkv, hd, page):
         vr = pc[i, (Hq + Hkv) * hd:].reshape(Hkv, hd)
         page_id = table[0, p // page].item()
         assert (q_out[i].double().cpu().reshape(Hq, hd) - qr).abs().max() <= tol
-        assert (storage[page_id, 0, 0, p % page].double().cpu() - kr).abs().max() <= tol
-        assert (storage[page_id, 0, 1, p % page].double().cpu() - vr).abs().max() <= tol
+        assert (storage[page_id, 0, 0, :, p % page].double().cpu() - kr).abs().max() <= tol
+        assert (storage[page_id, 0, 1, :, p % page].double().cpu() - vr).abs().max() <= tol
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 128, 64), (16, 256, 128), (5, 200, 72), (40, 384, 4096),

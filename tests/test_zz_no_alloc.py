@@ -21,14 +21,14 @@ def _setup(lengths, page, Hkv, hd, seed):
     g = torch.Generator().manual_seed(seed)
     n_pages = sum(-(-n // page) for n in lengths) + 2
     perm = torch.randperm(n_pages, generator=g).tolist()
-    storage = torch.zeros(n_pages, 1, 2, page, Hkv, hd, dtype=torch.bfloat16, device=DEV)
+    storage = torch.zeros(n_pages, 1, 2, Hkv, page, hd, dtype=torch.bfloat16, device=DEV)
     table = torch.full((len(lengths), max(-(-n // page) for n in lengths)), -1, dtype=torch.int32)
     at = 0
     for r, n in enumerate(lengths):
         for j in range(-(-n // page)):
             table[r, j] = perm[at]
             m = min(page, n - j * page)
-            storage[perm[at], 0, :, :m] = torch.randn(2, m, Hkv, hd, generator=g).to(torch.bfloat16).to(DEV)
+            storage[perm[at], 0, :, :, :m] = torch.randn(2, Hkv, m, hd, generator=g).to(torch.bfloat16).to(DEV)
             at += 1
     return storage, table.to(DEV)
 
