@@ -90,10 +90,13 @@ def cmd_attention(a) -> None:
             kernels.attention_flash(q, out, storage[0, 0, 0], storage[0, 0, 1], storage.stride(0),
                                     table, None, B, 16, Hq, Hkv, hd, page, hd ** -0.5, None, splits,
                                     po, pml, slot, pos)
-        else:
+        elif a.cp_async:
             kernels.attention_decode(q, out, storage[0, 0, 0], storage[0, 0, 1], storage.stride(0),
                                      table, None, B, Hq, Hkv, hd, page, hd ** -0.5, None, splits,
                                      po, pml, slot, pos)
+        else:
+            kernels.attention_decode_tma(q, out, storage, 0, table, None, B, Hq, Hkv, hd, page,
+                                         hd ** -0.5, None, splits, po, pml, slot, pos)
         if splits > 1:
             kernels.attention_merge(po, pml, out, None, B, Hq, hd, splits)
 
@@ -137,6 +140,8 @@ def main(argv=None) -> int:
     d.add_argument("--batch", type=int, default=8)
     d.add_argument("--context", type=int, default=1024)
     d.add_argument("--splits", type=int, default=0)
+    d.add_argument("--cp-async", action="store_true",
+                   help="the decode kernel that loads with cp.async instead of TMA tiles")
     d.add_argument("--row-major", action="store_true",
                    help="the 16-row kernel of attention_flash.cu instead of the decode kernel")
     d.set_defaults(fn=cmd_attention)

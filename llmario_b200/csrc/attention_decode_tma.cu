@@ -1,0 +1,297 @@
+// Decode attention with the cache streamed by the TMA unit.
+//
+// The arithmetic is that of attention_decode.cu (keys on the M side of mma.sync m16n8k16, at most
+// eight (token, head) pairs per item, 32-bit running maximum and sum per pair, optional split of
+// the key range).  What differs is how K and V reach shared memory.  The cache of a group of
+// layers is one tensor [page][cache slot][K|V][kv head][position][head dim]; seen as a matrix of
+// rows of head_dim elements it is tiled by one tensor map, and the positions of one page and KV
+// head are `page_size` consecutive rows.  One lane asks for them with a few TMA tile loads per
+// 32-key tile (64 columns x up to 32 rows each, 128-byte swizzle) and the bytes are counted on an
+// mbarrier per stage of a four-stage ring, so the warp spends its instructions on the products
+// and not on addresses.  Head sizes 64 and 128; other sizes use attention_decode.cu.
+#include "attention_common.cuh"
+#include "tcgen05.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+
+// byte offset of 16-byte chunk c (0 .. HD/8-1) of key row r inside a K or V tile of a stage:
+// the tile is [HD/64 column halves][KT rows][128 bytes] with the TMA 128-byte swizzle
+template <int KT> __device__ __forceinline__ int tile_off(int r, int c) {
+  return (c >> 3) * (KT * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+}
+
+template <int HD, int KT, int STAGES>
+__global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
+    const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, bf16* __restrict__ out,
+    float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_table,
+    int table_stride, const int* __restrict__ items, const int* __restrict__ row_slot,
+    const int* __restrict__ row_pos, int Hq, int Hkv, int page_size, long long rows_per_page,
+    int k_row0, int v_row0, float scale_log2, int window, int splits, int* __restrict__ status) {
+  constexpr int KS = HD / 16, MT = KT / 16, DM = HD / 16, HALVES = HD / 64;
+  constexpr int TILE_BYTES = KT * HD * 2;            // one K or V tile
+  extern __shared__ uint8_t raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* ks = smem;                                // [STAGES][TILE_BYTES]
+  uint8_t* vs = smem + STAGES * TILE_BYTES;          // [STAGES][TILE_BYTES]
+  uint64_t* full = reinterpret_cast<uint64_t*>(vs + STAGES * TILE_BYTES);
+  pdl_trigger();
+
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  // values of rows that no load fills are multiplied by zero weights: they must be finite
+  for (int i = lane; i < STAGES * TILE_BYTES / 16; i += 32)
+    reinterpret_cast<uint4*>(vs)[i] = make_uint4(0, 0, 0, 0);
+  if (lane == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  pdl_wait();
+
+  const Item it = items ? reinterpret_cast<const Item*>(items)[blockIdx.x]
+                        : Item{(int)blockIdx.x, 1, row_slot[blockIdx.x], row_pos[blockIdx.x]};
+  const int kvh = blockIdx.y, z = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int pairs = it.tokens * G;                 // <= 8
+  const int hi = it.pos_start + it.tokens - 1;
+  const int lo = (window > 0 && it.pos_start + 1 > window) ? it.pos_start + 1 - window : 0;
+  const int tile_first = lo / KT, tile_last = hi / KT;
+  const int ntiles = tile_last - tile_first + 1;
+  const int per = (ntiles + splits - 1) / splits;
+  const int tb0 = tile_first + z * per;
+  const int tb1 = min(tile_last + 1, tb0 + per);
+  const int* table = block_table + (size_t)it.slot * table_stride;
+
+  int cpos[2], clo[2];
+  bool cvalid[2];
+  size_t crow[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int n = 2 * t + j;
+    cvalid[j] = n < pairs;
+    const int tok = cvalid[j] ? n / G : 0, head = kvh * G + (cvalid[j] ? n % G : 0);
+    cpos[j] = it.pos_start + tok;
+    clo[j] = (window > 0 && cpos[j] + 1 > window) ? cpos[j] + 1 - window : 0;
+    crow[j] = (size_t)(it.row_start + tok) * Hq + head;
+  }
+  uint32_t qf[KS][2];
+  {
+    const bool valid = g < pairs;
+    const int tok = valid ? g / G : 0, head = kvh * G + (valid ? g % G : 0);
+    const bf16* src = q + ((size_t)(it.row_start + tok) * Hq + head) * HD + 2 * t;
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+      qf[k][0] = valid ? *reinterpret_cast<const uint32_t*>(src + k * 16) : 0u;
+      qf[k][1] = valid ? *reinterpret_cast<const uint32_t*>(src + k * 16 + 8) : 0u;
+    }
+  }
+  float o[DM][4];
+#pragma unroll
+  for (int d = 0; d < DM; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  // lane 0 asks for the pages of a tile: R = min(page_size, KT) rows per load
+  const int R = page_size < KT ? page_size : KT;
+  auto load_tile = [&](int tb, int stage) {
+    const int base = tb * KT;
+    uint32_t bytes = 0;
+    for (int p = base; p < base + KT; p += R)
+      if (p <= hi && p + R - 1 >= lo) bytes += (uint32_t)R * HD * 2 * 2;
+    mbar_expect_tx(&full[stage], bytes);
+    for (int p = base; p < base + KT; p += R) {
+      if (p > hi || p + R - 1 < lo) continue;       // no key of the item here: the page may be gone
+      const long long row = (long long)table[p / page_size] * rows_per_page + (long long)kvh * page_size +
+                            p % page_size;
+      const int dst = (p - base) * 128;
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        tma_load_2d(ks + stage * TILE_BYTES + h * KT * 128 + dst, &map_kv, h * 64, (int)(row + k_row0),
+                    &full[stage]);
+        tma_load_2d(vs + stage * TILE_BYTES + h * KT * 128 + dst, &map_kv, h * 64, (int)(row + v_row0),
+                    &full[stage]);
+      }
+    }
+  };
+
+  if (lane == 0)
+    for (int i = 0; i < STAGES && tb0 + i < tb1; ++i) load_tile(tb0 + i, i);
+  bool alive = true;
+  for (int tb = tb0; tb < tb1; ++tb) {
+    const int n_it = tb - tb0;
+    const int stage = n_it % STAGES;
+    alive = mbar_wait(&full[stage], (uint32_t)(n_it / STAGES) & 1);
+    alive = __all_sync(0xffffffffu, alive);
+    if (!alive) {
+      if (lane == 0) atomicExch(status, 4);
+      break;
+    }
+    const uint8_t* kt = ks + stage * TILE_BYTES;
+    const uint8_t* vt = vs + stage * TILE_BYTES;
+
+    // ---- S^T = K Q^T
+    float s[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t a[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4(a, kt + tile_off<KT>(mt * 16 + (mi & 1) * 8 + (lane & 7), 2 * k + (mi >> 1)));
+        mma_bf16(s[mt], a, qf[k][0], qf[k][1]);
+      }
+    }
+    // ---- mask, running maximum per pair, exponentials
+    const int base = tb * KT;
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = e & 1;
+        const int p = base + mt * 16 + g + 8 * (e >> 1);
+        const bool vis = cvalid[j] && p <= cpos[j] && p >= clo[j];
+        s[mt][e] = vis ? s[mt][e] * scale_log2 : -INFINITY;
+        tmax[j] = fmaxf(tmax[j], s[mt][e]);
+      }
+    float corr[2], muse[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 4));
+      tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 8));
+      tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 16));
+      const float mnew = fmaxf(m[j], tmax[j]);
+      muse[j] = mnew == -INFINITY ? 0.f : mnew;
+      corr[j] = fast_exp2(m[j] - muse[j]);
+      m[j] = mnew;
+      l[j] *= corr[j];
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pexp = fast_exp2(s[mt][e] - muse[e & 1]);
+        s[mt][e] = pexp;
+        l[e & 1] += pexp;
+      }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+      for (int d = 0; d < DM; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[1];
+        o[d][2] *= corr[0]; o[d][3] *= corr[1];
+      }
+    }
+    // ---- O^T += V^T P^T
+#pragma unroll
+    for (int kk = 0; kk < MT; ++kk) {
+      const uint32_t b0 = movmatrix_trans(pack_bf16(s[kk][0], s[kk][1]));
+      const uint32_t b1 = movmatrix_trans(pack_bf16(s[kk][2], s[kk][3]));
+#pragma unroll
+      for (int d = 0; d < DM; ++d) {
+        uint32_t a[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4_trans(a, vt + tile_off<KT>(kk * 16 + (mi >> 1) * 8 + (lane & 7), 2 * d + (mi & 1)));
+        mma_bf16(o[d], a, b0, b1);
+      }
+    }
+    __syncwarp();                  // every lane has read this stage
+    if (lane == 0 && tb + STAGES < tb1) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      load_tile(tb + STAGES, stage);
+    }
+  }
+  if (!alive) {   // let the loads that are still in flight land before the shared memory goes
+    for (int i = 0; i < STAGES; ++i) mbar_wait(&full[i], 0), mbar_wait(&full[i], 1);
+    return;
+  }
+
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    l[j] += __shfl_xor_sync(0xffffffffu, l[j], 4);
+    l[j] += __shfl_xor_sync(0xffffffffu, l[j], 8);
+    l[j] += __shfl_xor_sync(0xffffffffu, l[j], 16);
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    if (!cvalid[j]) continue;
+    if (splits == 1) {
+      const float inv = 1.0f / l[j];
+      bf16* dst = out + crow[j] * HD;
+#pragma unroll
+      for (int d = 0; d < DM; ++d) {
+        dst[d * 16 + g] = __float2bfloat16_rn(o[d][j] * inv);
+        dst[d * 16 + g + 8] = __float2bfloat16_rn(o[d][2 + j] * inv);
+      }
+    } else {
+      float* dst = part_o + (crow[j] * splits + z) * HD;
+#pragma unroll
+      for (int d = 0; d < DM; ++d) {
+        dst[d * 16 + g] = o[d][j];
+        dst[d * 16 + g + 8] = o[d][2 + j];
+      }
+      if (g == 0) {
+        part_ml[(crow[j] * splits + z) * 2] = m[j];
+        part_ml[(crow[j] * splits + z) * 2 + 1] = l[j];
+      }
+    }
+  }
+}
+
+template <int HD>
+int launch(const CUtensorMap& map, const bf16* q, bf16* out, float* part_o, float* part_ml, const int* table,
+           int table_stride, const int* items, const int* row_slot, const int* row_pos, int n_items, int Hq,
+           int Hkv, int page_size, long long rows_per_page, int k_row0, int v_row0, float scale, int window,
+           int splits, int* status, cudaStream_t s) {
+  constexpr int KT = 32, STAGES = 4;
+  auto kernel = flash_decode_tma_kernel<HD, KT, STAGES>;
+  constexpr int smem = 2 * STAGES * KT * HD * 2 + STAGES * 8 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(n_items, Hkv, splits);
+  return launch_pdl(kernel, grid, 32, smem, s, map, q, out, part_o, part_ml, table, table_stride, items,
+                    row_slot, row_pos, Hq, Hkv, page_size, rows_per_page, k_row0, v_row0,
+                    scale * 1.4426950408889634f, window, splits, status);
+}
+}  // namespace
+
+// storage: the group's whole cache [n_pages][n_slots][2][Hkv][page_size][hd] bfloat16, contiguous;
+// slot: the cache slot of this layer call.  page_size must divide 32 or be a multiple of it.
+// Other arguments as llm_attention_decode.
+LLM_EXPORT int llm_attention_decode_tma(const void* q, void* out, float* part_o, float* part_ml,
+                                        const void* storage, long long n_pages, int n_slots, int slot,
+                                        const int* block_table, int table_stride, const int* items,
+                                        const int* row_slot, const int* row_pos, int n_items, int Hq,
+                                        int Hkv, int hd, int page_size, float scale, int window,
+                                        int splits, int* status, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv || splits < 1) return LLM_ERR_ARGUMENT;
+  if (splits > 1 && (!part_o || !part_ml)) return LLM_ERR_ARGUMENT;
+  if (hd != 64 && hd != 128) return LLM_ERR_UNSUPPORTED;
+  if (!(32 % page_size == 0 || page_size % 32 == 0)) return LLM_ERR_UNSUPPORTED;
+  const long long rows_per_page = (long long)n_slots * 2 * Hkv * page_size;
+  const long long total_rows = n_pages * rows_per_page;
+  if (total_rows >= (1LL << 31)) return LLM_ERR_UNSUPPORTED;
+  CUtensorMap map;
+  if (!llm_tensor_map(storage, total_rows, hd, hd, page_size < 32 ? page_size : 32, 64, 0, &map))
+    return LLM_ERR_UNSUPPORTED;
+  const int k_row0 = (slot * 2 + 0) * Hkv * page_size, v_row0 = (slot * 2 + 1) * Hkv * page_size;
+#define GO(HD)                                                                                          \
+  return launch<HD>(map, (const bf16*)q, (bf16*)out, part_o, part_ml, block_table, table_stride, items,  \
+                    row_slot, row_pos, n_items, Hq, Hkv, page_size, rows_per_page, k_row0, v_row0, scale, \
+                    window, splits, status, stream)
+  if (hd == 128) GO(128);
+  GO(64);
+#undef GO
+}

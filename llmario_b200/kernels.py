@@ -52,6 +52,8 @@ def _declare(l) -> None:
         "llm_attention_flash": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "llm_attention_merge": [P, P, P, P, I, I, I, I, P],
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
+        "llm_attention_decode_tma": [P, P, P, P, P, L, I, I, P, I, P, P, P, I, I, I, I, I, F, I,
+                                     I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
     for name, args in sigs.items():
@@ -398,6 +400,34 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         int(window or 0), splits, _stream()), f"attention_decode (head_dim {head_dim})")
 
 
+def attention_decode_tma(q: torch.Tensor, out: torch.Tensor, storage: torch.Tensor, slot: int,
+                         block_table: torch.Tensor, items: Optional[torch.Tensor], n_items: int,
+                         num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                         scale: float, window: Optional[int], splits: int = 1,
+                         part_o: Optional[torch.Tensor] = None,
+                         part_ml: Optional[torch.Tensor] = None,
+                         row_slot: Optional[torch.Tensor] = None,
+                         row_pos: Optional[torch.Tensor] = None) -> None:
+    """As :func:`attention_decode`, with K and V fetched by TMA tile loads from the group's
+    whole cache tensor ``storage`` [pages, slots, 2, kv heads, page size, head dim]."""
+    _cuda(q, out, storage, block_table, items, part_o, part_ml, row_slot, row_pos)
+    assert q.dtype == torch.bfloat16 and storage.dtype == torch.bfloat16
+    assert storage.is_contiguous() and storage.dim() == 6
+    _check(lib().llm_attention_decode_tma(
+        _ptr(q), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(storage), storage.shape[0],
+        storage.shape[1], slot, _ptr(block_table), block_table.stride(0), _ptr(items),
+        _ptr(row_slot), _ptr(row_pos), n_items, num_heads, num_kv_heads, head_dim, page_size,
+        float(scale), int(window or 0), splits, _ptr(tc_status(q.device)), _stream()),
+        f"attention_decode_tma (head_dim {head_dim})")
+
+
+def decode_tma_ok(view, head_dim: int) -> bool:
+    st = getattr(view, "storage", None)
+    ps = view.page_size
+    return (st is not None and st.is_contiguous() and head_dim in (64, 128)
+            and (32 % ps == 0 or ps % 32 == 0) and st.numel() // head_dim < (1 << 31))
+
+
 def attention_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor,
                     rows: Optional[torch.Tensor], n_rows: int, num_heads: int, head_dim: int,
                     splits: int) -> None:
@@ -435,7 +465,11 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
                                 torch.float32)
             part_ml = ctx.buffer("attn.part_ml", (ctx.rows * num_heads * splits * 2,),
                                  torch.float32)
-        if group <= 8:      # at most eight (token, head) pairs per item: keys on the M side
+        if group <= 8 and decode_tma_ok(view, head_dim):
+            attention_decode_tma(q, out, view.storage, view.slot, view.block_table, plan.small,
+                                 plan.n_small, num_heads, num_kv_heads, head_dim, view.page_size,
+                                 scale, window, splits, part_o, part_ml, ctx.row_slot, ctx.row_pos)
+        elif group <= 8:    # at most eight (token, head) pairs per item: keys on the M side
             attention_decode(q, out, *common, plan.small, plan.n_small, num_heads, num_kv_heads,
                              head_dim, view.page_size, scale, window, splits, part_o, part_ml,
                              ctx.row_slot, ctx.row_pos)

@@ -339,10 +339,14 @@ def test_attention_flash(Hq, Hkv, hd, page, window):
 @pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (6, 3, 64, 8, 50),
                                                    (4, 4, 32, 4, None), (8, 1, 128, 16, 200),
                                                    (3, 1, 64, 32, None), (32, 8, 128, 16, None)])
-def test_attention_decode(Hq, Hkv, hd, page, window):
-    """The decode kernel (keys on the M side): one-token items with the keys split and merged,
-    and items of a few tokens (at most eight token-head pairs)."""
+@pytest.mark.parametrize("tma", [False, True])
+def test_attention_decode(Hq, Hkv, hd, page, window, tma):
+    """The decode kernels (keys on the M side; loads by cp.async or by TMA tiles): one-token
+    items with the keys split and merged, and items of a few tokens (at most eight token-head
+    pairs)."""
     from llmario_b200 import kernels
+    if tma and hd not in (64, 128):
+        pytest.skip("the TMA form has head sizes 64 and 128")
     dtype = torch.bfloat16
     G = Hq // Hkv
     lengths = [1, 33, 150, 64, 700, 385]
@@ -350,6 +354,15 @@ def test_attention_decode(Hq, Hkv, hd, page, window):
     scale = 1 / math.sqrt(hd)
     g = torch.Generator().manual_seed(5)
     common = (storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table)
+
+    def run(qd, out, items, n, splits=1, po=None, pml=None, slot=None, pos=None):
+        if tma:
+            kernels.attention_decode_tma(qd, out, storage, 1, table, items, n, Hq, Hkv, hd, page,
+                                         scale, window, splits, po, pml, slot, pos)
+            kernels.check_tc_status(DEV)
+        else:
+            kernels.attention_decode(qd, out, *common, items, n, Hq, Hkv, hd, page, scale, window,
+                                     splits, po, pml, slot, pos)
 
     def check(rows, out, q, tol=2e-2):
         for i, (r, p) in enumerate(rows):
@@ -366,8 +379,7 @@ def test_attention_decode(Hq, Hkv, hd, page, window):
         out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
         po = torch.empty(len(rows) * Hq * splits * hd, dtype=torch.float32, device=DEV)
         pml = torch.empty(len(rows) * Hq * splits * 2, dtype=torch.float32, device=DEV)
-        kernels.attention_decode(qd, out, *common, None, len(rows), Hq, Hkv, hd, page, scale, window,
-                                 splits, po, pml, slot, pos)
+        run(qd, out, None, len(rows), splits, po, pml, slot, pos)
         if splits > 1:
             kernels.attention_merge(po, pml, out, None, len(rows), Hq, hd, splits)
         check(rows, out, q)
@@ -387,5 +399,5 @@ def test_attention_decode(Hq, Hkv, hd, page, window):
         out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
         items = torch.tensor([(p0 - start, n, 4, p0) for p0, n in sizes], dtype=torch.int32,
                              device=DEV).reshape(-1)
-        kernels.attention_decode(qd, out, *common, items, len(sizes), Hq, Hkv, hd, page, scale, window)
+        run(qd, out, items, len(sizes))
         check(rows, out, q)
