@@ -275,7 +275,8 @@ def main() -> int:
             points[f"decode_b{b}"] = b / (pms / 1e3)
 
     line = {
-        "metric": "decode tok/s (Qwen3-8B sizes, random bf16 weights)", "value": value,
+        "metric": "decode tok/s at batch %d (Qwen3-8B sizes, random bf16 weights); prefill and "
+                  "batch 1 / 64 in `prefill` and `points`" % args.batch, "value": value,
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: uniform random token ids, seeded random weights", "impl": "ours",
@@ -287,7 +288,11 @@ def main() -> int:
                    "context": args.context, "page_size": args.page_size,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 15 GB)",
                    "peaks": pk["source"]},
-        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 3 * 4 * args.batch + 64,
+        # per step the engine copies one int32 array (header, token id, position, request slot
+        # and wanted row per request, block-table changes) and the sampler's options
+        # (10 float32 words per row capacity of 64), and reads back one token id per request
+        "e2e": {"value": e2e, "unit": "tokens/s",
+                "h2d_bytes_per_step": 4 * (16 + 4 * ((args.batch + 3) // 4 * 4)) + 4 * 10 * 64,
                 "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": launches, "clocks": clk, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
