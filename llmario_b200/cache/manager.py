@@ -278,6 +278,8 @@ class CacheManager:
             if need[gi] > g.pool.free:
                 self.counters["refusals"] += 1
                 raise CacheFull(gi, need[gi], g.pool.free)
+        if not any(need):
+            return
         for rid, n in growth:
             r = self._req(rid)
             for gi, k in enumerate(self.pages_needed(rid, n)):

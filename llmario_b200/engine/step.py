@@ -108,14 +108,14 @@ class ModelRunner:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request!r}: an entry needs at least one token")
-            for t in e.tokens:
-                if not 0 <= int(t) < vocab:
-                    raise StepError(f"request {e.request!r}: token {t} outside the vocabulary "
-                                    f"of {vocab}")
-            for w in e.want:
-                if not 0 <= int(w) < n:
-                    raise StepError(f"request {e.request!r}: wanted place {w} outside its "
-                                    f"{n} tokens")
+            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                bad = [t for t in e.tokens if not 0 <= int(t) < vocab][0]
+                raise StepError(f"request {e.request!r}: token {bad} outside the vocabulary "
+                                f"of {vocab}")
+            if e.want and (min(e.want) < 0 or max(e.want) >= n):
+                bad = [w for w in e.want if not 0 <= int(w) < n][0]
+                raise StepError(f"request {e.request!r}: wanted place {bad} outside its "
+                                f"{n} tokens")
             rows += n
         new = [e.request for e in entries if not self.cache.has(e.request)]
         if len(new) > self.cache.free_slots():
@@ -160,20 +160,30 @@ class ModelRunner:
 
         # ---- one array of integers for the whole step
         segments: List[Segment] = []
-        tokens = np.empty(rows, dtype=np.int32)
-        pos = np.empty(rows, dtype=np.int32)
-        slot = np.empty(rows, dtype=np.int32)
         want: List[int] = []
-        r0 = 0
-        for e in entries:
-            n = len(e.tokens)
-            s, p0 = cache.slot(e.request), cache.length(e.request)
-            tokens[r0:r0 + n] = np.asarray(e.tokens, dtype=np.int32)
-            pos[r0:r0 + n] = np.arange(p0, p0 + n, dtype=np.int32)
-            slot[r0:r0 + n] = s
-            want += [r0 + int(w) for w in e.want]
-            segments.append(Segment(e.request, s, r0, n, p0))
-            r0 += n
+        if rows == len(entries):      # single tokens only: no per-entry array work
+            reqs = [cache._req(e.request) for e in entries]
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=rows)
+            pos = np.fromiter((r.length for r in reqs), dtype=np.int32, count=rows)
+            slot = np.fromiter((r.slot for r in reqs), dtype=np.int32, count=rows)
+            for i, (e, r) in enumerate(zip(entries, reqs)):
+                if e.want:
+                    want.append(i)
+                segments.append(Segment(e.request, r.slot, i, 1, r.length))
+        else:
+            tokens = np.empty(rows, dtype=np.int32)
+            pos = np.empty(rows, dtype=np.int32)
+            slot = np.empty(rows, dtype=np.int32)
+            r0 = 0
+            for e in entries:
+                n = len(e.tokens)
+                s, p0 = cache.slot(e.request), cache.length(e.request)
+                tokens[r0:r0 + n] = np.asarray(e.tokens, dtype=np.int32)
+                pos[r0:r0 + n] = np.arange(p0, p0 + n, dtype=np.int32)
+                slot[r0:r0 + n] = s
+                want += [r0 + int(w) for w in e.want]
+                segments.append(Segment(e.request, s, r0, n, p0))
+                r0 += n
         updates = cache.take_table_updates()
         n_want = len(want)
         max_pos = int(pos.max())

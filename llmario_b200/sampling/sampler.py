@@ -91,17 +91,28 @@ class DeviceSampler:
                     tri += (r, tok, cnt)
         self._buffers(rows, len(tri) // 3)
         c = self._cap
-        h = self._host.numpy()
-        f = h[:6 * c].reshape(6, c)
-        k = h[6 * c:7 * c].view(np.int32)
-        u = h[8 * c:10 * c].view(np.float64)
-        for r, s in enumerate(samplers):
-            p = s.params
-            f[0, r], f[1, r], f[2, r] = p.temperature, p.top_p, p.min_p
-            f[3, r], f[4, r], f[5, r] = p.repeat_penalty, p.frequency_penalty, p.presence_penalty
-            k[r] = p.top_k
-            u[r] = s.next_uniform()
-        self._dev.copy_(self._host, non_blocking=True)
+        # the options of a row change only when the set of requests changes; the uniforms
+        # change with every draw (greedy rows draw nothing)
+        key = [id(s) for s in samplers]
+        same = key == getattr(self, "_last_key", None) and c == getattr(self, "_last_cap", 0)
+        any_draw = any(not s.params.greedy for s in samplers)
+        if not same or any_draw:
+            h = self._host.numpy()
+            if not same:
+                f = h[:6 * c].reshape(6, c)
+                k = h[6 * c:7 * c].view(np.int32)
+                for r, s in enumerate(samplers):
+                    p = s.params
+                    f[0, r], f[1, r], f[2, r] = p.temperature, p.top_p, p.min_p
+                    f[3, r], f[4, r], f[5, r] = (p.repeat_penalty, p.frequency_penalty,
+                                                 p.presence_penalty)
+                    k[r] = p.top_k
+            u = h[8 * c:10 * c].view(np.float64)
+            for r, s in enumerate(samplers):
+                u[r] = s.next_uniform()
+            self._dev.copy_(self._host, non_blocking=True)
+            self._last_key, self._last_cap = key, c
+            self._last_objs = list(samplers)     # keeps the ids above from being reused
         d = self._dev
         if tri:
             n = len(tri) // 3
