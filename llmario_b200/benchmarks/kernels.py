@@ -111,14 +111,19 @@ def cmd_prefill_attention(a) -> None:
     storage, table = _paged(1, T, Hkv, hd, page)
     q = torch.randn(T, Hq * hd, device=DEV).bfloat16()
     out = torch.empty_like(q)
-    cap = max(1, 64 // (Hq // Hkv))
+    cap = max(1, (64 if a.mma_sync else 128) // (Hq // Hkv))
     items = torch.tensor([[s, min(cap, T - s), 0, s] for s in range(0, T, cap)],
                          dtype=torch.int32, device=DEV).reshape(-1)
     n = items.numel() // 4
-    fn = lambda: kernels.attention_flash(q, out, storage[0, 0, 0], storage[0, 0, 1],
-                                         storage.stride(0), table, items, n, 64, Hq, Hkv, hd,
-                                         page, hd ** -0.5, None)
+    if a.mma_sync:
+        fn = lambda: kernels.attention_flash(q, out, storage[0, 0, 0], storage[0, 0, 1],
+                                             storage.stride(0), table, items, n, 64, Hq, Hkv, hd,
+                                             page, hd ** -0.5, None)
+    else:
+        fn = lambda: kernels.attention_tcgen05(q, out, storage, 0, table, items, n, Hq, Hkv, hd,
+                                               page, hd ** -0.5, None)
     ms = timed(fn, a.reps, None)
+    kernels.check_tc_status(DEV)
     flops = 2.0 * T * T * Hq * hd          # causal: half of QK^T and PV
     print(f"prefill attention tokens={T} heads={Hq}/{Hkv} hd={hd}: {ms * 1e3:.1f} us, "
           f"{flops / ms / 1e9:.1f} TFLOP/s (causal flops)")
@@ -147,6 +152,8 @@ def main(argv=None) -> int:
     d.set_defaults(fn=cmd_attention)
     p = sub.add_parser("prefill-attention")
     p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--mma-sync", action="store_true",
+                   help="the mma.sync kernel of attention_flash.cu instead of the tcgen05 kernel")
     p.set_defaults(fn=cmd_prefill_attention)
     for s in (g, d, p):
         s.add_argument("--reps", type=int, default=20)

@@ -1,0 +1,421 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores (bfloat16).
+//
+// A CTA takes one work item (up to 128 / G consecutive tokens of one request, G = query heads per
+// KV head) and one KV head.  Its 128 rows are (token, head of the group) pairs, one TMEM lane
+// each.  Keys are walked in tiles of 128 aligned to absolute positions:
+//
+//   warp 0     TMA: the Q tile once (a 3-D box over [token][head][dim]), then K and V tiles of the
+//              pages named by the block table (head-major pages: 2 x 2 loads of page_size rows per
+//              page) into a ring of two stages
+//   warp 1     one lane issues  S = Q K^T  (A and B from shared memory, K-major) into one of two
+//              TMEM score buffers, and  O += P V  (A = P from TMEM, B = V from shared memory,
+//              N-major); the order is S0, S1, PV0, S2, PV1, ... so the products of one tile
+//              overlap the softmax of the other
+//   warps 2-5  softmax, one thread per row: two passes over the row's scores with tcgen05.ld
+//              (maximum, then exponentials and sum in 32-bit), P written back as bfloat16 over
+//              the score buffer with tcgen05.st; the output accumulator is rescaled only when a
+//              row's maximum has grown by more than 2^8 since the scale in use (the exact
+//              normalisation happens once at the end); finally O / l is written
+//
+// TMEM: scores 2 x 128 columns, output head_dim columns.  Every mbarrier wait is bounded.
+// Head sizes 64 and 128; G must divide 128; page_size must divide 128.
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int ROWS = 128;          // rows of a CTA (TMEM lanes)
+constexpr int KT = 128;            // keys per tile
+constexpr int KV_STAGES = 2;
+
+struct Item { int row_start, tokens, slot, pos_start; };
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: A is 128 x 16 bf16 in TMEM (K-major), B as the descriptor says
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// N-major (MN-major) operand: 64-element runs of 128 bytes along N, eight K rows per 1024 bytes,
+// `lbo` bytes from one 64-element run to the next
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t lbo) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* v) {
+  tmem_st16(taddr, v);
+  tmem_st16(taddr + 16, v + 16);
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+struct alignas(1024) AttnStorage {
+  uint8_t q[ROWS * HD * 2];                    // [HD/64 halves][128 rows][128 bytes]
+  uint8_t k[KV_STAGES][KT * HD * 2];           // [HD/64 halves][128 keys][128 bytes]
+  uint8_t v[KV_STAGES][KT * HD * 2];
+  uint64_t q_full;
+  uint64_t kv_full[KV_STAGES];
+  uint64_t kv_empty[KV_STAGES];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_done;
+  uint32_t tmem_base;
+  int dead;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(192, 1) attention_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+    bf16* __restrict__ out, const int* __restrict__ block_table, int table_stride,
+    const int* __restrict__ items, int Hq, int Hkv, int page_size, long long rows_per_page, int k_row0,
+    int v_row0, float scale_log2, int window, int* __restrict__ status) {
+  constexpr int HALVES = HD / 64;
+  constexpr uint32_t TILE_BYTES = KT * HD * 2;
+  constexpr uint32_t S_COLS = KT;              // fp32 scores of a tile
+  constexpr uint32_t O_COL = 2 * S_COLS;       // first column of the output accumulator
+  // S = Q K^T: M 128, N 128, A and B K-major;  O += P V: M 128, N HD, B N-major
+  constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KT >> 3) << 17) |
+                               ((uint32_t)(ROWS >> 4) << 24);
+  constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
+                               ((uint32_t)(ROWS >> 4) << 24);
+  extern __shared__ uint8_t raw[];
+  auto& sm = *reinterpret_cast<AttnStorage<HD>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const Item it = reinterpret_cast<const Item*>(items)[blockIdx.x];
+  const int kvh = blockIdx.y;
+  const int G = Hq / Hkv;
+  const int hi = it.pos_start + it.tokens - 1;
+  const int lo = (window > 0 && it.pos_start + 1 > window) ? it.pos_start + 1 - window : 0;
+  const int tile_first = lo / KT;
+  const int ntiles = hi / KT - tile_first + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&sm.kv_full[s], 1);
+      mbar_init(&sm.kv_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.s_full[b], 1);
+      mbar_init(&sm.p_full[b], 4);           // one arrival per softmax warp
+    }
+    mbar_init(&sm.o_done, 1);
+    sm.dead = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // values of rows that no load fills meet zero weights: they must be finite
+  for (int i = threadIdx.x; i < (int)(KV_STAGES * TILE_BYTES / 16); i += blockDim.x)
+    reinterpret_cast<uint4*>(&sm.v[0][0])[i] = make_uint4(0, 0, 0, 0);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  // only now may the next kernel of the stream be scheduled: every CTA of this one that is
+  // running holds its tensor memory, so a successor that also allocates some cannot starve it
+  pdl_trigger();
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------------ loads
+    pdl_wait();
+    mbar_expect_tx(&sm.q_full, ROWS * HD * 2);
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h)
+      tma_load_3d(sm.q + h * ROWS * 128, &map_q, h * 64, kvh * G, it.row_start, &sm.q_full);
+    const int* table = block_table + (size_t)it.slot * table_stride;
+    bool ok = true;
+    int issued = 0;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int s = j % KV_STAGES;
+      ok = mbar_wait(&sm.kv_empty[s], (uint32_t)((j / KV_STAGES) & 1) ^ 1);
+      if (!ok) { atomicExch(status, 5); sm.dead = 1; break; }
+      const int base = (tile_first + j) * KT;
+      uint32_t bytes = 0;
+      for (int p = base; p < base + KT; p += page_size)
+        if (p <= hi && p + page_size - 1 >= lo) bytes += (uint32_t)page_size * HD * 2 * 2;
+      mbar_expect_tx(&sm.kv_full[s], bytes);
+      for (int p = base; p < base + KT; p += page_size) {
+        if (p > hi || p + page_size - 1 < lo) continue;      // no key of the item in this page
+        const long long row = (long long)table[p / page_size] * rows_per_page + (long long)kvh * page_size;
+        const int dst = (p - base) * 128;
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+          tma_load_2d(sm.k[s] + h * KT * 128 + dst, &map_kv, h * 64, (int)(row + k_row0), &sm.kv_full[s]);
+          tma_load_2d(sm.v[s] + h * KT * 128 + dst, &map_kv, h * 64, (int)(row + v_row0), &sm.kv_full[s]);
+        }
+      }
+      issued = j + 1;
+    }
+    if (!ok)
+      for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
+        mbar_wait(&sm.kv_full[j % KV_STAGES], (uint32_t)((j / KV_STAGES) & 1));
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    bool ok = mbar_wait(&sm.q_full, 0);
+    if (!ok) { atomicExch(status, 6); sm.dead = 1; }
+    for (int j = 0; j <= ntiles && ok; ++j) {
+      if (j < ntiles) {
+        const int s = j % KV_STAGES, b = j & 1;
+        ok = mbar_wait(&sm.kv_full[s], (uint32_t)((j / KV_STAGES) & 1));
+        if (!ok) { atomicExch(status, 6); sm.dead = 1; break; }
+        tc_fence_after();
+        const uint32_t acc = tmem + (uint32_t)b * S_COLS;
+#pragma unroll
+        for (int ks = 0; ks < HD / UMMA_K; ++ks) {
+          const uint32_t off = (uint32_t)(ks / 4) * (ROWS * 128) + (uint32_t)(ks % 4) * 32;
+          const uint32_t offk = (uint32_t)(ks / 4) * (KT * 128) + (uint32_t)(ks % 4) * 32;
+          tc_mma(acc, smem_desc(smem_u32(sm.q) + off), smem_desc(smem_u32(sm.k[s]) + offk), IDESC_S,
+                 ks > 0 ? 1u : 0u);
+        }
+        tc_commit(&sm.s_full[b]);
+      }
+      if (j >= 1) {
+        const int i = j - 1, s = i % KV_STAGES, b = i & 1;
+        ok = mbar_wait(&sm.p_full[b], (uint32_t)((i >> 1) & 1));
+        if (!ok) { atomicExch(status, 6); sm.dead = 1; break; }
+        tc_fence_after();
+        const uint32_t p_addr = tmem + (uint32_t)b * S_COLS;     // P over the first KT/2 columns
+#pragma unroll
+        for (int ks = 0; ks < KT / UMMA_K; ++ks)
+          tc_mma_ts(tmem + O_COL, p_addr + (uint32_t)ks * (UMMA_K / 2),
+                    smem_desc_mn(smem_u32(sm.v[s]) + (uint32_t)ks * UMMA_K * 128, KT * 128), IDESC_O,
+                    (i > 0 || ks > 0) ? 1u : 0u);
+        tc_commit(&sm.kv_empty[s]);
+        tc_commit(&sm.o_done);
+      }
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------------ softmax, one row per thread
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+    const int tok = row / G, head = kvh * G + row % G;
+    const bool rvalid = tok < it.tokens;
+    const int rpos = it.pos_start + tok;
+    const int rlo = (window > 0 && rpos + 1 > window) ? rpos + 1 - window : 0;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    pdl_wait();
+    for (int j = 0; j < ntiles; ++j) {
+      const int b = j & 1;
+      ok = mbar_wait(&sm.s_full[b], (uint32_t)((j >> 1) & 1));
+      if (!ok) { if (lane == 0) atomicExch(status, 7); sm.dead = 1; }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (sm.dead) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_addr = tmem + lane_base + (uint32_t)b * S_COLS;
+      const int base = (tile_first + j) * KT;
+      // keys of this tile the row sees: columns c_lo .. c_hi
+      const int c_hi = rvalid ? min(KT - 1, rpos - base) : -1;
+      const int c_lo = max(0, rlo - base);
+      // ---- pass 1: the row's maximum
+      float m_tile = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < KT; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(s_addr + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c + i >= c_lo && c + i <= c_hi) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+      }
+      m_tile *= scale_log2;
+      // the scale in use is replaced only when the maximum has grown by more than 2^8
+      const bool grow = m_tile > m_used + 8.0f;
+      float factor = 1.f;
+      if (grow) {
+        factor = m_used == -INFINITY ? 0.f : ex2(m_used - m_tile);
+        m_used = m_tile;
+        l *= factor;
+      }
+      if (j > 0) {
+        // the product P V of the tile before must be complete before O is touched
+        bool done = mbar_wait(&sm.o_done, (uint32_t)((j - 1) & 1));
+        if (!done) { if (lane == 0) atomicExch(status, 7); sm.dead = 1; }
+        if (__any_sync(0xffffffffu, grow)) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem + lane_base + O_COL + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
+            tmem_st32(tmem + lane_base + O_COL + c, v);
+          }
+          tmem_st_wait();
+        }
+      }
+      // ---- pass 2: exponentials, sum, P as bfloat16 over the scores
+      const float muse = m_used == -INFINITY ? 0.f : m_used;
+#pragma unroll 1
+      for (int c = 0; c < KT; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(s_addr + c, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const bool v0 = c + i >= c_lo && c + i <= c_hi, v1 = c + i + 1 >= c_lo && c + i + 1 <= c_hi;
+          const float p0 = v0 ? ex2(fmaf(__uint_as_float(v[i]), scale_log2, -muse)) : 0.f;
+          const float p1 = v1 ? ex2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -muse)) : 0.f;
+          l += p0 + p1;
+          pk[i >> 1] = pack2(p0, p1);
+        }
+        tmem_st16(s_addr + (c >> 1), pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.p_full[b]);
+    }
+    if (ok) {
+      // ---- the last product, then O / l
+      bool done = mbar_wait(&sm.o_done, (uint32_t)((ntiles - 1) & 1));
+      if (!done) { if (lane == 0) atomicExch(status, 7); }
+      done = __all_sync(0xffffffffu, done);
+      if (done) {
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        bf16* dst = out + ((size_t)(it.row_start + tok) * Hq + head) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + O_COL + c, v);
+          tmem_ld_wait();
+          if (rvalid) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack2(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+              w.y = pack2(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+              w.z = pack2(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+              w.w = pack2(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c + i) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// q [rows][Hq][hd] bf16 as a 3-D tensor, box of 64 dims x G heads x (128 / G) tokens
+bool q_tensor_map(const void* q, int rows, int Hq, int hd, int G, CUtensorMap* out) {
+  static EncodeTiled enc = nullptr;
+  if (!enc) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult r;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &r) != cudaSuccess ||
+        r != cudaDriverEntryPointSuccess)
+      return false;
+    enc = reinterpret_cast<EncodeTiled>(p);
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)Hq, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)Hq * hd * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(ROWS / G)};
+  cuuint32_t elem[3] = {1, 1, 1};
+  return enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mkv, bf16* out, const int* table, int table_stride,
+           const int* items, int n_items, int Hq, int Hkv, int page_size, long long rows_per_page, int k_row0,
+           int v_row0, float scale, int window, int* status, cudaStream_t s) {
+  auto kernel = attention_tcgen05_kernel<HD>;
+  constexpr int smem = (int)sizeof(AttnStorage<HD>) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(n_items, Hkv);
+  return launch_pdl(kernel, grid, 192, smem, s, mq, mkv, out, table, table_stride, items, Hq, Hkv, page_size,
+                    rows_per_page, k_row0, v_row0, scale * 1.4426950408889634f, window, status);
+}
+}  // namespace
+
+// q, out: [rows][Hq * hd] bfloat16; storage: the group's cache [n_pages][n_slots][2][Hkv][page_size][hd];
+// items: n_items x (first row, tokens <= 128 / (Hq / Hkv), request slot, first position).
+LLM_EXPORT int llm_attention_tcgen05(const void* q, void* out, int rows, const void* storage,
+                                     long long n_pages, int n_slots, int slot, const int* block_table,
+                                     int table_stride, const int* items, int n_items, int Hq, int Hkv,
+                                     int hd, int page_size, float scale, int window, int* status,
+                                     cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv) return LLM_ERR_ARGUMENT;
+  const int G = Hq / Hkv;
+  if ((hd != 64 && hd != 128) || ROWS % G || KT % page_size || page_size > KT) return LLM_ERR_UNSUPPORTED;
+  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)storage) & 15) return LLM_ERR_UNSUPPORTED;
+  const long long rows_per_page = (long long)n_slots * 2 * Hkv * page_size;
+  const long long total_rows = n_pages * rows_per_page;
+  if (total_rows >= (1LL << 31)) return LLM_ERR_UNSUPPORTED;
+  CUtensorMap mq, mkv;
+  if (!q_tensor_map(q, rows, Hq, hd, G, &mq)) return LLM_ERR_UNSUPPORTED;
+  if (!llm_tensor_map(storage, total_rows, hd, hd, page_size, 64, 0, &mkv)) return LLM_ERR_UNSUPPORTED;
+  const int k_row0 = (slot * 2 + 0) * Hkv * page_size, v_row0 = (slot * 2 + 1) * Hkv * page_size;
+  if (hd == 128)
+    return launch<128>(mq, mkv, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size,
+                       rows_per_page, k_row0, v_row0, scale, window, status, stream);
+  return launch<64>(mq, mkv, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size,
+                    rows_per_page, k_row0, v_row0, scale, window, status, stream);
+}

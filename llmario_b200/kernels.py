@@ -54,6 +54,7 @@ def _declare(l) -> None:
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
         "llm_attention_decode_tma": [P, P, P, P, P, L, I, I, P, I, P, P, P, I, I, I, I, I, F, I,
                                      I, P, P],
+        "llm_attention_tcgen05": [P, P, I, P, L, I, I, P, I, P, I, I, I, I, I, F, I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
     for name, args in sigs.items():
@@ -421,6 +422,29 @@ def attention_decode_tma(q: torch.Tensor, out: torch.Tensor, storage: torch.Tens
         f"attention_decode_tma (head_dim {head_dim})")
 
 
+def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, storage: torch.Tensor, slot: int,
+                      block_table: torch.Tensor, items: torch.Tensor, n_items: int,
+                      num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                      scale: float, window: Optional[int]) -> None:
+    """Attention of prompt portions on tcgen05: items of at most 128 / (heads per KV head)
+    tokens; scores and output accumulate in tensor memory."""
+    _cuda(q, out, storage, block_table, items)
+    assert q.dtype == torch.bfloat16 and storage.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous() and storage.is_contiguous()
+    _check(lib().llm_attention_tcgen05(
+        _ptr(q), _ptr(out), q.shape[0], _ptr(storage), storage.shape[0], storage.shape[1], slot,
+        _ptr(block_table), block_table.stride(0), _ptr(items), n_items, num_heads, num_kv_heads,
+        head_dim, page_size, float(scale), int(window or 0), _ptr(tc_status(q.device)),
+        _stream()), f"attention_tcgen05 (head_dim {head_dim})")
+
+
+def prefill_tcgen05_ok(view, head_dim: int, group: int) -> bool:
+    st = getattr(view, "storage", None)
+    ps = view.page_size
+    return (st is not None and st.is_contiguous() and head_dim in (64, 128) and 128 % group == 0
+            and 128 % ps == 0 and st.numel() // head_dim < (1 << 31))
+
+
 def decode_tma_ok(view, head_dim: int) -> bool:
     st = getattr(view, "storage", None)
     ps = view.page_size
@@ -454,7 +478,8 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
                           ctx.row_slot, ctx.row_pos, num_heads, num_kv_heads, head_dim,
                           view.page_size, scale, window)
         return
-    plan = ctx.attention_plan(group)
+    tc = prefill_tcgen05_ok(view, head_dim, group)
+    plan = ctx.attention_plan(group, (128 if tc else 64) // group)
     common = (view.k, view.v, view.page_stride, view.block_table)
     if plan.n_small:
         reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
@@ -480,6 +505,10 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
         if splits > 1:
             attention_merge(part_o, part_ml, out, plan.small_rows, plan.n_small, num_heads,
                             head_dim, splits)
-    if plan.n_large:
+    if plan.n_large and tc:
+        attention_tcgen05(q, out, view.storage, view.slot, view.block_table, plan.large,
+                          plan.n_large, num_heads, num_kv_heads, head_dim, view.page_size, scale,
+                          window)
+    elif plan.n_large:
         attention_flash(q, out, *common, plan.large, plan.n_large, 64, num_heads, num_kv_heads,
                         head_dim, view.page_size, scale, window)

@@ -126,22 +126,22 @@ class StepContext:
     fresh_slots: Sequence[int] = ()   # request slots opened since the last step
     max_pos: int = 0               # largest position in this step
 
-    plans: Dict[int, AttentionPlan] = field(default_factory=dict)
+    plans: Dict[Any, AttentionPlan] = field(default_factory=dict)
     shared: Dict[Any, Any] = field(default_factory=dict)   # what parts compute once per step
 
     def buffer(self, name: str, shape: Sequence[int], dtype: Optional[torch.dtype] = None
                ) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype or self.dtype)
 
-    def attention_plan(self, group: int) -> AttentionPlan:
+    def attention_plan(self, group: int, large_cap: Optional[int] = None) -> AttentionPlan:
         """Work items for attention kernels whose CTAs hold ``group`` query heads per token:
         small items have at most 8 (token, head) pairs (16 for a group above 8), large ones at
-        most 64."""
-        plan = self.plans.get(group)
+        most ``large_cap`` tokens (default: 64 pairs)."""
+        large_cap = max(1, large_cap or 64 // group)
+        plan = self.plans.get((group, large_cap))
         if plan is not None:
             return plan
         small_cap = max(1, (8 if group <= 8 else 16) // group)
-        large_cap = max(1, 64 // group)
         if all(s.rows == 1 for s in self.segments):
             plan = AttentionPlan(n_small=self.rows, small_single=True)   # rows describe themselves
         else:
@@ -162,7 +162,7 @@ class StepContext:
                 plan.small_rows = dev[4 * (len(small) + len(large)):]
             if large:
                 plan.large = dev[4 * len(small):4 * (len(small) + len(large))]
-        self.plans[group] = plan
+        self.plans[(group, large_cap)] = plan
         return plan
 
 

@@ -401,3 +401,42 @@ def test_attention_decode(Hq, Hkv, hd, page, window, tma):
                              device=DEV).reshape(-1)
         run(qd, out, items, len(sizes))
         check(rows, out, q)
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (4, 4, 64, 8, 70),
+                                                   (16, 2, 128, 32, None), (2, 2, 64, 64, None),
+                                                   (32, 8, 128, 16, 300)])
+def test_attention_tcgen05(Hq, Hkv, hd, page, window):
+    """The tcgen05 kernel for prompt portions: items of up to 128 / G tokens at the end of a long
+    request (several key tiles, the diagonal tile, a window's edge), short items, and an item at
+    the very start of a request."""
+    from llmario_b200 import kernels
+    dtype = torch.bfloat16
+    G = Hq // Hkv
+    cap = 128 // G
+    lengths = [700, 40, 129]
+    storage, table, ks, vs = paged_setup(lengths, page, Hkv, hd, dtype)
+    scale = 1 / math.sqrt(hd)
+    g = torch.Generator().manual_seed(7)
+    # rows: the last 2.5 items of request 0, all of request 1 (from position 0), a 3-token tail
+    spans = [(0, 700 - int(2.5 * cap), 700), (1, 0, 40), (2, 126, 129)]
+    rows, items = [], []
+    for r, a, b in spans:
+        at = a
+        while at < b:
+            n = min(cap, b - at)
+            items.append((len(rows), n, r, at))
+            rows += [(r, p) for p in range(at, at + n)]
+            at += n
+    q = torch.randn(len(rows), Hq, hd, generator=g).to(dtype)
+    qd = q.reshape(len(rows), -1).to(DEV).contiguous()
+    out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
+    dev_items = torch.tensor(items, dtype=torch.int32, device=DEV).reshape(-1)
+    kernels.attention_tcgen05(qd, out, storage, 1, table, dev_items, len(items), Hq, Hkv, hd, page,
+                              scale, window)
+    kernels.check_tc_status(DEV)
+    for i, (r, p) in enumerate(rows):
+        ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
+        got = out[i].reshape(Hq, hd).double().cpu()
+        assert torch.isfinite(got).all(), (i, r, p)
+        assert (got - ref).abs().max() <= 2e-2, (i, r, p, (got - ref).abs().max())
