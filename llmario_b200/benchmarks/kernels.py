@@ -120,7 +120,8 @@ def cmd_prefill_attention(a) -> None:
                                              storage.stride(0), table, items, n, 64, Hq, Hkv, hd,
                                              page, hd ** -0.5, None)
     else:
-        fn = lambda: kernels.attention_tcgen05(q, out, storage, 0, table, items, n, Hq, Hkv, hd,
+        fn = lambda: kernels.attention_tcgen05(q, out, storage[0, 0, 0], storage[0, 0, 1],
+                                               storage.stride(0), table, items, n, Hq, Hkv, hd,
                                                page, hd ** -0.5, None)
     ms = timed(fn, a.reps, None)
     kernels.check_tc_status(DEV)

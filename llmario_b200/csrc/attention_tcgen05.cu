@@ -4,28 +4,30 @@
 // KV head) and one KV head.  Its 128 rows are (token, head of the group) pairs, one TMEM lane
 // each.  Keys are walked in tiles of 128 aligned to absolute positions:
 //
-//   warp 0     TMA: the Q tile once (a 3-D box over [token][head][dim]), then K and V tiles of the
-//              pages named by the block table (head-major pages: 2 x 2 loads of page_size rows per
-//              page) into a ring of two stages
+//   warp 0     TMA: the Q tile once (a 3-D box over [token][head][dim])
+//   warps 6-9  K and V tiles of the pages named by the block table, as 16-byte cp.async copies
+//              into the 128-byte-swizzled layout the tensor core reads, a ring of three stages
+//              (TMA tile loads of one page are too small: the unit spends ~140 cycles per load
+//              whatever its size, which capped this kernel at a third of its present rate)
 //   warp 1     one lane issues  S = Q K^T  (A and B from shared memory, K-major) into one of two
 //              TMEM score buffers, and  O += P V  (A = P from TMEM, B = V from shared memory,
 //              N-major); the order is S0, S1, PV0, S2, PV1, ... so the products of one tile
 //              overlap the softmax of the other
-//   warps 2-5  softmax, one thread per row: two passes over the row's scores with tcgen05.ld
-//              (maximum, then exponentials and sum in 32-bit), P written back as bfloat16 over
+//   warps 2-5  softmax, one thread per row: the row's 128 scores come into registers with one
+//              tcgen05.ld round trip (maximum, exponentials and sum in 32-bit), P goes back as bfloat16 over
 //              the score buffer with tcgen05.st; the output accumulator is rescaled only when a
 //              row's maximum has grown by more than 2^8 since the scale in use (the exact
 //              normalisation happens once at the end); finally O / l is written
 //
 // TMEM: scores 2 x 128 columns, output head_dim columns.  Every mbarrier wait is bounded.
-// Head sizes 64 and 128; G must divide 128; page_size must divide 128.
+// Head sizes 64 and 128; G must divide 128; any page size.
 #include "tcgen05.cuh"
 
 namespace {
 
 constexpr int ROWS = 128;          // rows of a CTA (TMEM lanes)
 constexpr int KT = 128;            // keys per tile
-constexpr int KV_STAGES = 2;
+constexpr int KV_STAGES = 3;
 
 struct Item { int row_start, tokens, slot, pos_start; };
 
@@ -104,13 +106,12 @@ struct alignas(1024) AttnStorage {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1) attention_tcgen05_kernel(
-    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
-    bf16* __restrict__ out, const int* __restrict__ block_table, int table_stride,
-    const int* __restrict__ items, int Hq, int Hkv, int page_size, long long rows_per_page, int k_row0,
-    int v_row0, float scale_log2, int window, int* __restrict__ status) {
+__global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap map_q, const bf16* __restrict__ k_cache,
+    const bf16* __restrict__ v_cache, long long page_stride, bf16* __restrict__ out, const int* __restrict__ block_table, int table_stride,
+    const int* __restrict__ items, int Hq, int Hkv, int page_size, float scale_log2, int window,
+    int* __restrict__ status) {
   constexpr int HALVES = HD / 64;
-  constexpr uint32_t TILE_BYTES = KT * HD * 2;
   constexpr uint32_t S_COLS = KT;              // fp32 scores of a tile
   constexpr uint32_t O_COL = 2 * S_COLS;       // first column of the output accumulator
   // S = Q K^T: M 128, N 128, A and B K-major;  O += P V: M 128, N HD, B N-major
@@ -132,7 +133,7 @@ __global__ void __launch_bounds__(192, 1) attention_tcgen05_kernel(
   if (threadIdx.x == 0) {
     mbar_init(&sm.q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&sm.kv_full[s], 1);
+      mbar_init(&sm.kv_full[s], 128);        // one arrival per producer thread
       mbar_init(&sm.kv_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -143,10 +144,6 @@ __global__ void __launch_bounds__(192, 1) attention_tcgen05_kernel(
     sm.dead = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // values of rows that no load fills meet zero weights: they must be finite
-  for (int i = threadIdx.x; i < (int)(KV_STAGES * TILE_BYTES / 16); i += blockDim.x)
-    reinterpret_cast<uint4*>(&sm.v[0][0])[i] = make_uint4(0, 0, 0, 0);
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
                  "r"(512u)
@@ -161,40 +158,85 @@ __global__ void __launch_bounds__(192, 1) attention_tcgen05_kernel(
   // running holds its tensor memory, so a successor that also allocates some cannot starve it
   pdl_trigger();
 
-  if (warp == 0 && lane == 0) {
-    // ------------------------------------------------------------------ loads
-    pdl_wait();
-    mbar_expect_tx(&sm.q_full, ROWS * HD * 2);
+  if (warp == 0) {
+    // ------------------------------------------------------------------ the Q tile
+    if (lane == 0) {
+      pdl_wait();
+      mbar_expect_tx(&sm.q_full, ROWS * HD * 2);
 #pragma unroll
-    for (int h = 0; h < HALVES; ++h)
-      tma_load_3d(sm.q + h * ROWS * 128, &map_q, h * 64, kvh * G, it.row_start, &sm.q_full);
+      for (int h = 0; h < HALVES; ++h)
+        tma_load_3d(sm.q + h * ROWS * 128, &map_q, h * 64, kvh * G, it.row_start, &sm.q_full);
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ K and V tiles
+    // Thread p of the 128 copies the 16-byte piece (p % CPR) of rows (p / CPR), + 128 / CPR, ...
+    // of every tile: its column and its row inside a group of eight never change, so the
+    // swizzled destination advances by a constant.  Rows without a key are zero-filled.
+    constexpr int CPR = HD / 8;                 // 16-byte pieces per row
+    constexpr int RPP = 128 / CPR;              // rows per pass of the 128 threads
+    const int p = threadIdx.x - 192;
+    const int c = p % CPR, r0 = p / CPR;
+    const uint32_t dst0 = (uint32_t)(c >> 3) * (KT * 128) + (uint32_t)r0 * 128 + (uint32_t)(((c & 7) ^ (r0 & 7)) << 4);
     const int* table = block_table + (size_t)it.slot * table_stride;
+    pdl_wait();
     bool ok = true;
-    int issued = 0;
-    for (int j = 0; j < ntiles && ok; ++j) {
+    for (int j = 0; j < ntiles; ++j) {
       const int s = j % KV_STAGES;
       ok = mbar_wait(&sm.kv_empty[s], (uint32_t)((j / KV_STAGES) & 1) ^ 1);
-      if (!ok) { atomicExch(status, 5); sm.dead = 1; break; }
+      if (!ok) { if (p == 0) atomicExch(status, 5); sm.dead = 1; break; }
       const int base = (tile_first + j) * KT;
-      uint32_t bytes = 0;
-      for (int p = base; p < base + KT; p += page_size)
-        if (p <= hi && p + page_size - 1 >= lo) bytes += (uint32_t)page_size * HD * 2 * 2;
-      mbar_expect_tx(&sm.kv_full[s], bytes);
-      for (int p = base; p < base + KT; p += page_size) {
-        if (p > hi || p + page_size - 1 < lo) continue;      // no key of the item in this page
-        const long long row = (long long)table[p / page_size] * rows_per_page + (long long)kvh * page_size;
-        const int dst = (p - base) * 128;
+      const uint32_t kdst = smem_u32(sm.k[s]) + dst0, vdst = smem_u32(sm.v[s]) + dst0;
+      auto copy_row = [&](int r, long long off, bool live) {
+        const int bytes = live ? 16 : 0;
+        const uint32_t d = (uint32_t)(r - r0) * 128;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kdst + d), "l"(k_cache + off), "r"(bytes)
+                     : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vdst + d), "l"(v_cache + off), "r"(bytes)
+                     : "memory");
+      };
+      if (page_size >= 16 && (page_size & (page_size - 1)) == 0) {
+        // pages of a power of two of at least 16 positions: the block-table entries of the
+        // tile (at most eight) are fetched together, then every copy is one address addition
+        const int rows_here = page_size >= KT ? KT : page_size;      // rows of the tile in one page
+        const int ppt = KT / rows_here;
+        const int p_first = base / page_size, inp0 = base % page_size;
+        long long pb[8];
 #pragma unroll
-        for (int h = 0; h < HALVES; ++h) {
-          tma_load_2d(sm.k[s] + h * KT * 128 + dst, &map_kv, h * 64, (int)(row + k_row0), &sm.kv_full[s]);
-          tma_load_2d(sm.v[s] + h * KT * 128 + dst, &map_kv, h * 64, (int)(row + v_row0), &sm.kv_full[s]);
+        for (int g = 0; g < 8; ++g) {
+          const int pos0 = base + g * rows_here;
+          const bool live_page = g < ppt && pos0 <= hi && pos0 + rows_here - 1 >= lo;
+          pb[g] = live_page ? (long long)table[p_first + g] * page_stride : -1;
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          if (g >= ppt) break;
+          for (int rr = r0; rr < rows_here; rr += RPP) {
+            const int r = g * rows_here + rr, pos = base + r;
+            const bool live = pb[g] >= 0 && pos >= lo && pos <= hi;
+            copy_row(r, live ? pb[g] + ((long long)kvh * page_size + inp0 + rr) * HD + c * 8 : 0, live);
+          }
+        }
+      } else {
+        for (int r = r0; r < KT; r += RPP) {      // RPP is a multiple of 8 or divides it: r & 7 == r0 & 7
+          const int pos = base + r;
+          const bool live = pos >= lo && pos <= hi;
+          long long off = 0;
+          if (live)
+            off = (long long)table[pos / page_size] * page_stride +
+                  ((long long)kvh * page_size + pos % page_size) * HD + c * 8;
+          copy_row(r, off, live);
         }
       }
-      issued = j + 1;
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (j > 0) {      // the tile before this one has landed: hand it to the tensor core
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(&sm.kv_full[(j - 1) % KV_STAGES]);
+      }
     }
-    if (!ok)
-      for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
-        mbar_wait(&sm.kv_full[j % KV_STAGES], (uint32_t)((j / KV_STAGES) & 1));
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (ok && ntiles > 0) mbar_arrive(&sm.kv_full[(ntiles - 1) % KV_STAGES]);
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------------------------ MMA issuer
     bool ok = mbar_wait(&sm.q_full, 0);
@@ -230,7 +272,7 @@ __global__ void __launch_bounds__(192, 1) attention_tcgen05_kernel(
         tc_commit(&sm.o_done);
       }
     }
-  } else if (warp >= 2) {
+  } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------------ softmax, one row per thread
     const int q4 = warp & 3;
     const int row = q4 * 32 + lane;
@@ -254,17 +296,29 @@ __global__ void __launch_bounds__(192, 1) attention_tcgen05_kernel(
       // keys of this tile the row sees: columns c_lo .. c_hi
       const int c_hi = rvalid ? min(KT - 1, rpos - base) : -1;
       const int c_lo = max(0, rlo - base);
-      // ---- pass 1: the row's maximum
-      float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < KT; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + c, v);
-        tmem_ld_wait();
+      // a tile that every row of the CTA sees completely needs no per-key tests
+      const bool interior = it.tokens * G >= ROWS && base + KT - 1 <= it.pos_start &&
+                            (window <= 0 || base >= hi + 1 - window);
+      // ---- the whole row of scores into registers (one round trip to tensor memory)
+      uint32_t v[KT];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c + i >= c_lo && c + i <= c_hi) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+      for (int c = 0; c < KT; c += 32) tmem_ld32(s_addr + c, v + c);
+      tmem_ld_wait();
+      if (!interior) {
+#pragma unroll
+        for (int i = 0; i < KT; ++i)
+          if (i < c_lo || i > c_hi) v[i] = 0xff800000u;      // -inf: the key is not visible
       }
+      // four independent chains, so that a comparison does not wait for the one before it
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < KT; i += 4) {
+        mx[0] = fmaxf(mx[0], __uint_as_float(v[i]));
+        mx[1] = fmaxf(mx[1], __uint_as_float(v[i + 1]));
+        mx[2] = fmaxf(mx[2], __uint_as_float(v[i + 2]));
+        mx[3] = fmaxf(mx[3], __uint_as_float(v[i + 3]));
+      }
+      float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       m_tile *= scale_log2;
       // the scale in use is replaced only when the maximum has grown by more than 2^8
       const bool grow = m_tile > m_used + 8.0f;
@@ -292,22 +346,27 @@ __global__ void __launch_bounds__(192, 1) attention_tcgen05_kernel(
           tmem_st_wait();
         }
       }
-      // ---- pass 2: exponentials, sum, P as bfloat16 over the scores
+      // ---- exponentials, sum, P as bfloat16 over the scores (masked scores are -inf: weight 0)
       const float muse = m_used == -INFINITY ? 0.f : m_used;
-#pragma unroll 1
+      // all exponentials first (independent of one another), then the sums, then the packing
+#pragma unroll
+      for (int i = 0; i < KT; ++i)
+        v[i] = __float_as_uint(ex2(fmaf(__uint_as_float(v[i]), scale_log2, -muse)));
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < KT; i += 4) {
+        sum[0] += __uint_as_float(v[i]);
+        sum[1] += __uint_as_float(v[i + 1]);
+        sum[2] += __uint_as_float(v[i + 2]);
+        sum[3] += __uint_as_float(v[i + 3]);
+      }
+      l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+#pragma unroll
       for (int c = 0; c < KT; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + c, v);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const bool v0 = c + i >= c_lo && c + i <= c_hi, v1 = c + i + 1 >= c_lo && c + i + 1 <= c_hi;
-          const float p0 = v0 ? ex2(fmaf(__uint_as_float(v[i]), scale_log2, -muse)) : 0.f;
-          const float p1 = v1 ? ex2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -muse)) : 0.f;
-          l += p0 + p1;
-          pk[i >> 1] = pack2(p0, p1);
-        }
+        for (int i = 0; i < 32; i += 2)
+          pk[i >> 1] = pack2(__uint_as_float(v[c + i]), __uint_as_float(v[c + i + 1]));
         tmem_st16(s_addr + (c >> 1), pk);
       }
       tmem_st_wait();
@@ -377,9 +436,9 @@ bool q_tensor_map(const void* q, int rows, int Hq, int hd, int G, CUtensorMap* o
 }
 
 template <int HD>
-int launch(const CUtensorMap& mq, const CUtensorMap& mkv, bf16* out, const int* table, int table_stride,
-           const int* items, int n_items, int Hq, int Hkv, int page_size, long long rows_per_page, int k_row0,
-           int v_row0, float scale, int window, int* status, cudaStream_t s) {
+int launch(const CUtensorMap& mq, const bf16* kc, const bf16* vc, long long page_stride, bf16* out,
+           const int* table, int table_stride, const int* items, int n_items, int Hq, int Hkv, int page_size,
+           float scale, int window, int* status, cudaStream_t s) {
   auto kernel = attention_tcgen05_kernel<HD>;
   constexpr int smem = (int)sizeof(AttnStorage<HD>) + 1024;
   static bool configured = false;
@@ -389,33 +448,30 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, bf16* out, const int* 
     configured = true;
   }
   dim3 grid(n_items, Hkv);
-  return launch_pdl(kernel, grid, 192, smem, s, mq, mkv, out, table, table_stride, items, Hq, Hkv, page_size,
-                    rows_per_page, k_row0, v_row0, scale * 1.4426950408889634f, window, status);
+  return launch_pdl(kernel, grid, 320, smem, s, mq, kc, vc, page_stride, out, table, table_stride, items, Hq, Hkv,
+                    page_size, scale * 1.4426950408889634f, window, status);
 }
 }  // namespace
 
-// q, out: [rows][Hq * hd] bfloat16; storage: the group's cache [n_pages][n_slots][2][Hkv][page_size][hd];
+// q, out: [rows][Hq * hd] bfloat16; k_cache / v_cache: this layer call's K and V planes of page 0 in a
+// cache [page][...][kv head][position][head dim] with `page_stride` elements from page to page;
 // items: n_items x (first row, tokens <= 128 / (Hq / Hkv), request slot, first position).
-LLM_EXPORT int llm_attention_tcgen05(const void* q, void* out, int rows, const void* storage,
-                                     long long n_pages, int n_slots, int slot, const int* block_table,
+LLM_EXPORT int llm_attention_tcgen05(const void* q, void* out, int rows, const void* k_cache,
+                                     const void* v_cache, long long page_stride, const int* block_table,
                                      int table_stride, const int* items, int n_items, int Hq, int Hkv,
                                      int hd, int page_size, float scale, int window, int* status,
                                      cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv) return LLM_ERR_ARGUMENT;
   const int G = Hq / Hkv;
-  if ((hd != 64 && hd != 128) || ROWS % G || KT % page_size || page_size > KT) return LLM_ERR_UNSUPPORTED;
-  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)storage) & 15) return LLM_ERR_UNSUPPORTED;
-  const long long rows_per_page = (long long)n_slots * 2 * Hkv * page_size;
-  const long long total_rows = n_pages * rows_per_page;
-  if (total_rows >= (1LL << 31)) return LLM_ERR_UNSUPPORTED;
-  CUtensorMap mq, mkv;
+  if ((hd != 64 && hd != 128) || ROWS % G) return LLM_ERR_UNSUPPORTED;
+  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return LLM_ERR_UNSUPPORTED;
+  if ((page_stride * 2) % 16) return LLM_ERR_UNSUPPORTED;
+  CUtensorMap mq;
   if (!q_tensor_map(q, rows, Hq, hd, G, &mq)) return LLM_ERR_UNSUPPORTED;
-  if (!llm_tensor_map(storage, total_rows, hd, hd, page_size, 64, 0, &mkv)) return LLM_ERR_UNSUPPORTED;
-  const int k_row0 = (slot * 2 + 0) * Hkv * page_size, v_row0 = (slot * 2 + 1) * Hkv * page_size;
   if (hd == 128)
-    return launch<128>(mq, mkv, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size,
-                       rows_per_page, k_row0, v_row0, scale, window, status, stream);
-  return launch<64>(mq, mkv, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size,
-                    rows_per_page, k_row0, v_row0, scale, window, status, stream);
+    return launch<128>(mq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, (bf16*)out, block_table,
+                       table_stride, items, n_items, Hq, Hkv, page_size, scale, window, status, stream);
+  return launch<64>(mq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, (bf16*)out, block_table,
+                    table_stride, items, n_items, Hq, Hkv, page_size, scale, window, status, stream);
 }

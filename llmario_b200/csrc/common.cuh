@@ -63,8 +63,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
-// Bounded wait for the phase with the given parity: polls without blocking and gives up after
-// WAIT_CYCLES clock cycles (about two seconds).  Returns false when the bound ran out.
+// Bounded wait for the phase with the given parity.  mbarrier.try_wait parks the thread until the
+// phase completes or a hardware time limit passes, so waking up costs no polling delay; the loop
+// around it gives up after WAIT_CYCLES clock cycles (about two seconds).  Returns false then.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t addr = smem_u32(bar);
   long long start = 0;
@@ -72,17 +73,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
-    if (i == 64) start = clock64();
-    if (i > 64) {
-      __nanosleep(32);
-      if ((i & 255u) == 0 && clock64() - start > WAIT_CYCLES) return false;
-    }
+    if (i == 0) start = clock64();
+    else if (clock64() - start > WAIT_CYCLES) return false;
   }
 }
 static inline int launch_status() { return (int)cudaGetLastError(); }

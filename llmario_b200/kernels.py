@@ -54,7 +54,7 @@ def _declare(l) -> None:
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
         "llm_attention_decode_tma": [P, P, P, P, P, L, I, I, P, I, P, P, P, I, I, I, I, I, F, I,
                                      I, P, P],
-        "llm_attention_tcgen05": [P, P, I, P, L, I, I, P, I, P, I, I, I, I, I, F, I, P, P],
+        "llm_attention_tcgen05": [P, P, I, P, P, L, P, I, P, I, I, I, I, I, F, I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
     for name, args in sigs.items():
@@ -272,7 +272,7 @@ def tc_status(device) -> torch.Tensor:
     """The device word in which the tensor-core kernels record a wait that gave up."""
     key = torch.device(device).index or 0
     if key not in _tc_status:
-        _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _tc_status[key] = torch.zeros(4, dtype=torch.int32, device=device)
     return _tc_status[key]
 
 
@@ -280,7 +280,7 @@ def check_tc_status(device) -> None:
     """Raise if a tensor-core kernel gave up waiting (synchronises the device)."""
     st = _tc_status.get(torch.device(device).index or 0)
     if st is not None:
-        code = int(st.item())
+        code = int(st[0].item())
         if code:
             st.zero_()
             raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (role {code})")
@@ -422,27 +422,24 @@ def attention_decode_tma(q: torch.Tensor, out: torch.Tensor, storage: torch.Tens
         f"attention_decode_tma (head_dim {head_dim})")
 
 
-def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, storage: torch.Tensor, slot: int,
-                      block_table: torch.Tensor, items: torch.Tensor, n_items: int,
-                      num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
-                      scale: float, window: Optional[int]) -> None:
+def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
+                      v_cache: torch.Tensor, page_stride: int, block_table: torch.Tensor,
+                      items: torch.Tensor, n_items: int, num_heads: int, num_kv_heads: int,
+                      head_dim: int, page_size: int, scale: float, window: Optional[int]) -> None:
     """Attention of prompt portions on tcgen05: items of at most 128 / (heads per KV head)
     tokens; scores and output accumulate in tensor memory."""
-    _cuda(q, out, storage, block_table, items)
-    assert q.dtype == torch.bfloat16 and storage.dtype == torch.bfloat16
-    assert q.is_contiguous() and out.is_contiguous() and storage.is_contiguous()
+    _cuda(q, out, k_cache, v_cache, block_table, items)
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous()
     _check(lib().llm_attention_tcgen05(
-        _ptr(q), _ptr(out), q.shape[0], _ptr(storage), storage.shape[0], storage.shape[1], slot,
+        _ptr(q), _ptr(out), q.shape[0], _ptr(k_cache), _ptr(v_cache), page_stride,
         _ptr(block_table), block_table.stride(0), _ptr(items), n_items, num_heads, num_kv_heads,
         head_dim, page_size, float(scale), int(window or 0), _ptr(tc_status(q.device)),
         _stream()), f"attention_tcgen05 (head_dim {head_dim})")
 
 
 def prefill_tcgen05_ok(view, head_dim: int, group: int) -> bool:
-    st = getattr(view, "storage", None)
-    ps = view.page_size
-    return (st is not None and st.is_contiguous() and head_dim in (64, 128) and 128 % group == 0
-            and 128 % ps == 0 and st.numel() // head_dim < (1 << 31))
+    return head_dim in (64, 128) and 128 % group == 0 and (view.page_stride * 2) % 16 == 0
 
 
 def decode_tma_ok(view, head_dim: int) -> bool:
@@ -506,9 +503,8 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
             attention_merge(part_o, part_ml, out, plan.small_rows, plan.n_small, num_heads,
                             head_dim, splits)
     if plan.n_large and tc:
-        attention_tcgen05(q, out, view.storage, view.slot, view.block_table, plan.large,
-                          plan.n_large, num_heads, num_kv_heads, head_dim, view.page_size, scale,
-                          window)
+        attention_tcgen05(q, out, *common, plan.large, plan.n_large, num_heads, num_kv_heads,
+                          head_dim, view.page_size, scale, window)
     elif plan.n_large:
         attention_flash(q, out, *common, plan.large, plan.n_large, 64, num_heads, num_kv_heads,
                         head_dim, view.page_size, scale, window)
