@@ -29,7 +29,7 @@ def plain_greedy(name, dtype, prompt, n, margin):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_greedy_generation_through_the_entry_point(name, dtype):
     from llmario_b200 import Engine, SamplingParams
     eng = Engine(model_dir(name, dtype), dtype=dtype, page_size=TINY[name]["page_size"],

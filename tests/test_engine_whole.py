@@ -19,7 +19,7 @@ def make_runner(name, dtype, n_tokens=512, max_requests=8):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_prompts(name, dtype):
     from llmario_b200.engine import StepEntry
 

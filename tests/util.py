@@ -15,7 +15,7 @@ from plain import qwen3_plain as P
 
 # Tiny configurations that differ in every size and option.  A and B are the two of the
 # benchmark description; C adds a window on some layers, a group of three and sizes that are
-# not even a multiple of four.
+# not even a multiple of four; D runs the tensor-core attention kernels.
 TINY = {
     "A": dict(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
               head_dim=16, intermediate_size=128, vocab_size=256, rope_theta=10000.0,
@@ -31,6 +31,13 @@ TINY = {
               use_sliding_window=True, sliding_window=21,
               layer_types=["full_attention", "sliding_attention", "sliding_attention",
                            "full_attention"], page_size=16, seed=2),
+    # D has the head size and group of the tensor-core attention kernels (tcgen05 for portions,
+    # TMA-fed decode) and a window that is longer than a key tile on one layer
+    "D": dict(num_hidden_layers=2, hidden_size=128, num_attention_heads=8, num_key_value_heads=2,
+              head_dim=64, intermediate_size=192, vocab_size=500, rope_theta=1000000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=2048,
+              use_sliding_window=True, sliding_window=150,
+              layer_types=["full_attention", "sliding_attention"], page_size=16, seed=4),
 }
 
 
