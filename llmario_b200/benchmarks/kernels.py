@@ -45,7 +45,7 @@ def cmd_gemm(a) -> None:
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
     if a.mode == "gated":
         out = torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
-        fn = lambda: kernels.gemm_tcgen05(x, w, out, 2, N // 2, bn=a.tile)
+        fn = lambda: kernels.gemm_tcgen05(x, w, out, 3 if a.interleaved else 2, N // 2, bn=a.tile)
     elif a.mode == "accumulate":
         out = torch.zeros(T, N, dtype=torch.float32, device=DEV)
         fn = lambda: kernels.gemm_tcgen05(x, w, out, 1, bn=a.tile, splits=a.splits)
@@ -141,6 +141,8 @@ def main(argv=None) -> int:
     g.add_argument("--tile", type=int, default=None)
     g.add_argument("--splits", type=int, default=1)
     g.add_argument("--f32", action="store_true")
+    g.add_argument("--interleaved", action="store_true",
+                   help="gated mode: the matrix holds alternating blocks of 16 gate and 16 up rows")
     g.set_defaults(fn=cmd_gemm)
     d = sub.add_parser("attention")
     d.add_argument("--batch", type=int, default=8)

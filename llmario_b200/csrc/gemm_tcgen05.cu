@@ -51,7 +51,7 @@ template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     const __grid_constant__ CUtensorMap map_c, int tma_out, TC* __restrict__ C, int ldc, int T, int N,
-    int K, int half, int* __restrict__ status) {
+    int K, int half, int interleaved, int* __restrict__ status) {
   extern __shared__ uint8_t raw[];
   auto& sm = *reinterpret_cast<SharedStorage<BN, STAGES>*>(
       (reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -97,7 +97,10 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
         const int s = i % STAGES;
         mbar_expect_tx(&sm.full[s], STAGE_BYTES);
         const int k = (kb_begin + i) * TILE_K;
-        if (EPI == EPI_GATED) {
+        if (EPI == EPI_GATED && interleaved) {
+          // the matrix is stored with 16 gate rows, their 16 up rows, the next 16 gate rows, ...
+          tma_load_2d(sm.a[s], &map_w, k, 2 * n0, &sm.full[s]);
+        } else if (EPI == EPI_GATED) {
           // 16 gate rows, their 16 up rows, the next 16 gate rows, ...: every 32-lane quarter of
           // the accumulator then holds gate and up of the same 16 features
 #pragma unroll
@@ -307,7 +310,7 @@ namespace {
 
 template <int BN, int STAGES, int EPI, typename TC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K, int half,
-           int splits, int* status, cudaStream_t stream) {
+           int splits, int interleaved, int* status, cudaStream_t stream) {
   // the output goes through TMA when its rows are 16-byte multiples on a 16-byte aligned base
   CUtensorMap mc = mw;
   int tma_out = 0;
@@ -326,17 +329,18 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, 
   const int feat = EPI == EPI_GATED ? 64 : TILE_M;
   const int limit = EPI == EPI_GATED ? half : N;
   dim3 grid((limit + feat - 1) / feat, (T + BN - 1) / BN, splits);
-  return launch_pdl(kernel, grid, 192, smem, stream, mw, mx, mc, tma_out, C, ldc, T, N, K, half, status);
+  return launch_pdl(kernel, grid, 192, smem, stream, mw, mx, mc, tma_out, C, ldc, T, N, K, half, interleaved,
+                    status);
 }
 
 template <int EPI, typename TC>
 int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K,
-             int half, int splits, int* status, cudaStream_t stream) {
+             int half, int splits, int interleaved, int* status, cudaStream_t stream) {
   switch (bn) {
-    case 16: return launch<16, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
-    case 32: return launch<32, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
-    case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
-    case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, status, stream);
+    case 16: return launch<16, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
+    case 32: return launch<32, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
+    case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
+    case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
   }
   return LLM_ERR_UNSUPPORTED;
 }
@@ -346,6 +350,7 @@ int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ld
 //   mode 0: C = X W^T (c_dtype bf16 or f32; with splits > 1: f32, zeroed here first)
 //   mode 1: C += X W^T (f32)
 //   mode 2: W = [gate; up] with `half` rows each, C[t][n] = silu(gate) * up, n < half
+//   mode 3: the same with W stored interleaved: 16 gate rows, their 16 up rows, 16 gate rows, ...
 // bn: token tile, one of 16, 32, 64, 128, or 256 for the persistent kernel.  status: device int, set non-zero when a wait
 // inside the kernel gave up.
 LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
@@ -378,21 +383,21 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dty
       if (z != 0) return z;
     }
     if (c_dtype == LLM_F32)
-      return dispatch<EPI_STORE, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, splits, status, stream);
+      return dispatch<EPI_STORE, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, splits, 0, status, stream);
     if (c_dtype == LLM_BF16 && splits == 1)
-      return dispatch<EPI_STORE, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, half, 1, status, stream);
+      return dispatch<EPI_STORE, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, half, 1, mode == 3, status, stream);
     return LLM_ERR_UNSUPPORTED;
   }
   if (mode == 1) {
     if (c_dtype != LLM_F32) return LLM_ERR_UNSUPPORTED;
-    return dispatch<EPI_ACCUM, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, splits, status, stream);
+    return dispatch<EPI_ACCUM, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, splits, 0, status, stream);
   }
-  if (mode == 2) {
-    if (N != 2 * half) return LLM_ERR_ARGUMENT;
+  if (mode == 2 || mode == 3) {
+    if (N != 2 * half || (mode == 3 && half % 16)) return LLM_ERR_ARGUMENT;
     if (c_dtype == LLM_BF16)
-      return dispatch<EPI_GATED, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, half, 1, status, stream);
+      return dispatch<EPI_GATED, bf16>(bn, mw, mx, (bf16*)C, ldc, T, N, K, half, 1, mode == 3, status, stream);
     if (c_dtype == LLM_F32)
-      return dispatch<EPI_GATED, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, 1, status, stream);
+      return dispatch<EPI_GATED, float>(bn, mw, mx, (float*)C, ldc, T, N, K, half, 1, mode == 3, status, stream);
     return LLM_ERR_UNSUPPORTED;
   }
   return LLM_ERR_ARGUMENT;

@@ -40,8 +40,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 template <int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-    const __grid_constant__ CUtensorMap map_c, int T, int N, int K, int half, int m_tiles, int n_tiles,
-    int* __restrict__ status) {
+    const __grid_constant__ CUtensorMap map_c, int T, int N, int K, int half, int interleaved, int m_tiles,
+    int n_tiles, int* __restrict__ status) {
   constexpr int FEAT = EPI == EPI_GATED ? 64 : TILE_M;
   extern __shared__ uint8_t raw[];
   auto& sm = *reinterpret_cast<PersistentStorage<STAGES, FEAT, TC>*>(
@@ -82,7 +82,9 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(
     // ------------------------------------------------------------------ producer
     auto load_w = [&](int s, int n0, int k) {
       mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-      if (EPI == EPI_GATED) {
+      if (EPI == EPI_GATED && interleaved) {
+        tma_load_2d(sm.a[s], &map_w, k, 2 * n0, &sm.full[s]);     // 16 gate rows, 16 up rows, ... as stored
+      } else if (EPI == EPI_GATED) {
 #pragma unroll
         for (int b = 0; b < 8; ++b)
           tma_load_2d(sm.a[s] + b * 16 * TILE_K * 2, &map_w, k, ((b & 1) ? half : 0) + n0 + (b >> 1) * 16,
@@ -220,7 +222,7 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(
 
 template <int STAGES, int EPI, typename TC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, int T, int N, int K, int half,
-           int sm_count, int* status, cudaStream_t stream) {
+           int interleaved, int sm_count, int* status, cudaStream_t stream) {
   constexpr int FEAT = EPI == EPI_GATED ? 64 : TILE_M;
   auto kernel = gemm_persistent_kernel<STAGES, EPI, TC>;
   constexpr int smem = (int)sizeof(PersistentStorage<STAGES, FEAT, TC>) + 1024;
@@ -233,7 +235,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, 
   const int limit = EPI == EPI_GATED ? half : N;
   const int m_tiles = (limit + FEAT - 1) / FEAT, n_tiles = (T + BN - 1) / BN;
   const int grid = m_tiles * n_tiles < sm_count ? m_tiles * n_tiles : sm_count;
-  return launch_pdl(kernel, grid, 192, smem, stream, mw, mx, mc, T, N, K, half, m_tiles, n_tiles, status);
+  return launch_pdl(kernel, grid, 192, smem, stream, mw, mx, mc, T, N, K, half, interleaved, m_tiles, n_tiles,
+                    status);
 }
 }  // namespace
 
@@ -254,17 +257,17 @@ int llm_gemm_tcgen05_persistent(const void* X, const void* W, void* C, int c_dty
   CUtensorMap mw, mx, mc;
   if (!llm_tensor_map(W, N, K, ldw, mode == 2 ? 16 : TILE_M, TILE_K, 0, &mw)) return LLM_ERR_UNSUPPORTED;
   if (!llm_tensor_map(X, T, K, lda, BN, TILE_K, 0, &mx)) return LLM_ERR_UNSUPPORTED;
-  const int out_cols = mode == 2 ? half : N;
-  if (!llm_tensor_map(C, T, out_cols, ldc, CH, mode == 2 ? 64 : TILE_M, c_dtype == LLM_F32 ? 2 : 1, &mc))
+  const int out_cols = mode >= 2 ? half : N;
+  if (!llm_tensor_map(C, T, out_cols, ldc, CH, mode >= 2 ? 64 : TILE_M, c_dtype == LLM_F32 ? 2 : 1, &mc))
     return LLM_ERR_UNSUPPORTED;
   if (mode == 0) {
-    if (c_dtype == LLM_F32) return launch<4, EPI_STORE, float>(mw, mx, mc, T, N, K, half, sm_count, status, stream);
-    if (c_dtype == LLM_BF16) return launch<4, EPI_STORE, bf16>(mw, mx, mc, T, N, K, half, sm_count, status, stream);
+    if (c_dtype == LLM_F32) return launch<4, EPI_STORE, float>(mw, mx, mc, T, N, K, half, mode == 3, sm_count, status, stream);
+    if (c_dtype == LLM_BF16) return launch<4, EPI_STORE, bf16>(mw, mx, mc, T, N, K, half, mode == 3, sm_count, status, stream);
   } else if (mode == 1) {
-    if (c_dtype == LLM_F32) return launch<4, EPI_ACCUM, float>(mw, mx, mc, T, N, K, half, sm_count, status, stream);
-  } else if (mode == 2) {
-    if (c_dtype == LLM_BF16) return launch<4, EPI_GATED, bf16>(mw, mx, mc, T, N, K, half, sm_count, status, stream);
-    if (c_dtype == LLM_F32) return launch<4, EPI_GATED, float>(mw, mx, mc, T, N, K, half, sm_count, status, stream);
+    if (c_dtype == LLM_F32) return launch<4, EPI_ACCUM, float>(mw, mx, mc, T, N, K, half, mode == 3, sm_count, status, stream);
+  } else if (mode == 2 || mode == 3) {
+    if (c_dtype == LLM_BF16) return launch<4, EPI_GATED, bf16>(mw, mx, mc, T, N, K, half, mode == 3, sm_count, status, stream);
+    if (c_dtype == LLM_F32) return launch<4, EPI_GATED, float>(mw, mx, mc, T, N, K, half, mode == 3, sm_count, status, stream);
   }
   return LLM_ERR_UNSUPPORTED;
 }

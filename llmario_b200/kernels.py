@@ -305,7 +305,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
                  bn: Optional[int] = None, splits: int = 1) -> None:
     """Tensor-core product of bfloat16 operands.  mode 0: out = a w^T (bfloat16 or float32);
     1: out += a w^T (float32); 2: out = silu(a wg^T) * (a wu^T), w = [wg; wu] of ``half`` rows
-    each.  ``bn``: token tile (16..256); ``splits`` > 1 splits K and adds partial sums with
+    each; 3: the same with w stored as alternating blocks of 16 gate rows and 16 up rows.  ``bn``: token tile (16..256); ``splits`` > 1 splits K and adds partial sums with
     atomics (mode 0 then needs ``out`` float32 and zeroed)."""
     _cuda(a, w, out)
     T, K = a.shape
@@ -344,9 +344,22 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
         gemm_simt(a, w, out, accumulate)
 
 
-def gate_up_silu(ctx, h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> None:
-    """act = silu(h Wg^T) * (h Wu^T) for Wg, Wu stacked in ``w_gate_up`` ([2 ff][hidden])."""
+def gated_interleave_ok(gate: torch.Tensor, up: torch.Tensor) -> bool:
+    """Whether the gate and up matrices can be stored interleaved for the tensor-core product."""
+    return (gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and gate.is_cuda
+            and gate.shape == up.shape and gate.shape[0] % 16 == 0 and gate.shape[1] % 8 == 0)
+
+
+def gate_up_silu(ctx, h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor,
+                 interleaved: bool = False) -> None:
+    """act = silu(h Wg^T) * (h Wu^T) for Wg, Wu stacked in ``w_gate_up`` ([2 ff][hidden]):
+    gate rows then up rows, or (``interleaved``) alternating blocks of 16 gate and 16 up rows."""
     rows, ff = act.shape
+    if interleaved:
+        if not _tc_ok(h, w_gate_up):
+            raise KernelError("interleaved gate/up weights need the tensor-core product")
+        gemm_tcgen05(h, w_gate_up, act, 3, ff)
+        return
     if _tc_ok(h, w_gate_up):
         gemm_tcgen05(h, w_gate_up, act, 2, ff)
         return

@@ -17,14 +17,23 @@ class SwiGLU:
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
         self.hidden = int(spec["hidden_size"])
         self.ff = int(spec["intermediate_size"])
-        self.gate_up = Linear.stacked([tensor_of(spec, "gate", weights),
-                                       tensor_of(spec, "up", weights)])
+        gate, up = tensor_of(spec, "gate", weights), tensor_of(spec, "up", weights)
+        # For the tensor-core product gate and up rows are stored interleaved in blocks of 16
+        # (16 gate rows, their 16 up rows, ...): one 128-row weight tile then holds 64 features
+        # with gate and up of a feature in the same quarter of the accumulator.
+        self.interleaved = kernels.gated_interleave_ok(gate, up)
+        if self.interleaved:
+            ff, k = gate.shape
+            both = torch.stack([gate.view(ff // 16, 16, k), up.view(ff // 16, 16, k)], dim=1)
+            self.gate_up = Linear(both.reshape(2 * ff, k))
+        else:
+            self.gate_up = Linear.stacked([gate, up])
         self.down = Linear(tensor_of(spec, "down", weights))
 
     def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor) -> None:
         rows = ctx.rows
         act = ctx.buffer("ffn.act", (rows, self.ff))
-        kernels.gate_up_silu(ctx, h, self.gate_up.weight, act)
+        kernels.gate_up_silu(ctx, h, self.gate_up.weight, act, self.interleaved)
         self.down(act, x, accumulate=True)
 
 

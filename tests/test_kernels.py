@@ -260,7 +260,7 @@ def test_gemm_tcgen05(T, N, K):
 
 
 @pytest.mark.parametrize("T,ff,K", [(3, 64, 64), (20, 200, 136), (150, 1000, 512),
-                                    (600, 200, 136), (1030, 72, 64)])
+                                    (600, 200, 136), (1030, 72, 64), (40, 208, 72), (700, 1008, 256)])
 def test_gemm_tcgen05_gated(T, ff, K):
     from llmario_b200 import kernels
     a, w = rnd(T, K, dtype=torch.bfloat16), rnd(2 * ff, K, dtype=torch.bfloat16, seed=3, scale=0.3)
@@ -275,6 +275,12 @@ def test_gemm_tcgen05_gated(T, ff, K):
     actb = torch.empty(T, ff, dtype=torch.bfloat16, device=DEV)
     kernels.gemm_tcgen05(a, w, actb, 2, ff)
     assert (actb.double() - want).abs().max() <= 2 ** -8 * float(want.abs().max()) + tol
+    if ff % 16 == 0:      # the same matrices stored as alternating blocks of 16 gate and 16 up rows
+        wi = torch.stack([w[:ff].view(ff // 16, 16, K), w[ff:].view(ff // 16, 16, K)], 1).reshape(2 * ff, K)
+        act2 = torch.empty(T, ff, dtype=torch.float32, device=DEV)
+        kernels.gemm_tcgen05(a, wi.contiguous(), act2, 3, ff)
+        kernels.check_tc_status(DEV)
+        assert (act2.double() - want).abs().max() <= tol
 
 
 @pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (6, 3, 64, 8, 50),
