@@ -351,11 +351,12 @@ int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ld
 //   mode 1: C += X W^T (f32)
 //   mode 2: W = [gate; up] with `half` rows each, C[t][n] = silu(gate) * up, n < half
 //   mode 3: the same with W stored interleaved: 16 gate rows, their 16 up rows, 16 gate rows, ...
-// bn: token tile, one of 16, 32, 64, 128, or 256 for the persistent kernel.  status: device int, set non-zero when a wait
+// bn: token tile, one of 16, 32, 64, 128, or 256 for the persistent kernel.  out_is_zero: with
+// mode 0 and splits > 1 the caller guarantees that C holds zeros (it is not cleared here).  status: device int, set non-zero when a wait
 // inside the kernel gave up.
 LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
                                 int lda, int ldw, int ldc, int mode, int half, int bn, int splits,
-                                int* status, cudaStream_t stream) {
+                                int out_is_zero, int* status, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return LLM_ERR_UNSUPPORTED;
   if (((uintptr_t)X | (uintptr_t)W) & 15) return LLM_ERR_UNSUPPORTED;
@@ -378,7 +379,7 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dty
   if (!llm_tensor_map(W, N, K, ldw, mode == 2 ? 16 : TILE_M, TILE_K, 0, &mw)) return LLM_ERR_UNSUPPORTED;
   if (!llm_tensor_map(X, T, K, lda, bn, TILE_K, 0, &mx)) return LLM_ERR_UNSUPPORTED;
   if (mode == 0) {
-    if (c_dtype == LLM_F32 && splits > 1) {   // partial sums are added into zeros
+    if (c_dtype == LLM_F32 && splits > 1 && !(out_is_zero)) {   // partial sums are added into zeros
       const int z = llm_zero_f32((float*)C, T, N, ldc, stream);
       if (z != 0) return z;
     }

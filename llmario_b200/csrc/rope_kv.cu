@@ -3,6 +3,8 @@
 // the other), in one pass over the projection output.
 //   order per head: norm -> rotation -> store; values are stored as projected.
 // All arithmetic is 32-bit; rounding to the cache / activation type happens once, at the store.
+// On request the kernel clears the projection values it has consumed, so that the buffer is all
+// zeros again when the next split-K product adds its partial sums into it.
 #include "common.cuh"
 
 namespace {
@@ -16,7 +18,7 @@ __global__ void qk_norm_rope_store_kernel(
     const int* __restrict__ row_pos, const float* __restrict__ q_norm_w,
     const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
     const float2* __restrict__ cos_sin, float attn_factor, int rows, int Hq, int Hkv, int hd, int rot_dim,
-    int page_size, float eps, int has_kv, int use_norm) {
+    int page_size, float eps, int has_kv, int use_norm, int clear_proj) {
   pdl_trigger();
   pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -24,7 +26,7 @@ __global__ void qk_norm_rope_store_kernel(
   const int heads = Hq + (has_kv ? 2 * Hkv : 0);
   if (warp >= rows * heads) return;
   const int t = warp / heads, h = warp % heads;
-  const float* src = proj + (size_t)t * proj_stride + (size_t)h * hd;
+  float* src = const_cast<float*>(proj) + (size_t)t * proj_stride + (size_t)h * hd;
   const int pos = row_pos[t];
 
   TC* cache_dst = nullptr;
@@ -37,7 +39,10 @@ __global__ void qk_norm_rope_store_kernel(
     cache_dst = base + (size_t)page * page_stride + ((size_t)kvh * page_size + in_page) * hd;
   }
   if (h >= Hq + Hkv) {  // value: copy
-    for (int i = lane; i < hd; i += 32) cache_dst[i] = from_f32<TC>(src[i]);
+    for (int i = lane; i < hd; i += 32) {
+      cache_dst[i] = from_f32<TC>(src[i]);
+      if (clear_proj) src[i] = 0.f;
+    }
     return;
   }
   const bool is_q = h < Hq;
@@ -56,6 +61,7 @@ __global__ void qk_norm_rope_store_kernel(
   const float fpos = (float)pos;
   for (int i = lane; i < half; i += 32) {
     float a = src[i], b = src[i + half];
+    if (clear_proj) src[i] = src[i + half] = 0.f;     // the next split-K product adds into zeros
     if (use_norm) {
       a = a * scale * w[i];
       b = b * scale * w[i + half];
@@ -81,6 +87,7 @@ __global__ void qk_norm_rope_store_kernel(
   }
   for (int i = rot_dim + lane; i < hd; i += 32) {  // dimensions beyond the rotated ones
     float a = src[i];
+    if (clear_proj) src[i] = 0.f;
     if (use_norm) a = a * scale * w[i];
     if (is_q)
       q_out[(size_t)t * Hq * hd + (size_t)h * hd + i] = from_f32<TQ>(a);
@@ -95,7 +102,7 @@ LLM_EXPORT int llm_qk_norm_rope_store(
     long long page_stride, const int* block_table, int table_stride, const int* row_slot,
     const int* row_pos, const float* q_norm_w, const float* k_norm_w, const float* inv_freq,
     const float* cos_sin, float attn_factor, int rows, int Hq, int Hkv, int hd, int rot_dim,
-    int page_size, float eps, int has_kv, int use_norm, cudaStream_t stream) {
+    int page_size, float eps, int has_kv, int use_norm, int clear_proj, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (rot_dim > hd || (rot_dim & 1)) return LLM_ERR_ARGUMENT;
   const int heads = Hq + (has_kv ? 2 * Hkv : 0);
@@ -104,7 +111,7 @@ LLM_EXPORT int llm_qk_norm_rope_store(
   const int blocks = (int)((warps * 32 + threads - 1) / threads);
 #define ARGS proj, proj_stride, (TQ*)q_out, (TQ*)k_cache, (TQ*)v_cache, page_stride, block_table, \
   table_stride, row_slot, row_pos, q_norm_w, k_norm_w, inv_freq, (const float2*)cos_sin, attn_factor, \
-  rows, Hq, Hkv, hd, rot_dim, page_size, eps, has_kv, use_norm
+  rows, Hq, Hkv, hd, rot_dim, page_size, eps, has_kv, use_norm, clear_proj
   if (dtype == LLM_F32) {
     typedef float TQ;
     return launch_pdl(qk_norm_rope_store_kernel<float, float>, blocks, threads, 0, stream, ARGS);

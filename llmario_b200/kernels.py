@@ -43,12 +43,12 @@ def _declare(l) -> None:
         "llm_table_update_counted": [P, I, P, P, I, P],
         "llm_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, I, I, P],
         "llm_qk_norm_rope_store": [P, I, P, P, P, I, L, P, I, P, P, P, P, P, P, F, I, I, I, I, I,
-                                   I, F, I, I, P],
+                                   I, F, I, I, I, P],
         "llm_rope_table": [P, P, P, I, I, F, P],
         "llm_attention_generic": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P],
         "llm_sample": [P, L, I, I, P, P, P, P, P, P, P],
         "llm_gemv_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, P],
-        "llm_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
+        "llm_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "llm_attention_flash": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "llm_attention_merge": [P, P, P, P, I, I, I, I, P],
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
@@ -172,7 +172,7 @@ def qk_norm_rope_store(proj: torch.Tensor, q_out: torch.Tensor,
                        k_norm_w: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
                        attn_factor: float, num_heads: int, num_kv_heads: int, head_dim: int,
                        rot_dim: int, page_size: int, eps: float,
-                       cos_sin: Optional[torch.Tensor] = None) -> None:
+                       cos_sin: Optional[torch.Tensor] = None, clear_proj: bool = False) -> None:
     """Per-head norm, rotation and stores for the rows of ``proj`` (float32,
     [rows, (Hq + 2 Hkv) * hd], or [rows, Hq * hd] when no cache is given)."""
     _cuda(proj, q_out, k_cache, v_cache, block_table, row_slot, row_pos, q_norm_w, k_norm_w,
@@ -190,7 +190,7 @@ def qk_norm_rope_store(proj: torch.Tensor, q_out: torch.Tensor,
         _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq), _ptr(cos_sin), float(attn_factor), rows,
         num_heads,
         num_kv_heads, head_dim, rot_dim, page_size, float(eps), int(has_kv), int(use_norm),
-        _stream()), "qk_norm_rope_store")
+        int(clear_proj), _stream()), "qk_norm_rope_store")
 
 
 def rope_table(row_pos: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor,
@@ -302,7 +302,7 @@ def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, half: int = 0,
-                 bn: Optional[int] = None, splits: int = 1) -> None:
+                 bn: Optional[int] = None, splits: int = 1, out_is_zero: bool = False) -> None:
     """Tensor-core product of bfloat16 operands.  mode 0: out = a w^T (bfloat16 or float32);
     1: out += a w^T (float32); 2: out = silu(a wg^T) * (a wu^T), w = [wg; wu] of ``half`` rows
     each; 3: the same with w stored as alternating blocks of 16 gate rows and 16 up rows.  ``bn``: token tile (16..256); ``splits`` > 1 splits K and adds partial sums with
@@ -314,10 +314,14 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
     bn = bn or token_tile(T)
     _check(lib().llm_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(out), _dt(out), T, N, K, a.stride(0),
                                   w.stride(0), out.stride(0), mode, half, bn, splits,
-                                  _ptr(tc_status(a.device)), _stream()), "gemm_tcgen05")
+                                  int(out_is_zero), _ptr(tc_status(a.device)), _stream()),
+           "gemm_tcgen05")
 
 
 SM_COUNT = 148
+# Up to this many rows a caller may keep a split-K destination at zero itself (the kernel that
+# consumes it clears it) instead of having it cleared before every product.
+SPLIT_K_MAX_ROWS = 256
 
 
 def k_splits(rows: int, out_features: int, in_features: int) -> int:
@@ -329,15 +333,18 @@ def k_splits(rows: int, out_features: int, in_features: int) -> int:
     return max(1, min(16, round(2 * SM_COUNT / tiles), in_features // 256))
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+           out_is_zero: bool = False) -> None:
     """out (=|+=) a @ w.T with the fastest hand-written kernel that takes these operands:
     tensor cores for bfloat16 (they fetch weights ahead of the kernel before them), the
-    CUDA-core kernels for everything else (32-bit operands, unaligned sizes)."""
+    CUDA-core kernels for everything else (32-bit operands, unaligned sizes).
+    ``out_is_zero``: the caller guarantees that ``out`` holds zeros, so a split-K product need
+    not clear it first."""
     if _tc_ok(a, w):
         rows, k = a.shape
         n = w.shape[0]
         splits = k_splits(rows, n, k) if out.dtype == torch.float32 else 1
-        gemm_tcgen05(a, w, out, 1 if accumulate else 0, splits=splits)
+        gemm_tcgen05(a, w, out, 1 if accumulate else 0, splits=splits, out_is_zero=out_is_zero)
     elif _gemv_ok(a, w):
         gemv_bf16(a, w, out, 1 if accumulate else 0)
     else:

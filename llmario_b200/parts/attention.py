@@ -50,12 +50,14 @@ class Attention:
         view = ctx.cache.view(call.cache_entry)
         if view is None:
             raise RuntimeError(f"run-order entry {call.index}: attention needs a cache")
-        if call.writes_cache:
-            proj = ctx.buffer("attn.proj", (rows, self.q_width + 2 * self.kv_width), torch.float32)
-            self.qkv_proj(h, proj)
-        else:
-            proj = ctx.buffer("attn.proj", (rows, self.q_width), torch.float32)
-            self.q_proj(h, proj)
+        # With few rows the product is cut along K and its partial sums are added into the
+        # buffer.  That buffer is created as zeros and the kernel that consumes it clears what it
+        # read, which saves a clearing pass per layer.
+        width = self.q_width + (2 * self.kv_width if call.writes_cache else 0)
+        kept_zero = rows <= kernels.SPLIT_K_MAX_ROWS
+        proj = ctx.buffer("attn.proj.%s%d" % ("z" if kept_zero else "", width), (rows, width),
+                          torch.float32, zero=kept_zero)
+        (self.qkv_proj if call.writes_cache else self.q_proj)(h, proj, out_is_zero=kept_zero)
         q = ctx.buffer("attn.q", (rows, self.q_width))
         tables = self.position.rotary_tables() if self.position is not None else None
         if self.position is not None and tables is None:
@@ -71,7 +73,8 @@ class Attention:
             self.q_norm.weight if self.q_norm is not None else None,
             self.k_norm.weight if self.k_norm is not None else None,
             inv_freq, attn_factor, self.num_heads, self.num_kv_heads, self.head_dim, rot_dim,
-            view.page_size, self.q_norm.eps if self.q_norm is not None else 0.0, angles)
+            view.page_size, self.q_norm.eps if self.q_norm is not None else 0.0, angles,
+            clear_proj=kept_zero)
         out = ctx.buffer("attn.out", (rows, self.q_width))
         kernels.attention(ctx, q, out, view, self.num_heads, self.num_kv_heads, self.head_dim,
                           self.scale, self.window)

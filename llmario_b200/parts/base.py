@@ -82,14 +82,17 @@ class Workspace:
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self.generation = 0     # grows whenever a buffer moves: recorded launches are stale then
 
-    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype, zero: bool = False
+            ) -> torch.Tensor:
+        """``zero``: the buffer is created holding zeros (its users keep it that way)."""
         n = 1
         for d in shape:
             n *= int(d)
         key = (name, dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < n:
-            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            make = torch.zeros if zero else torch.empty
+            buf = make(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
             self.generation += 1
         return buf[:n].view(*shape)
@@ -129,9 +132,9 @@ class StepContext:
     plans: Dict[Any, AttentionPlan] = field(default_factory=dict)
     shared: Dict[Any, Any] = field(default_factory=dict)   # what parts compute once per step
 
-    def buffer(self, name: str, shape: Sequence[int], dtype: Optional[torch.dtype] = None
-               ) -> torch.Tensor:
-        return self.workspace.get(name, shape, dtype or self.dtype)
+    def buffer(self, name: str, shape: Sequence[int], dtype: Optional[torch.dtype] = None,
+               zero: bool = False) -> torch.Tensor:
+        return self.workspace.get(name, shape, dtype or self.dtype, zero)
 
     def attention_plan(self, group: int, large_cap: Optional[int] = None) -> AttentionPlan:
         """Work items for attention kernels whose CTAs hold ``group`` query heads per token:

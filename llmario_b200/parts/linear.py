@@ -26,6 +26,8 @@ class Linear:
         dt = torch.float32 if len(dtypes) > 1 else weights[0].dtype
         return cls(torch.cat([w.to(dt) for w in weights], dim=0))
 
-    def __call__(self, a: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
-        """out (=|+=) a @ W^T.  ``out`` is float32 when accumulating."""
-        kernels.linear(a, self.weight, out, accumulate)
+    def __call__(self, a: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+                 out_is_zero: bool = False) -> None:
+        """out (=|+=) a @ W^T.  ``out`` is float32 when accumulating.  ``out_is_zero``: the
+        caller guarantees ``out`` holds zeros (saves the clearing before a split-K product)."""
+        kernels.linear(a, self.weight, out, accumulate, out_is_zero)

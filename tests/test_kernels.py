@@ -224,6 +224,12 @@ def test_qk_norm_rope_store(dtype, Hq, Hkv, hd, page):
         assert (q_out[i].double().cpu().reshape(Hq, hd) - qr).abs().max() <= tol
         assert (storage[page_id, 0, 0, :, p % page].double().cpu() - kr).abs().max() <= tol
         assert (storage[page_id, 0, 1, :, p % page].double().cpu() - vr).abs().max() <= tol
+    # on request the consumed projection is cleared, for the split-K product that adds into it
+    q_again, used = torch.empty_like(q_out), proj.clone()
+    kernels.qk_norm_rope_store(used, q_again, storage[0, 0, 0], storage[0, 0, 1], storage.stride(0),
+                               table, slot, pos, qw, kw, inv_freq, 1.0, Hq, Hkv, hd, hd, page, eps,
+                               clear_proj=True)
+    assert torch.equal(q_again, q_out) and int((used != 0).sum()) == 0
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 128, 64), (16, 256, 128), (5, 200, 72), (40, 384, 4096),
@@ -238,6 +244,11 @@ def test_gemm_tcgen05(T, N, K):
     kernels.gemm_tcgen05(a, w, out, 0)
     kernels.check_tc_status(DEV)
     assert (out.double() - ref).abs().max() <= tol
+    if T <= 128 and K >= 256:     # split K into a destination the caller keeps at zero
+        zeros = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+        kernels.gemm_tcgen05(a, w, zeros, 0, splits=2, out_is_zero=True)
+        kernels.check_tc_status(DEV)
+        assert (zeros.double() - ref).abs().max() <= tol
     outb = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
     kernels.gemm_tcgen05(a, w, outb, 0)
     assert (outb.double() - ref).abs().max() <= 2 ** -8 * float(ref.abs().max()) + tol
