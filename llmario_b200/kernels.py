@@ -33,9 +33,11 @@ def lib():
     return _lib
 
 
-def _declare(l) -> None:
+def _signatures():
+    """Argument types of every exported entry point, as the C sources declare them (a test
+    compares the two): P pointer or stream, I int, L long long, F float."""
     P, I, L, F = c_void_p, c_int, c_longlong, c_float
-    sigs = {
+    return {
         "llm_embed": [P, P, I, P, I, I, I, P, P],
         "llm_rms_norm": [P, P, P, I, P, I, I, F, P],
         "llm_silu_mul": [P, P, I, I, I, P],
@@ -57,6 +59,10 @@ def _declare(l) -> None:
         "llm_attention_tcgen05": [P, P, I, P, P, L, P, I, P, I, I, I, I, I, F, I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
+
+
+def _declare(l) -> None:
+    sigs = _signatures()
     for name, args in sigs.items():
         if hasattr(l, name):
             fn = getattr(l, name)
@@ -305,8 +311,9 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
                  bn: Optional[int] = None, splits: int = 1, out_is_zero: bool = False) -> None:
     """Tensor-core product of bfloat16 operands.  mode 0: out = a w^T (bfloat16 or float32);
     1: out += a w^T (float32); 2: out = silu(a wg^T) * (a wu^T), w = [wg; wu] of ``half`` rows
-    each; 3: the same with w stored as alternating blocks of 16 gate rows and 16 up rows.  ``bn``: token tile (16..256); ``splits`` > 1 splits K and adds partial sums with
-    atomics (mode 0 then needs ``out`` float32 and zeroed)."""
+    each; 3: the same with w stored as alternating blocks of 16 gate rows and 16 up rows.
+    ``bn``: token tile (16..256); ``splits`` > 1 splits K and adds partial sums with atomics
+    (mode 0 then needs ``out`` float32, zeroed here unless ``out_is_zero``)."""
     _cuda(a, w, out)
     T, K = a.shape
     N = w.shape[0]

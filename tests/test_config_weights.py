@@ -236,3 +236,37 @@ def test_sharded_folder():
             json.dump({"weight_map": weight_map}, f)
         with pytest.raises(SafetensorsError, match="disagree"):
             SafetensorsFolder(d)
+
+
+def test_python_bindings_match_the_c_declarations():
+    """The argument lists that the ctypes bindings declare are those of the exported C entry
+    points: same count, same kinds, in the same order."""
+    import ctypes
+    import pathlib
+    import re
+    from llmario_b200 import kernels
+    src = ""
+    for f in sorted((pathlib.Path(kernels.__file__).parent / "csrc").glob("*.cu")):
+        src += f.read_text()
+    kinds = {ctypes.c_void_p: "P", ctypes.c_int: "I", ctypes.c_longlong: "L", ctypes.c_float: "F"}
+
+    def kind(param: str) -> str:
+        param = param.strip()
+        if "*" in param or param.startswith("cudaStream_t"):
+            return "P"
+        base = re.sub(r"\b(const|unsigned)\b", "", param).split()
+        if base[:2] == ["long", "long"]:
+            return "L"
+        return {"int": "I", "float": "F"}[base[0]]
+
+    sigs = kernels._signatures()
+    seen = set()
+    for m in re.finditer(r"LLM_EXPORT\s+int\s+(\w+)\s*\(([^)]*)\)\s*\{", src):
+        name, params = m.group(1), m.group(2)
+        if name not in sigs:
+            continue
+        seen.add(name)
+        declared = "".join(kind(p) for p in params.split(",")) if params.strip() else ""
+        bound = "".join(kinds[t] for t in sigs[name])
+        assert declared == bound, f"{name}: C has {declared}, the binding {bound}"
+    assert seen == set(sigs), sorted(set(sigs) - seen)
