@@ -484,10 +484,22 @@ def attention_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tens
                                      num_heads, head_dim, splits, _stream()), "attention_merge")
 
 
-def decode_splits(n_items: int, num_kv_heads: int, max_len: int) -> int:
-    """Parts into which the keys of a one-token item are cut so that the GPU is filled."""
+def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int = 3 * SM_COUNT
+                  ) -> int:
+    """Parts into which the keys of a one-token item are cut.  ``resident``: how many CTAs of
+    the kernel the GPU holds at once.  The cost of a choice is modelled as waves of CTAs times
+    the length of one CTA's walk (its tiles of 32 keys plus a fixed start-up of about three
+    tiles), plus the merge, which grows with the number of parts; measured step times at batch
+    1, 8 and 64 and contexts of 1024 and 4096 keys rank the choices the same way."""
     ctas = max(1, n_items * num_kv_heads)
-    return max(1, min(-(-1024 // ctas), max_len // 128, 32))
+    tiles = max(1, -(-max_len // 32))
+    best, best_cost = 1, None
+    for s in range(1, min(32, max(1, max_len // 64)) + 1):
+        waves = -(-ctas * s // resident)
+        cost = waves * (-(-tiles // s) + 3) + 0.1 * s
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
@@ -507,14 +519,16 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
     common = (view.k, view.v, view.page_stride, view.block_table)
     if plan.n_small:
         reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
-        splits = decode_splits(plan.n_small, num_kv_heads, reach) if plan.small_single else 1
+        tma = group <= 8 and decode_tma_ok(view, head_dim)
+        splits = decode_splits(plan.n_small, num_kv_heads, reach,
+                               (3 if tma else 6) * SM_COUNT) if plan.small_single else 1
         part_o = part_ml = None
         if splits > 1:
             part_o = ctx.buffer("attn.part_o", (ctx.rows * num_heads * splits * head_dim,),
                                 torch.float32)
             part_ml = ctx.buffer("attn.part_ml", (ctx.rows * num_heads * splits * 2,),
                                  torch.float32)
-        if group <= 8 and decode_tma_ok(view, head_dim):
+        if tma:
             attention_decode_tma(q, out, view.storage, view.slot, view.block_table, plan.small,
                                  plan.n_small, num_heads, num_kv_heads, head_dim, view.page_size,
                                  scale, window, splits, part_o, part_ml, ctx.row_slot, ctx.row_pos)
