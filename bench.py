@@ -178,7 +178,7 @@ def e2e_bench(engine, batch, prompt_len, steps, warmup, rng):
     t1 = time.perf_counter()
     n1 = sum(len(engine.request(i).output) for i in ids)
     for i in ids:
-        engine.scheduler.abort(engine.request(i))
+        engine.abort(i)
     return (n1 - n0) / (t1 - t0)
 
 

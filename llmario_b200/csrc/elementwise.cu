@@ -186,6 +186,21 @@ LLM_EXPORT int llm_table_update(int* table, int row_stride, const int* updates, 
   return launch_status();
 }
 
+// tokens[i] = source[index[i]] where index[i] >= 0: rows whose token was drawn by the previous
+// step and has not been to the host yet take it from the sampler's output on the device.
+__global__ void patch_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ source,
+                                    const int* __restrict__ index, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && index[i] >= 0) tokens[i] = source[index[i]];
+}
+
+LLM_EXPORT int llm_patch_tokens(int* tokens, const int* source, const int* index, int n,
+                                cudaStream_t stream) {
+  if (n <= 0) return 0;
+  patch_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, source, index, n);
+  return launch_status();
+}
+
 // Clear a [rows][cols] float matrix with row stride ld (a kernel rather than a memset, so that it
 // can take part in programmatic dependent launch).
 __global__ void zero_f32_kernel(float* __restrict__ p, int rows, int cols, int ld) {

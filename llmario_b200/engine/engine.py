@@ -21,17 +21,28 @@ from .scheduler import FINISHED, Request, Scheduler, StepPlan
 from .step import ModelRunner, StepEntry
 
 
+class _Launched:
+    """A step that is queued on the device: its plan and the tokens it will have drawn."""
+
+    def __init__(self, plan: StepPlan, pending):
+        self.plan, self.pending = plan, pending
+
+
 class Engine:
     def __init__(self, model: Union[str, Model, None] = None, *, config=None, seed: int = 0,
                  dtype="bfloat16", device: str = "cuda:0", page_size: int = 16,
                  num_pages: Optional[int] = None, cache_tokens: Optional[int] = None,
                  token_budget: int = 512, max_requests: int = 64,
-                 context: Optional[int] = None, num_layers: Optional[int] = None):
+                 context: Optional[int] = None, num_layers: Optional[int] = None,
+                 lookahead: bool = True):
         """``model``: a folder with config.json and model.safetensors, or a built
         :class:`Model`; or give ``config`` (a typed configuration) and ``seed`` for random
         weights.  ``context``: most tokens of one request; ``max_requests``: requests running at
         once; ``token_budget``: most tokens in one step; ``num_pages`` / ``cache_tokens``: size
-        of the cache (default: room for every request slot at full context)."""
+        of the cache (default: room for every request slot at full context).  ``lookahead``:
+        while a step of decoding requests runs, the next one is already queued on the device
+        with its input tokens taken from the sampler's output there, so that the device does
+        not wait for the host between steps; the tokens a caller sees are the same."""
         if not torch.cuda.is_available():
             raise RuntimeError("llmario_b200 needs a CUDA device; there is no CPU path")
         if isinstance(model, Model):
@@ -52,6 +63,8 @@ class Engine:
         self._ids = itertools.count()
         self._requests: Dict[Any, Request] = {}
         self.timers = {"step_s": 0.0, "sample_s": 0.0}
+        self.lookahead = bool(lookahead)
+        self._flying: Optional[_Launched] = None     # a step queued ahead, not yet read
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -79,31 +92,64 @@ class Engine:
     def step(self) -> List[Request]:
         """One iteration: plan, run the batch, sample, finish.  Returns requests that finished
         (or failed) in this iteration."""
-        plan = self.scheduler.plan()
-        finished: List[Request] = list(plan.failed)
-        if not plan.entries:
-            return finished
-        entries = []
-        for e in plan.entries:
-            toks = e.request.tokens(e.start, e.count)
-            entries.append(StepEntry(e.request.id, toks, [e.count - 1] if e.samples else []))
+        finished: List[Request] = []
+        cur, self._flying = self._flying, None
+        if cur is None:
+            plan = self.scheduler.plan()
+            finished += plan.failed
+            if not plan.entries:
+                return finished
+            cur = self._launch(plan, None)
+        if self.lookahead:
+            # queue the step after this one before waiting for this one's tokens
+            ahead = self.scheduler.plan_ahead(cur.plan)
+            if ahead is not None:
+                self._flying = self._launch(ahead, cur)
         t0 = time.perf_counter()
-        logits = self.runner.step(entries)
-        samplers = [e.request.sampler for e in plan.entries if e.samples]
-        t1 = time.perf_counter()
-        tokens = self.sampler.sample(logits, samplers) if samplers else []
-        t2 = time.perf_counter()
-        self.timers["step_s"] += t1 - t0
-        self.timers["sample_s"] += t2 - t1
+        tokens = cur.pending.result() if cur.pending is not None else []
+        self.timers["wait_s"] = self.timers.get("wait_s", 0.0) + time.perf_counter() - t0
         sampled = {}
         i = 0
-        for e in plan.entries:
+        for e in cur.plan.entries:
             if e.samples:
                 sampled[e.request.id] = tokens[i]
                 e.request.sampler.accept(tokens[i])
                 i += 1
-        finished += self.scheduler.complete(plan, sampled)
+        finished += self.scheduler.complete(cur.plan, sampled)
         return finished
+
+    def _launch(self, plan: StepPlan, after: Optional["_Launched"]) -> "_Launched":
+        """Queue the step of ``plan`` and its draw on the device.  ``after``: the step that is
+        still running and whose drawn tokens are this step's input."""
+        entries = []
+        source = None
+        if after is None:
+            for e in plan.entries:
+                toks = e.request.tokens(e.start, e.count)
+                entries.append(StepEntry(e.request.id, toks, [e.count - 1] if e.samples else []))
+        else:
+            row_of = {}
+            i = 0
+            for e in after.plan.entries:
+                if e.samples:
+                    row_of[e.request.id] = i
+                    i += 1
+            entries = [StepEntry(e.request.id, [0], [0]) for e in plan.entries]
+            source = (self.sampler.device_tokens, [row_of[e.request.id] for e in plan.entries])
+        t0 = time.perf_counter()
+        logits = self.runner.step(entries, source)
+        samplers = [e.request.sampler for e in plan.entries if e.samples]
+        t1 = time.perf_counter()
+        pending = self.sampler.launch(logits, samplers) if samplers else None
+        t2 = time.perf_counter()
+        self.timers["step_s"] += t1 - t0
+        self.timers["sample_s"] += t2 - t1
+        return _Launched(plan, pending)
+
+    def abort(self, request_id: Any) -> None:
+        """Drop a request wherever it is; a step already queued for it runs to its end and its
+        result is ignored."""
+        self.scheduler.abort(self._requests[request_id])
 
     def run_until_done(self) -> List[Request]:
         done: List[Request] = []

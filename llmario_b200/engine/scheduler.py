@@ -211,6 +211,38 @@ class Scheduler:
         self.counters["steps_planned"] += 1
         return plan
 
+    def plan_ahead(self, flying: StepPlan) -> Optional[StepPlan]:
+        """The step after ``flying``, decided while ``flying`` is still running and the tokens it
+        draws are unknown, or None when that step cannot be known yet.  It can when ``flying``
+        draws a token for every running request, nothing waits for admission, and the pages
+        suffice: then every request that does not end for certain (``max_tokens`` or the
+        context reached) decodes one more token.  A request that ends on an end-of-sequence
+        token drawn by ``flying`` has a row too many in the step ahead; :meth:`complete`
+        passes over it.  Changes nothing; the cache lengths already count ``flying``."""
+        if self.waiting or flying.preempted or flying.failed or not flying.entries:
+            return None
+        if len(flying.entries) != len(self.running) or not all(e.samples for e in flying.entries):
+            return None
+        free = list(self.cache.free_pages())
+        entries: List[PlanEntry] = []
+        for e in flying.entries:
+            r = e.request
+            if r.state != RUNNING or r.params.penalties_active:
+                return None
+            if len(r.output) + 1 >= r.params.max_tokens or \
+                    r.sequence_len + 1 >= self.max_context:
+                continue                      # its last token is the one in flight
+            need = self._pages_for(r, 1, True)
+            if any(n > f for n, f in zip(need, free)):
+                return None                   # someone has to go: decided with all facts known
+            free = [f - n for f, n in zip(free, need)]
+            entries.append(PlanEntry(r, e.start + e.count, 1, True))
+        if not entries or len(entries) > self.token_budget:
+            return None
+        self.counters["steps_planned"] += 1
+        self.counters["steps_planned_ahead"] = self.counters.get("steps_planned_ahead", 0) + 1
+        return StepPlan(entries=entries)
+
     def _planned_new(self, entries: List[PlanEntry]) -> int:
         return sum(1 for e in entries if not self.cache.has(e.request.id))
 
@@ -255,6 +287,8 @@ class Scheduler:
         done: List[Request] = []
         for e in plan.entries:
             r = e.request
+            if r.state != RUNNING:
+                continue        # it ended while this step, planned ahead, was already running
             r.computed += e.count
             if r.output and e.count == 1 and e.samples:
                 self.counters["decode_tokens"] += 1

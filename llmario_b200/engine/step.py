@@ -138,12 +138,19 @@ class ModelRunner:
             ev.synchronize()
         return self._meta_dev, self._meta_host[i], i
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry],
+             device_tokens: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> torch.Tensor:
         """Run the tokens of ``entries`` as one batch.  Returns float32 logits
         ``[number of wanted places, vocab]`` on the device, in the order of the entries and of
         each entry's ``want``.  Raises :class:`CacheFull` with nothing changed when the pages
-        do not suffice."""
+        do not suffice.
+
+        ``device_tokens = (source, index)``: row i of the step takes its token from
+        ``source[index[i]]`` (int32, on the device) when ``index[i] >= 0``, whatever the entry
+        says: the token was drawn by an earlier step and has not been read by the host yet."""
         rows = self._validate(entries)
+        if device_tokens is not None and len(device_tokens[1]) != rows:
+            raise StepError("device_tokens needs one index for every row of the step")
         cache = self.cache
         opened = []
         try:
@@ -206,6 +213,9 @@ class ModelRunner:
         for cap in upd_cap:
             o_upd.append(off)
             off += _round4(3 * cap)
+        o_src = off                      # behind everything a recorded graph reads
+        if device_tokens is not None:
+            off += _round4(rows)
         dev, host, which = self._meta_buffers(off)
         h = host.numpy()
         h[:HEADER] = 0
@@ -219,7 +229,12 @@ class ModelRunner:
         for u, o in zip(updates, o_upd):
             if len(u):
                 h[o:o + 3 * len(u)] = u.reshape(-1)
+        if device_tokens is not None:
+            h[o_src:o_src + rows] = np.asarray(device_tokens[1], dtype=np.int32)
         dev[:off].copy_(host[:off], non_blocking=True)
+        if device_tokens is not None:
+            kernels.patch_tokens(dev[o_tok:o_tok + rows], device_tokens[0],
+                                 dev[o_src:o_src + rows])
         ev = torch.cuda.Event()
         ev.record()
         self._meta_event[which] = ev

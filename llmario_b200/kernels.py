@@ -40,6 +40,7 @@ def _signatures():
     return {
         "llm_embed": [P, P, I, P, I, I, I, P, P],
         "llm_rms_norm": [P, P, P, I, P, I, I, F, P],
+        "llm_patch_tokens": [P, P, P, I, P],
         "llm_silu_mul": [P, P, I, I, I, P],
         "llm_table_update": [P, I, P, I, P],
         "llm_table_update_counted": [P, I, P, P, I, P],
@@ -147,6 +148,15 @@ def table_update(table: torch.Tensor, updates: torch.Tensor, n: int) -> None:
     assert table.dtype == torch.int32 and updates.dtype == torch.int32
     _check(lib().llm_table_update(_ptr(table), table.stride(0), _ptr(updates), n, _stream()),
            "table_update")
+
+
+def patch_tokens(tokens: torch.Tensor, source: torch.Tensor, index: torch.Tensor) -> None:
+    """tokens[i] = source[index[i]] for every i with index[i] >= 0 (all int32, on the device)."""
+    _cuda(tokens, source, index)
+    assert tokens.dtype == source.dtype == index.dtype == torch.int32
+    assert tokens.numel() == index.numel()
+    _check(lib().llm_patch_tokens(_ptr(tokens), _ptr(source), _ptr(index), tokens.numel(),
+                                  _stream()), "patch_tokens")
 
 
 def table_update_counted(table: torch.Tensor, updates: torch.Tensor, count: torch.Tensor,

@@ -50,6 +50,18 @@ class RequestSampler:
         return 0.0 if self.params.greedy else self.rng.next_f64()
 
 
+class PendingTokens:
+    """Tokens that the device has drawn (or will, in stream order) and the host has not read."""
+
+    def __init__(self, event, host: torch.Tensor, rows: int):
+        self._event, self._host, self.rows = event, host, rows
+
+    def result(self) -> List[int]:
+        """Wait for the draw and return the token ids."""
+        self._event.synchronize()
+        return self._host[:self.rows].tolist()
+
+
 class DeviceSampler:
     """Samples one token for each row of a logits tensor on the device."""
 
@@ -65,10 +77,19 @@ class DeviceSampler:
             # host (pinned) and device copies of the per-row options, packed in one buffer:
             # [temperature f32 | top_p f32 | min_p f32 | repeat f32 | freq f32 | presence f32 |
             #  top_k i32 | pad | uniform f64]
-            self._host = torch.empty(c * 10, dtype=torch.float32, pin_memory=True)
+            # (two host copies in turn, each with the event of its last copy to the device: a
+            # draw may be prepared while the copy for the one before it is still queued)
+            self._host = [torch.empty(c * 10, dtype=torch.float32, pin_memory=True)
+                          for _ in range(2)]
+            self._host_key = [None, None]
+            self._host_event = [None, None]
             self._dev = torch.empty(c * 10, dtype=torch.float32, device=self.device)
+            self._dev_key = None
             self._out = torch.empty(c, dtype=torch.int32, device=self.device)
-            self._out_host = torch.empty(c, dtype=torch.int32, pin_memory=True)
+            # two host copies in turn: a draw may be launched before the one before it is read
+            self._out_host = [torch.empty(c, dtype=torch.int32, pin_memory=True)
+                              for _ in range(2)]
+            self._flip = 0
         if triples:
             if getattr(self, "_tri_cap", 0) < triples:
                 self._tri_cap = max(1024, 2 * triples)
@@ -77,13 +98,23 @@ class DeviceSampler:
                 self._tri_dev = torch.empty(self._tri_cap * 3, dtype=torch.int32,
                                             device=self.device)
 
+    @property
+    def device_tokens(self) -> torch.Tensor:
+        """The int32 device buffer whose first rows hold the tokens of the latest draw."""
+        return self._out
+
     def sample(self, logits: torch.Tensor, samplers: Sequence[RequestSampler]) -> List[int]:
         """``logits`` float32 [rows, vocab] on the device (modified in place by penalties);
         one :class:`RequestSampler` per row.  Returns the sampled token ids."""
-        rows = logits.shape[0]
-        assert rows == len(samplers) and logits.dtype == torch.float32
-        if rows == 0:
+        if logits.shape[0] == 0:
             return []
+        return self.launch(logits, samplers).result()
+
+    def launch(self, logits: torch.Tensor, samplers: Sequence[RequestSampler]) -> PendingTokens:
+        """As :meth:`sample` without waiting: the draw and the copy of the tokens to the host
+        are queued on the stream; at most two draws may be unread at a time."""
+        rows = logits.shape[0]
+        assert rows == len(samplers) and logits.dtype == torch.float32 and rows > 0
         tri: List[int] = []
         for r, s in enumerate(samplers):
             if s.params.penalties_active:
@@ -94,11 +125,13 @@ class DeviceSampler:
         # the options of a row change only when the set of requests changes; the uniforms
         # change with every draw (greedy rows draw nothing)
         key = [id(s) for s in samplers]
-        same = key == getattr(self, "_last_key", None) and c == getattr(self, "_last_cap", 0)
         any_draw = any(not s.params.greedy for s in samplers)
-        if not same or any_draw:
-            h = self._host.numpy()
-            if not same:
+        if key != self._dev_key or any_draw:
+            i = self._flip
+            if self._host_event[i] is not None:
+                self._host_event[i].synchronize()
+            h = self._host[i].numpy()
+            if key != self._host_key[i]:
                 f = h[:6 * c].reshape(6, c)
                 k = h[6 * c:7 * c].view(np.int32)
                 for r, s in enumerate(samplers):
@@ -107,21 +140,31 @@ class DeviceSampler:
                     f[3, r], f[4, r], f[5, r] = (p.repeat_penalty, p.frequency_penalty,
                                                  p.presence_penalty)
                     k[r] = p.top_k
+                self._host_key[i] = key
             u = h[8 * c:10 * c].view(np.float64)
             for r, s in enumerate(samplers):
                 u[r] = s.next_uniform()
-            self._dev.copy_(self._host, non_blocking=True)
-            self._last_key, self._last_cap = key, c
+            self._dev.copy_(self._host[i], non_blocking=True)
+            self._host_event[i] = torch.cuda.Event()
+            self._host_event[i].record()
+            self._dev_key = key
             self._last_objs = list(samplers)     # keeps the ids above from being reused
         d = self._dev
         if tri:
             n = len(tri) // 3
+            if getattr(self, "_tri_event", None) is not None:
+                self._tri_event.synchronize()       # the copy of the draw before has left
             self._tri_host[:3 * n] = torch.tensor(tri, dtype=torch.int32)
             self._tri_dev[:3 * n].copy_(self._tri_host[:3 * n], non_blocking=True)
+            self._tri_event = torch.cuda.Event()
+            self._tri_event.record()
             kernels.apply_penalties(logits, self._tri_dev, n, d[3 * c:4 * c], d[4 * c:5 * c],
                                     d[5 * c:6 * c])
         kernels.sample(logits, d[0:c], d[6 * c:7 * c].view(torch.int32), d[c:2 * c],
                        d[2 * c:3 * c], d[8 * c:10 * c].view(torch.float64), self._out)
-        self._out_host[:rows].copy_(self._out[:rows], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._out_host[:rows].tolist()
+        host = self._out_host[self._flip]
+        self._flip ^= 1
+        host[:rows].copy_(self._out[:rows], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(event, host, rows)

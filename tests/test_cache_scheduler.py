@@ -332,3 +332,73 @@ def test_random_load_finishes_everything(seed):
     assert all(r.state == FINISHED and r.finish_reason in ("length", "stop") for r in reqs)
     assert all(len(r.output) == r.params.max_tokens or r.sequence_len == 48 for r in reqs)
     assert m.free_pages() == [12, 12]
+
+
+# ------------------------------------------------------------------------------ the step ahead
+def launch(s, plan):
+    """What the step function does to the cache when a plan is queued."""
+    for e in plan.entries:
+        if not s.cache.has(e.request.id):
+            s.cache.open(e.request.id)
+    s.cache.reserve([(e.request.id, e.count) for e in plan.entries])
+    for e in plan.entries:
+        s.cache.advance(e.request.id, e.count)
+
+
+def finish(s, plan, token=7):
+    return s.complete(plan, {e.request.id: token for e in plan.entries if e.samples})
+
+
+def test_a_step_is_planned_ahead_only_when_it_is_certain():
+    s = Scheduler(manager(n_pages=64, ctx=64), token_budget=8, eos_token_ids=[99])
+    a, b = req("a", 10, max_tokens=3), req("b", 3, max_tokens=50)
+    s.add(a), s.add(b)
+    p1 = s.plan()                       # a's first portion: nothing is drawn for b
+    launch(s, p1)
+    assert s.plan_ahead(p1) is None
+    finish(s, p1)
+    p2 = s.plan()                       # the rest of a and all of b: both draw a token
+    launch(s, p2)
+    p3 = s.plan_ahead(p2)
+    assert [(e.request.id, e.start, e.count, e.samples) for e in p3.entries] == \
+        [("a", 10, 1, True), ("b", 3, 1, True)]
+    launch(s, p3)
+    finish(s, p2)
+    p4 = s.plan_ahead(p3)               # a's third and last token will be the one p4 draws
+    assert [e.request.id for e in p4.entries] == ["a", "b"]
+    launch(s, p4)
+    finish(s, p3)
+    p5 = s.plan_ahead(p4)               # a ends for certain with p4: only b goes on
+    assert [(e.request.id, e.start) for e in p5.entries] == [("b", 5)]
+    launch(s, p5)
+    assert finish(s, p4) == [a] and a.output == [7, 7, 7] and a.finish_reason == "length"
+    # b draws an end-of-sequence token in p5 while p6 is already queued for it
+    p6 = s.plan_ahead(p5)
+    launch(s, p6)
+    assert finish(s, p5, token=99) == [b] and b.finish_reason == "stop"
+    assert finish(s, p6) == [] and b.output == [7, 7, 7, 99]     # the row too many is passed over
+    assert s.plan_ahead(p6) is None and not s.has_work()
+    assert s.cache.free_pages() == [64]
+    s.cache.check_invariants()
+
+
+def test_no_step_ahead_when_someone_waits_or_pages_are_short():
+    m = manager(n_pages=4, page=4, max_requests=2, ctx=64)
+    s = Scheduler(m, token_budget=64)
+    a, b, c = req("a", 7, 50), req("b", 7, 50), req("c", 3, 50)
+    s.add(a), s.add(b), s.add(c)        # two request slots: c waits
+    p = s.plan()
+    launch(s, p)
+    assert [e.request.id for e in p.entries] == ["a", "b"] and s.plan_ahead(p) is None
+    finish(s, p)
+    s.abort(c)
+    p = s.plan()                        # a and b at 8 tokens each: all four pages are full
+    launch(s, p)
+    assert s.plan_ahead(p) is None      # the next token of each needs a page that is not there
+    pen = req("p", 3, 50)
+    pen.params.repeat_penalty = 1.3     # penalties need the tokens on the host
+    s2 = Scheduler(manager(n_pages=64, ctx=64), token_budget=8)
+    s2.add(pen)
+    p = s2.plan()
+    launch(s2, p)
+    assert pen.params.penalties_active and s2.plan_ahead(p) is None

@@ -177,6 +177,55 @@ def test_temperature_generation_is_reproducible_and_batch_independent():
     assert a == b
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_queued_ahead_give_the_same_tokens(dtype):
+    """With a step queued while the one before it still runs (its input tokens taken from the
+    sampler's output on the device), the engine returns what it returns step by step: greedy
+    and seeded temperature sampling, different lengths, an end-of-sequence token in the middle
+    of one request, and a request that joins later."""
+    from llmario_b200 import Engine, SamplingParams
+    name = "D"
+    prompts = [random_tokens(name, n, 90 + n) for n in (3, 19, 33, 6)]
+    params = [SamplingParams(temperature=0.0, max_tokens=40),
+              SamplingParams(temperature=0.8, seed=5, max_tokens=25),
+              SamplingParams(temperature=0.0, max_tokens=9),
+              SamplingParams(temperature=0.6, seed=9, max_tokens=30)]
+
+    def run(lookahead, eos=()):
+        eng = Engine(model_dir(name, dtype), dtype=dtype, page_size=16, cache_tokens=1024,
+                     max_requests=4, context=256, token_budget=32, lookahead=lookahead)
+        eng.scheduler.eos = frozenset(eos)
+        ids = [eng.add_request(p, sp) for p, sp in zip(prompts[:3], params[:3])]
+        for _ in range(6):
+            eng.step()
+        ids.append(eng.add_request(prompts[3], params[3]))      # joins while the others decode
+        eng.run_until_done()
+        assert min(eng.runner.cache.free_pages()) == eng.runner.cache.groups[0].n_pages
+        eng.runner.cache.check_invariants()
+        return [(list(eng.request(i).output), eng.request(i).finish_reason) for i in ids], \
+            eng.stats()
+
+    plain_run, _ = run(False)
+    ahead_run, stats = run(True)
+    assert ahead_run == plain_run
+    assert stats.get("steps_planned_ahead", 0) >= 20          # and most steps were queued ahead
+    eos = plain_run[0][0][17]               # the first request now stops at its 18th token
+    stop_plain, _ = run(False, [eos])
+    stop_ahead, _ = run(True, [eos])
+    assert stop_ahead == stop_plain
+    first = stop_plain[0][0]
+    assert stop_plain[0][1] == "stop" and first[-1] == eos and len(first) <= 18
+
+
+def test_patch_tokens_kernel():
+    from llmario_b200 import kernels
+    tokens = torch.arange(10, 20, dtype=torch.int32, device=DEV)
+    source = torch.tensor([100, 200, 300], dtype=torch.int32, device=DEV)
+    index = torch.tensor([-1, 2, 0, -1, 1, 1, -1, -1, 0, 2], dtype=torch.int32, device=DEV)
+    kernels.patch_tokens(tokens, source, index)
+    assert tokens.tolist() == [10, 300, 100, 13, 200, 200, 16, 17, 100, 300]
+
+
 # ----------------------------------------------------------------------------- parts alone
 def test_parts_alone():
     """Each part built from its spec and stepped by itself against the plain functions."""
