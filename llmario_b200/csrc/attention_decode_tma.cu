@@ -3,12 +3,14 @@
 // The arithmetic is that of attention_decode.cu (keys on the M side of mma.sync m16n8k16, at most
 // eight (token, head) pairs per item, 32-bit running maximum and sum per pair, optional split of
 // the key range).  What differs is how K and V reach shared memory.  The cache of a group of
-// layers is one tensor [page][cache slot][K|V][kv head][position][head dim]; seen as a matrix of
-// rows of head_dim elements it is tiled by one tensor map, and the positions of one page and KV
-// head are `page_size` consecutive rows.  One lane asks for them with a few TMA tile loads per
-// 32-key tile (64 columns x up to 32 rows each, 128-byte swizzle) and the bytes are counted on an
-// mbarrier per stage of a four-stage ring, so the warp spends its instructions on the products
-// and not on addresses.  Head sizes 64 and 128; other sizes use attention_decode.cu.
+// layers is one tensor [page][cache slot][K|V][kv head][position][head dim].  One tensor map of
+// five dimensions describes it (64 columns of a row, the 64-column halves of a row, the
+// positions of a page, the KV heads, the K and V planes of all pages and cache slots), and ONE
+// tile load brings the keys and the values of a page and KV head: up to 32 positions, 8 KB for a
+// page of 16 at head size 128.  The TMA unit spends about the same time on a load whatever its
+// size, so few large loads are what lets a warp stream at the memory's speed.  The bytes are
+// counted on an mbarrier per stage of a four-stage ring; the warp spends its instructions on the
+// products and not on addresses.  Head sizes 64 and 128; other sizes use attention_decode.cu.
 #include "attention_common.cuh"
 #include "tcgen05.cuh"
 
@@ -20,10 +22,13 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
   return r;
 }
 
-// byte offset of 16-byte chunk c (0 .. HD/8-1) of key row r inside a K or V tile of a stage:
-// the tile is [HD/64 column halves][KT rows][128 bytes] with the TMA 128-byte swizzle
-template <int KT> __device__ __forceinline__ int tile_off(int r, int c) {
-  return (c >> 3) * (KT * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+// Byte offset, inside a stage, of 16-byte chunk c (0 .. HD/8-1) of key row r (0 .. KT-1) of the
+// K (kv = 0) or V (kv = 1) tile.  A stage holds KT >> lgR loads of R = 1 << lgR positions, each
+// laid out as the TMA unit writes its box: [K|V][position][HD * 2 bytes], with the 128-byte
+// swizzle (the chunk index is xor-ed with bits 7..9 of the address; stages are 1024-byte aligned).
+template <int HD> __device__ __forceinline__ int tile_off(int kv, int r, int c, int lgR) {
+  const int lin = ((((r >> lgR) * 2 + kv) << lgR) + (r & ((1 << lgR) - 1))) * (HD * 2) + (c >> 3) * 128;
+  return lin + (((c & 7) ^ ((lin >> 7) & 7)) << 4);
 }
 
 template <int HD, int KT, int STAGES>
@@ -31,22 +36,21 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, bf16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ items, const int* __restrict__ row_slot,
-    const int* __restrict__ row_pos, int Hq, int Hkv, int page_size, long long rows_per_page,
-    int k_row0, int v_row0, float scale_log2, int window, int splits, int* __restrict__ status) {
-  constexpr int KS = HD / 16, MT = KT / 16, DM = HD / 16, HALVES = HD / 64;
+    const int* __restrict__ row_pos, int Hq, int Hkv, int page_size, int n_slots, int slot,
+    float scale_log2, int window, int splits, int* __restrict__ status) {
+  constexpr int KS = HD / 16, MT = KT / 16, DM = HD / 16;
   constexpr int TILE_BYTES = KT * HD * 2;            // one K or V tile
   extern __shared__ uint8_t raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* ks = smem;                                // [STAGES][TILE_BYTES]
-  uint8_t* vs = smem + STAGES * TILE_BYTES;          // [STAGES][TILE_BYTES]
-  uint64_t* full = reinterpret_cast<uint64_t*>(vs + STAGES * TILE_BYTES);
+  uint8_t* kv_tiles = smem;                          // [STAGES][2 * TILE_BYTES]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * 2 * TILE_BYTES);
   pdl_trigger();
 
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   // values of rows that no load fills are multiplied by zero weights: they must be finite
-  for (int i = lane; i < STAGES * TILE_BYTES / 16; i += 32)
-    reinterpret_cast<uint4*>(vs)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = lane; i < STAGES * 2 * TILE_BYTES / 16; i += 32)
+    reinterpret_cast<uint4*>(kv_tiles)[i] = make_uint4(0, 0, 0, 0);
   if (lane == 0) {
     for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -97,8 +101,10 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
   for (int d = 0; d < DM; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  // lane 0 asks for the pages of a tile: R = min(page_size, KT) rows per load
+  // lane 0 asks for the pages of a tile: R = min(page_size, KT) positions per load, K and V of
+  // them in one box
   const int R = page_size < KT ? page_size : KT;
+  const int lgR = 31 - __clz(R);
   auto load_tile = [&](int tb, int stage) {
     const int base = tb * KT;
     uint32_t bytes = 0;
@@ -107,16 +113,9 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
     mbar_expect_tx(&full[stage], bytes);
     for (int p = base; p < base + KT; p += R) {
       if (p > hi || p + R - 1 < lo) continue;       // no key of the item here: the page may be gone
-      const long long row = (long long)table[p / page_size] * rows_per_page + (long long)kvh * page_size +
-                            p % page_size;
-      const int dst = (p - base) * 128;
-#pragma unroll
-      for (int h = 0; h < HALVES; ++h) {
-        tma_load_2d(ks + stage * TILE_BYTES + h * KT * 128 + dst, &map_kv, h * 64, (int)(row + k_row0),
-                    &full[stage]);
-        tma_load_2d(vs + stage * TILE_BYTES + h * KT * 128 + dst, &map_kv, h * 64, (int)(row + v_row0),
-                    &full[stage]);
-      }
+      const int plane = (table[p / page_size] * n_slots + slot) * 2;
+      tma_load_5d(kv_tiles + stage * 2 * TILE_BYTES + ((p - base) >> lgR) * (2 * R * HD * 2), &map_kv, 0, 0,
+                  p % page_size, kvh, plane, &full[stage]);
     }
   };
 
@@ -132,8 +131,7 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
       if (lane == 0) atomicExch(status, 4);
       break;
     }
-    const uint8_t* kt = ks + stage * TILE_BYTES;
-    const uint8_t* vt = vs + stage * TILE_BYTES;
+    const uint8_t* tile = kv_tiles + stage * 2 * TILE_BYTES;
 
     // ---- S^T = K Q^T
     float s[MT][4];
@@ -145,7 +143,7 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
       for (int mt = 0; mt < MT; ++mt) {
         uint32_t a[4];
         const int mi = lane >> 3;
-        ldmatrix_x4(a, kt + tile_off<KT>(mt * 16 + (mi & 1) * 8 + (lane & 7), 2 * k + (mi >> 1)));
+        ldmatrix_x4(a, tile + tile_off<HD>(0, mt * 16 + (mi & 1) * 8 + (lane & 7), 2 * k + (mi >> 1), lgR));
         mma_bf16(s[mt], a, qf[k][0], qf[k][1]);
       }
     }
@@ -198,7 +196,7 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
       for (int d = 0; d < DM; ++d) {
         uint32_t a[4];
         const int mi = lane >> 3;
-        ldmatrix_x4_trans(a, vt + tile_off<KT>(kk * 16 + (mi >> 1) * 8 + (lane & 7), 2 * d + (mi & 1)));
+        ldmatrix_x4_trans(a, tile + tile_off<HD>(1, kk * 16 + (mi >> 1) * 8 + (lane & 7), 2 * d + (mi & 1), lgR));
         mma_bf16(o[d], a, b0, b1);
       }
     }
@@ -248,8 +246,8 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
 template <int HD>
 int launch(const CUtensorMap& map, const bf16* q, bf16* out, float* part_o, float* part_ml, const int* table,
            int table_stride, const int* items, const int* row_slot, const int* row_pos, int n_items, int Hq,
-           int Hkv, int page_size, long long rows_per_page, int k_row0, int v_row0, float scale, int window,
-           int splits, int* status, cudaStream_t s) {
+           int Hkv, int page_size, int n_slots, int slot, float scale, int window, int splits, int* status,
+           cudaStream_t s) {
   constexpr int KT = 32, STAGES = 4;
   auto kernel = flash_decode_tma_kernel<HD, KT, STAGES>;
   constexpr int smem = 2 * STAGES * KT * HD * 2 + STAGES * 8 + 1024;
@@ -261,8 +259,8 @@ int launch(const CUtensorMap& map, const bf16* q, bf16* out, float* part_o, floa
   }
   dim3 grid(n_items, Hkv, splits);
   return launch_pdl(kernel, grid, 32, smem, s, map, q, out, part_o, part_ml, table, table_stride, items,
-                    row_slot, row_pos, Hq, Hkv, page_size, rows_per_page, k_row0, v_row0,
-                    scale * 1.4426950408889634f, window, splits, status);
+                    row_slot, row_pos, Hq, Hkv, page_size, n_slots, slot, scale * 1.4426950408889634f, window,
+                    splits, status);
 }
 }  // namespace
 
@@ -280,17 +278,22 @@ LLM_EXPORT int llm_attention_decode_tma(const void* q, void* out, float* part_o,
   if (splits > 1 && (!part_o || !part_ml)) return LLM_ERR_ARGUMENT;
   if (hd != 64 && hd != 128) return LLM_ERR_UNSUPPORTED;
   if (!(32 % page_size == 0 || page_size % 32 == 0)) return LLM_ERR_UNSUPPORTED;
-  const long long rows_per_page = (long long)n_slots * 2 * Hkv * page_size;
-  const long long total_rows = n_pages * rows_per_page;
-  if (total_rows >= (1LL << 31)) return LLM_ERR_UNSUPPORTED;
+  if (page_size & (page_size - 1)) return LLM_ERR_UNSUPPORTED;
+  const long long planes = n_pages * n_slots * 2;
+  if (planes >= (1LL << 31) || slot < 0 || slot >= n_slots) return LLM_ERR_UNSUPPORTED;
+  // innermost first: 64 columns, the halves of a row, the positions of a page, the KV heads, the
+  // K and V planes of every (page, cache slot)
+  const int R = page_size < 32 ? page_size : 32;
+  const long long dims[5] = {64, hd / 64, page_size, Hkv, planes};
+  const long long strides[4] = {128, (long long)hd * 2, (long long)page_size * hd * 2,
+                                (long long)Hkv * page_size * hd * 2};
+  const int box[5] = {64, hd / 64, R, 1, 2};
   CUtensorMap map;
-  if (!llm_tensor_map(storage, total_rows, hd, hd, page_size < 32 ? page_size : 32, 64, 0, &map))
-    return LLM_ERR_UNSUPPORTED;
-  const int k_row0 = (slot * 2 + 0) * Hkv * page_size, v_row0 = (slot * 2 + 1) * Hkv * page_size;
+  if (!llm_tensor_map_tiled(storage, 5, dims, strides, box, &map)) return LLM_ERR_UNSUPPORTED;
 #define GO(HD)                                                                                          \
   return launch<HD>(map, (const bf16*)q, (bf16*)out, part_o, part_ml, block_table, table_stride, items,  \
-                    row_slot, row_pos, n_items, Hq, Hkv, page_size, rows_per_page, k_row0, v_row0, scale, \
-                    window, splits, status, stream)
+                    row_slot, row_pos, n_items, Hq, Hkv, page_size, (int)n_slots, slot, scale, window, splits,  \
+                    status, stream)
   if (hd == 128) GO(128);
   GO(64);
 #undef GO

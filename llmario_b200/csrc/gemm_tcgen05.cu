@@ -21,6 +21,7 @@
 // *status, drains the loads it still has in flight, frees its TMEM and returns.
 #include <cuda.h>
 
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -299,6 +300,58 @@ bool llm_tensor_map(const void* ptr, long long rows, long long cols, long long l
                    const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+// A bfloat16 tensor of `rank` dimensions (innermost first: extents `dims`, strides in bytes of
+// dimensions 1 .. rank-1 in `strides`), tiled in boxes of `box` elements with the 128-byte
+// swizzle.  Cached like the matrices above.
+bool llm_tensor_map_tiled(const void* ptr, int rank, const long long* dims, const long long* strides,
+                          const int* box, CUtensorMap* out) {
+  struct Key {
+    const void* ptr;
+    int rank;
+    long long dims[5], strides[4];
+    int box[5];
+    bool operator==(const Key& o) const { return memcmp(this, &o, sizeof(Key)) == 0; }
+  };
+  struct KeyHash {
+    size_t operator()(const Key& k) const {
+      size_t h = 1469598103934665603ULL;
+      const unsigned char* b = reinterpret_cast<const unsigned char*>(&k);
+      for (size_t i = 0; i < sizeof(Key); ++i) h = (h ^ b[i]) * 1099511628211ULL;
+      return h;
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  static std::mutex mu;
+  if (rank < 2 || rank > 5) return false;
+  Key key;
+  memset(&key, 0, sizeof(key));
+  key.ptr = ptr;
+  key.rank = rank;
+  for (int i = 0; i < rank; ++i) key.dims[i] = dims[i], key.box[i] = box[i];
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides[i];
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiled enc = encoder();
+  if (!enc) return false;
+  cuuint64_t gd[5], gs[4];
+  cuuint32_t bx[5], el[5];
+  for (int i = 0; i < rank; ++i) gd[i] = (cuuint64_t)dims[i], bx[i] = (cuuint32_t)box[i], el[i] = 1;
+  for (int i = 0; i + 1 < rank; ++i) gs[i] = (cuuint64_t)strides[i];
+  CUtensorMap m;
+  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), gd, gs, bx, el,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, m);

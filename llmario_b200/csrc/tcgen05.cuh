@@ -17,6 +17,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            int c4, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar))
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -61,3 +68,7 @@ constexpr uint32_t instr_desc() {
 // Maps are made once per (pointer, shape, box) and cached.  Defined in gemm_tcgen05.cu.
 bool llm_tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols,
                     int kind, CUtensorMap* out);
+// A bfloat16 tensor of 2 to 5 dimensions (innermost first; strides in bytes of dimensions
+// 1 .. rank-1), tiled in boxes with the 128-byte swizzle.  Cached; defined in gemm_tcgen05.cu.
+bool llm_tensor_map_tiled(const void* ptr, int rank, const long long* dims, const long long* strides,
+                          const int* box, CUtensorMap* out);

@@ -483,7 +483,7 @@ def decode_tma_ok(view, head_dim: int) -> bool:
     st = getattr(view, "storage", None)
     ps = view.page_size
     return (st is not None and st.is_contiguous() and head_dim in (64, 128)
-            and (32 % ps == 0 or ps % 32 == 0) and st.numel() // head_dim < (1 << 31))
+            and ps & (ps - 1) == 0 and st.shape[0] * st.shape[1] * 2 < (1 << 31))
 
 
 def attention_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor,
