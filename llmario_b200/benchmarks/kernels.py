@@ -40,6 +40,7 @@ def timed(fn, reps: int, flush) -> float:
 
 def cmd_gemm(a) -> None:
     T, N, K = a.rows, a.out, getattr(a, "in")
+    kernels.use_cta_pairs(not a.one_cta)
     x = torch.randn(T, K, device=DEV).bfloat16()
     w = (0.02 * torch.randn(N, K, device=DEV)).bfloat16()
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
@@ -140,6 +141,8 @@ def main(argv=None) -> int:
     g.add_argument("--mode", default="store", choices=["store", "accumulate", "gated", "gemv", "simt"])
     g.add_argument("--tile", type=int, default=None)
     g.add_argument("--splits", type=int, default=1)
+    g.add_argument("--one-cta", action="store_true",
+                   help="many rows: the one-CTA persistent kernel instead of CTA pairs")
     g.add_argument("--f32", action="store_true")
     g.add_argument("--interleaved", action="store_true",
                    help="gated mode: the matrix holds alternating blocks of 16 gate and 16 up rows")

@@ -30,6 +30,8 @@
 #include "tcgen05.cuh"
 
 int llm_zero_f32(float* p, int rows, int cols, int ld, cudaStream_t stream);   // elementwise.cu
+int llm_gemm_tcgen05_pair(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K, int lda,
+                          int ldw, int ldc, int mode, int half, int* status, cudaStream_t stream);
 int llm_gemm_tcgen05_persistent(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
                                 int lda, int ldw, int ldc, int mode, int half, int* status,
                                 cudaStream_t stream);                        // gemm_tcgen05_persistent.cu
@@ -175,18 +177,18 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(
           tmem_ld_wait();
           if (EPI == EPI_GATED) {
             // lanes 0..15 hold gate of feature q*16 + lane, lanes 16..31 the matching up values
+            // (both halves of the warp compute: eight columns each, see gated_columns)
             const int f = q * 16 + (lane & 15);
             const int n = n0 + f;
+            const int col0 = c + (lane < 16 ? 0 : 8);
+            float r[8];
+            gated_columns<TC>(v, lane, r);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float mine = __uint_as_float(v[j]);
-              const float u = __shfl_down_sync(0xffffffffu, mine, 16);
-              if (lane < 16) {
-                const int t = t0 + c + j;
-                const TC a = from_f32<TC>(mine / (1.0f + __expf(-mine)) * u);
-                if (tma_out) stage_out[(c + j) * FEAT + f] = a;
-                else if (t < T && n < half) C[(size_t)t * ldc + n] = a;
-              }
+            for (int i = 0; i < 8; ++i) {
+              const int t = t0 + col0 + i;
+              const TC a = from_f32<TC>(r[i]);
+              if (tma_out) stage_out[(col0 + i) * FEAT + f] = a;
+              else if (t < T && n < half) C[(size_t)t * ldc + n] = a;
             }
           } else {
             const int n = n0 + row;
@@ -415,11 +417,13 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dty
   if (((uintptr_t)X | (uintptr_t)W) & 15) return LLM_ERR_UNSUPPORTED;
   if (splits < 1) return LLM_ERR_ARGUMENT;
   if (bn == 256) {
-    // many rows: the persistent kernel (tiles of 256 tokens, epilogue overlapped with the next
-    // tile); if the output cannot be written by TMA, the one-tile kernel with 128 tokens
+    // many rows: the persistent kernels (tiles of 256 tokens, epilogue overlapped with the next
+    // tile), on CTA pairs where that form exists; if the output cannot be written by TMA, the
+    // one-tile kernel with 128 tokens
     if (splits == 1) {
-      const int r = llm_gemm_tcgen05_persistent(X, W, C, c_dtype, T, N, K, lda, ldw, ldc, mode, half, status,
-                                                stream);
+      int r = llm_gemm_tcgen05_pair(X, W, C, c_dtype, T, N, K, lda, ldw, ldc, mode, half, status, stream);
+      if (r != LLM_ERR_UNSUPPORTED) return r;
+      r = llm_gemm_tcgen05_persistent(X, W, C, c_dtype, T, N, K, lda, ldw, ldc, mode, half, status, stream);
       if (r != LLM_ERR_UNSUPPORTED) return r;
     }
     bn = 128;

@@ -178,13 +178,11 @@ __global__ void __launch_bounds__(192, 1) gemm_persistent_kernel(
           tmem_ld_wait();
           if (EPI == EPI_GATED) {
             const int f = q * 16 + (lane & 15);
+            const int col0 = h * 16 + (lane < 16 ? 0 : 8);
+            float r[8];
+            gated_columns<TC>(v, lane, r);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float mine = __uint_as_float(v[j]);
-              const float u = __shfl_down_sync(0xffffffffu, mine, 16);
-              if (lane < 16)
-                stage_out[(h * 16 + j) * FEAT + f] = from_f32<TC>(mine / (1.0f + __expf(-mine)) * u);
-            }
+            for (int i = 0; i < 8; ++i) stage_out[(col0 + i) * FEAT + f] = from_f32<TC>(r[i]);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j)

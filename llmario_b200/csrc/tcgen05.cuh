@@ -56,6 +56,27 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// silu(g) * u = g / (1 + exp(-g)) * u in 32-bit; with a 16-bit result the division is the fast
+// one (two units in the last place, far below the rounding of the result).
+template <typename TC> __device__ __forceinline__ float silu_mul(float g, float u) {
+  if (sizeof(TC) == 2) return __fdividef(g, 1.0f + __expf(-g)) * u;
+  return g / (1.0f + __expf(-g)) * u;
+}
+// Gated epilogue of 16 accumulator columns v[0..15].  In each warp lanes 0..15 hold gate rows and
+// lanes 16..31 the up rows of the same 16 features.  Both halves of the warp work: lane L < 16
+// and lane L + 16 swap half of their columns, so that L computes columns 0..7 of its feature and
+// L + 16 columns 8..15.  out[i] is column (lane < 16 ? i : 8 + i).
+template <typename TC> __device__ __forceinline__ void gated_columns(const uint32_t* v, int lane, float* out) {
+  const bool low = lane < 16;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float keep = __uint_as_float(low ? v[i] : v[8 + i]);
+    const float send = __uint_as_float(low ? v[8 + i] : v[i]);
+    const float got = __shfl_xor_sync(0xffffffffu, send, 16);
+    out[i] = low ? silu_mul<TC>(keep, got) : silu_mul<TC>(got, keep);
+  }
+}
+
 template <int BN>
 constexpr uint32_t instr_desc() {
   // float32 accumulator, bf16 A and B, both K-major, N = BN, M = 128

@@ -317,6 +317,15 @@ def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def use_cta_pairs(on: bool) -> None:
+    """Whether products of many rows run on CTA pairs (tcgen05 cta_group::2; the default) or on
+    the one-CTA persistent kernel.  For comparisons."""
+    l = lib()
+    l.llm_set_pair.argtypes = [c_int]
+    l.llm_set_pair.restype = None
+    l.llm_set_pair(int(on))
+
+
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, half: int = 0,
                  bn: Optional[int] = None, splits: int = 1, out_is_zero: bool = False) -> None:
     """Tensor-core product of bfloat16 operands.  mode 0: out = a w^T (bfloat16 or float32);
