@@ -122,7 +122,8 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
   extern __shared__ uint8_t raw[];
   auto& sm = *reinterpret_cast<AttnStorage<HD>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const Item it = reinterpret_cast<const Item*>(items)[blockIdx.x];
+  // the last items of a prompt have the most keys to walk: they are started first
+  const Item it = reinterpret_cast<const Item*>(items)[gridDim.x - 1 - blockIdx.x];
   const int kvh = blockIdx.y;
   const int G = Hq / Hkv;
   const int hi = it.pos_start + it.tokens - 1;
