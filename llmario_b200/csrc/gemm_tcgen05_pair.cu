@@ -20,8 +20,6 @@
 // 16.  The output must be reachable by TMA.  Every wait is bounded: a CTA that gives up sets
 // *status and walks to the final cluster barrier, where its peer (whose own waits run out in
 // turn) meets it before tensor memory is freed.  No load is multicast.
-#include <cstdio>
-#include <cstdlib>
 #include "tcgen05.cuh"
 
 namespace {
@@ -336,8 +334,6 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, 
       return LLM_ERR_UNSUPPORTED;
     }
     resident_pairs = n < sm_count / 2 ? n : sm_count / 2;
-    if (getenv("LLM_PAIR_DEBUG")) fprintf(stderr, "pair kernel: %d clusters resident (query said %d)\n", resident_pairs, n);
-    if (getenv("LLM_PAIRS")) resident_pairs = atoi(getenv("LLM_PAIRS"));
   }
   const int pairs = m_tiles * n_tiles < resident_pairs ? m_tiles * n_tiles : resident_pairs;
   cfg.gridDim = dim3(2 * pairs);

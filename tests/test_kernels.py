@@ -234,7 +234,8 @@ def test_qk_norm_rope_store(dtype, Hq, Hkv, hd, page):
 
 @pytest.mark.parametrize("T,N,K", [(1, 128, 64), (16, 256, 128), (5, 200, 72), (40, 384, 4096),
                                    (130, 130, 264), (300, 1000, 512), (64, 4096, 12288),
-                                   (700, 384, 520), (1100, 130, 72)])
+                                   (700, 384, 520), (1100, 130, 72), (600, 300, 4096),
+                                   (1024, 512, 3080)])
 def test_gemm_tcgen05(T, N, K):
     from llmario_b200 import kernels
     a, w = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=3)
