@@ -261,6 +261,16 @@ def test_gemm_tcgen05(T, N, K):
         o2 = torch.empty(T, N, dtype=torch.float32, device=DEV)
         kernels.gemm_tcgen05(a, w, o2, 0, bn=bn)
         assert (o2.double() - ref).abs().max() <= tol, bn
+    try:                               # tiles of 256 tokens on one CTA instead of a CTA pair
+        kernels.use_cta_pairs(False)
+        o2 = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tcgen05(a, w, o2, 0, bn=256)
+        assert (o2.double() - ref).abs().max() <= 2 ** -8 * float(ref.abs().max()) + tol
+        acc = base.clone()
+        kernels.gemm_tcgen05(a, w, acc, 1, bn=256)
+        assert (acc.double() - (base.double() + ref)).abs().max() <= tol
+    finally:
+        kernels.use_cta_pairs(True)
     if K >= 256:                       # K split in three, partial sums added
         acc = base.clone()
         kernels.gemm_tcgen05(a, w, acc, 1, splits=3)
@@ -293,6 +303,14 @@ def test_gemm_tcgen05_gated(T, ff, K):
         kernels.gemm_tcgen05(a, wi.contiguous(), act2, 3, ff)
         kernels.check_tc_status(DEV)
         assert (act2.double() - want).abs().max() <= tol
+        try:              # many rows: on one CTA per tile instead of a CTA pair
+            kernels.use_cta_pairs(False)
+            act3 = torch.empty(T, ff, dtype=torch.bfloat16, device=DEV)
+            kernels.gemm_tcgen05(a, wi.contiguous(), act3, 3, ff)
+            kernels.check_tc_status(DEV)
+            assert (act3.double() - want).abs().max() <= 2 ** -8 * float(want.abs().max()) + tol
+        finally:
+            kernels.use_cta_pairs(True)
 
 
 @pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (6, 3, 64, 8, 50),
