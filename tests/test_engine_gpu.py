@@ -381,3 +381,136 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
         assert_close(out, reference(b), "float32", "toy mixer, slot used again")
     finally:
         unregister_part("mixer", "running_mean")
+
+
+# ------------------------------------------------- a toy feed-forward and a toy position encoding
+class TopOneOfTwo:
+    """A feed-forward with routing, defined here and not in the package: a router scores two
+    small gated experts per token in 32-bit, the token goes to the better one and the expert's
+    output is weighted by the softmax probability of its score."""
+
+    def __init__(self, spec, weights, dtype, device):
+        t = spec["tensors"]
+        self.router = weights[t["router"][0]].float()
+        self.experts = [tuple(weights[t[f"{r}{e}"][0]].float() for r in ("gate", "up", "down"))
+                        for e in range(2)]
+
+    def forward(self, ctx, h, x):
+        hf = h.float()
+        scores = hf @ self.router.T
+        prob = torch.softmax(scores, -1)
+        choice = scores.argmax(-1)
+        for e, (gate, up, down) in enumerate(self.experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                g = hf[rows] @ gate.T
+                y = (g / (1 + torch.exp(-g)) * (hf[rows] @ up.T)) @ down.T
+                x.index_add_(0, rows, y * prob[rows, e:e + 1])
+
+
+class InterpolatedPartialRotary:
+    """A position encoding defined here: only the first half of each head is rotated, positions
+    are divided by a factor (interpolation), and the rotated values are scaled by a constant.
+    It offers no per-step table, so the fused kernel computes the angles itself."""
+
+    def __init__(self, spec, weights, dtype, device):
+        self.rot_dim, self.theta = int(spec["rot_dim"]), float(spec["theta"])
+        self.factor, self.gain = float(spec["factor"]), float(spec["gain"])
+        i = np.arange(self.rot_dim // 2, dtype=np.float64)
+        freq = self.theta ** (-(2.0 * i) / self.rot_dim) / self.factor
+        self.inv_freq = torch.tensor(freq.astype(np.float32), device=device)
+
+    def rotary_tables(self):
+        return self.inv_freq, self.rot_dim, self.gain
+
+
+def test_a_toy_feed_forward_with_routing_and_a_toy_position_encoding():
+    """Both are registered from here, chosen by a spec for layer 1 of config A, built and
+    stepped in portions and in a mixed batch; the framework's files are untouched."""
+    from llmario_b200.config import PartSpec, load_spec
+    from llmario_b200.engine import Model, ModelRunner, StepEntry
+    from llmario_b200.parts import register_part, unregister_part
+    from llmario_b200.weights import expected_tensors, random_tensors
+    register_part("feed_forward", "top_one_of_two", TopOneOfTwo, replace=True)
+    register_part("position", "interpolated_partial", InterpolatedPartialRotary, replace=True)
+    try:
+        base = load_spec(model_dir("A", "float32"))
+        cfg = P.read_config(model_dir("A", "float32"))
+        hidden, ff, hd = base.hidden_size, 24, cfg["head_dim"]
+        tensors = {"router": ("toy.router.weight", (2, hidden))}
+        for e in range(2):
+            tensors[f"gate{e}"] = (f"toy.expert{e}.gate.weight", (ff, hidden))
+            tensors[f"up{e}"] = (f"toy.expert{e}.up.weight", (ff, hidden))
+            tensors[f"down{e}"] = (f"toy.expert{e}.down.weight", (hidden, ff))
+        routed = PartSpec("top_one_of_two", {"hidden_size": hidden, "tensors": tensors})
+        rot, factor, gain = hd // 2, 4.0, 1.25
+        position = PartSpec("interpolated_partial", {"rot_dim": rot, "theta": 5000.0,
+                                                     "factor": factor, "gain": gain})
+        layers = list(base.layers)
+        mixer = dataclasses.replace(layers[1].mixer,
+                                    params={**layers[1].mixer.params, "position": position})
+        layers[1] = dataclasses.replace(layers[1], mixer=mixer, feed_forward=routed)
+        spec = dataclasses.replace(base, layers=tuple(layers))
+        names = expected_tensors(spec)
+        assert "toy.router.weight" in names and "model.layers.1.mlp.up_proj.weight" not in names
+        weights = random_tensors(spec, 11, torch.float32, DEV)
+        host = {k: v.double().cpu() for k, v in weights.items()}
+        runner = ModelRunner(Model(spec, weights, torch.float32, DEV), page_size=4, n_pages=40,
+                             max_requests=3, max_context=64)
+
+        def rotate(x, positions, heads):      # first `rot` dims of each head, pairs (i, i + rot/2)
+            t = x.shape[0]
+            xh = x.reshape(t, heads, hd).clone()
+            i = torch.arange(rot // 2, dtype=torch.float64)
+            freq = torch.tensor(5000.0, dtype=torch.float64) ** (-(2.0 * i) / rot) / factor
+            ang = positions.double()[:, None] * freq[None, :]
+            cos, sin = torch.cos(ang)[:, None, :] * gain, torch.sin(ang)[:, None, :] * gain
+            a, b = xh[..., :rot // 2].clone(), xh[..., rot // 2:rot].clone()
+            xh[..., :rot // 2] = a * cos - b * sin
+            xh[..., rot // 2:rot] = a * sin + b * cos
+            return xh.reshape(t, heads * hd)
+
+        def reference(tokens):
+            xx = P.embed(host["model.embed_tokens.weight"], tokens)
+            pos = torch.arange(len(tokens))
+            xx, _ = P.decoder_layer(xx, pos, host, 0, cfg)
+            p = "model.layers.1."
+            h = P.rms_norm(xx, host[p + "input_layernorm.weight"], cfg["eps"])
+            hq, hkv = cfg["heads"], cfg["kv_heads"]
+            q = P.per_head_norm(P.linear(h, host[p + "self_attn.q_proj.weight"]),
+                                host[p + "self_attn.q_norm.weight"], cfg["eps"], hq)
+            k = P.per_head_norm(P.linear(h, host[p + "self_attn.k_proj.weight"]),
+                                host[p + "self_attn.k_norm.weight"], cfg["eps"], hkv)
+            v = P.linear(h, host[p + "self_attn.v_proj.weight"])
+            a = P.attention(rotate(q, pos, hq), rotate(k, pos, hkv), v, hq, hkv, hd,
+                            cfg["windows"][1], pos)
+            xx = xx + P.linear(a, host[p + "self_attn.o_proj.weight"])
+            h = P.rms_norm(xx, host[p + "post_attention_layernorm.weight"], cfg["eps"])
+            scores = h @ host["toy.router.weight"].T
+            prob = torch.softmax(scores, -1)
+            y = torch.zeros_like(xx)
+            for t in range(len(tokens)):
+                e = int(scores[t].argmax())
+                g = h[t] @ host[f"toy.expert{e}.gate.weight"].T
+                u = h[t] @ host[f"toy.expert{e}.up.weight"].T
+                y[t] = ((g / (1 + torch.exp(-g)) * u) @ host[f"toy.expert{e}.down.weight"].T) * prob[t, e]
+            xx = xx + y
+            return P.linear(P.rms_norm(xx, host["model.norm.weight"], cfg["eps"]),
+                            host["model.embed_tokens.weight"]).numpy()
+
+        a, b = random_tokens("A", 23, 3), random_tokens("A", 9, 4)
+        toks, got = {"a": a, "b": b}, {"a": [], "b": []}
+        plan = [[("a", 0, 7)], [("a", 7, 2), ("b", 0, 8)], [("a", 9, 1), ("b", 8, 1)], [("a", 10, 13)]]
+        for step in plan:
+            entries = [StepEntry(r, toks[r][s:s + n], list(range(n))) for r, s, n in step]
+            out = runner.step(entries).cpu().numpy()
+            at = 0
+            for r, s, n in step:
+                got[r].append(out[at:at + n])
+                at += n
+        ref_a, ref_b = reference(a), reference(b)
+        assert_close(np.concatenate(got["a"]), ref_a, "float32", "toy routed feed-forward a")
+        assert_close(np.concatenate(got["b"]), ref_b, "float32", "toy routed feed-forward b")
+    finally:
+        unregister_part("feed_forward", "top_one_of_two")
+        unregister_part("position", "interpolated_partial")
