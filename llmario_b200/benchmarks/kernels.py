@@ -123,7 +123,8 @@ def cmd_prefill_attention(a) -> None:
     else:
         fn = lambda: kernels.attention_tcgen05(q, out, storage[0, 0, 0], storage[0, 0, 1],
                                                storage.stride(0), table, items, n, Hq, Hkv, hd,
-                                               page, hd ** -0.5, None)
+                                               page, hd ** -0.5, None,
+                                               0 if a.cp_async else storage.shape[0])
     ms = timed(fn, a.reps, None)
     kernels.check_tc_status(DEV)
     flops = 2.0 * T * T * Hq * hd          # causal: half of QK^T and PV
@@ -160,6 +161,8 @@ def main(argv=None) -> int:
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--mma-sync", action="store_true",
                    help="the mma.sync kernel of attention_flash.cu instead of the tcgen05 kernel")
+    p.add_argument("--cp-async", action="store_true",
+                   help="K and V by cp.async copies even where the pages are large enough for TMA")
     p.set_defaults(fn=cmd_prefill_attention)
     for s in (g, d, p):
         s.add_argument("--reps", type=int, default=20)

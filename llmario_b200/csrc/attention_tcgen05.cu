@@ -6,9 +6,10 @@
 //
 //   warp 0     TMA: the Q tile once (a 3-D box over [token][head][dim])
 //   warps 6-9  K and V tiles of the pages named by the block table, as 16-byte cp.async copies
-//              into the 128-byte-swizzled layout the tensor core reads, a ring of three stages
-//              (TMA tile loads of one page are too small: the unit spends ~140 cycles per load
-//              whatever its size, which capped this kernel at a third of its present rate)
+//              into the 128-byte-swizzled layout the tensor core reads, a ring of three stages.
+//              With pages of 32 positions or more warp 0 fetches them by TMA instead (boxes of
+//              64 columns x up to 128 positions, 4 to 16 KB); for smaller pages the TMA unit,
+//              which spends ~140 cycles per box whatever its size, is slower than the copies.
 //   warp 1     one lane issues  S = Q K^T  (A and B from shared memory, K-major) into one of two
 //              TMEM score buffers, and  O += P V  (A = P from TMEM, B = V from shared memory,
 //              N-major); the order is S0, S1, PV0, S2, PV1, ... so the products of one tile
@@ -107,7 +108,8 @@ struct alignas(1024) AttnStorage {
 
 template <int HD>
 __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
-    const __grid_constant__ CUtensorMap map_q, const bf16* __restrict__ k_cache,
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, int tma_kv,
+    long long rows_per_page, int v_row_off, const bf16* __restrict__ k_cache,
     const bf16* __restrict__ v_cache, long long page_stride, bf16* __restrict__ out, const int* __restrict__ block_table, int table_stride,
     const int* __restrict__ items, int Hq, int Hkv, int page_size, float scale_log2, int window,
     int* __restrict__ status) {
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
   if (threadIdx.x == 0) {
     mbar_init(&sm.q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&sm.kv_full[s], 128);        // one arrival per producer thread
+      mbar_init(&sm.kv_full[s], tma_kv ? 1 : 128);   // the TMA thread, or one arrival per producer thread
       mbar_init(&sm.kv_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -150,6 +152,13 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
                  "r"(512u)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tma_kv && warp >= 6) {
+    // TMA brings whole pages; a page without a key of the item is not fetched and leaves what
+    // the stage held.  Such values meet zero weights and must be finite: start from zeros.
+    uint4* v4 = reinterpret_cast<uint4*>(sm.v);
+    for (int i = threadIdx.x - 192; i < KV_STAGES * KT * HD * 2 / 16; i += 128) v4[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -167,8 +176,41 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
 #pragma unroll
       for (int h = 0; h < HALVES; ++h)
         tma_load_3d(sm.q + h * ROWS * 128, &map_q, h * 64, kvh * G, it.row_start, &sm.q_full);
+      if (tma_kv) {
+        // K and V tiles by TMA: one box of 64 columns x R positions per page (or per tile when
+        // a page holds more than a tile), half and operand
+        const int R = page_size < KT ? page_size : KT;
+        const int* table = block_table + (size_t)it.slot * table_stride;
+        bool ok = true;
+        int issued = 0;
+        for (int j = 0; j < ntiles && ok; ++j) {
+          const int s = j % KV_STAGES;
+          ok = mbar_wait(&sm.kv_empty[s], (uint32_t)((j / KV_STAGES) & 1) ^ 1);
+          if (!ok) { atomicExch(status, 5); sm.dead = 1; break; }
+          const int base = (tile_first + j) * KT;
+          uint32_t bytes = 0;
+          for (int p = base; p < base + KT; p += R)
+            if (p <= hi && p + R - 1 >= lo) bytes += (uint32_t)R * HD * 2 * 2;
+          mbar_expect_tx(&sm.kv_full[s], bytes);
+          for (int p = base; p < base + KT; p += R) {
+            if (p > hi || p + R - 1 < lo) continue;      // no key of the item here: the page may be gone
+            const long long row = (long long)table[p / page_size] * rows_per_page + (long long)kvh * page_size +
+                                  p % page_size;
+            const int dst = (p - base) * 128;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+              tma_load_2d(sm.k[s] + h * KT * 128 + dst, &map_kv, h * 64, (int)row, &sm.kv_full[s]);
+              tma_load_2d(sm.v[s] + h * KT * 128 + dst, &map_kv, h * 64, (int)(row + v_row_off), &sm.kv_full[s]);
+            }
+          }
+          issued = j + 1;
+        }
+        if (!ok)      // let what is in flight land before the shared memory is given up
+          for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
+            mbar_wait(&sm.kv_full[j % KV_STAGES], (uint32_t)((j / KV_STAGES) & 1));
+      }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 6 && !tma_kv) {
     // ------------------------------------------------------------------ K and V tiles
     // Thread p of the 128 copies the 16-byte piece (p % CPR) of rows (p / CPR), + 128 / CPR, ...
     // of every tile: its column and its row inside a group of eight never change, so the
@@ -437,7 +479,8 @@ bool q_tensor_map(const void* q, int rows, int Hq, int hd, int G, CUtensorMap* o
 }
 
 template <int HD>
-int launch(const CUtensorMap& mq, const bf16* kc, const bf16* vc, long long page_stride, bf16* out,
+int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long rows_per_page, int v_row_off,
+           const bf16* kc, const bf16* vc, long long page_stride, bf16* out,
            const int* table, int table_stride, const int* items, int n_items, int Hq, int Hkv, int page_size,
            float scale, int window, int* status, cudaStream_t s) {
   auto kernel = attention_tcgen05_kernel<HD>;
@@ -449,16 +492,19 @@ int launch(const CUtensorMap& mq, const bf16* kc, const bf16* vc, long long page
     configured = true;
   }
   dim3 grid(n_items, Hkv);
-  return launch_pdl(kernel, grid, 320, smem, s, mq, kc, vc, page_stride, out, table, table_stride, items, Hq, Hkv,
-                    page_size, scale * 1.4426950408889634f, window, status);
+  return launch_pdl(kernel, grid, 320, smem, s, mq, mkv, tma_kv, rows_per_page, v_row_off, kc, vc, page_stride, out,
+                    table, table_stride, items, Hq, Hkv, page_size, scale * 1.4426950408889634f, window, status);
 }
 }  // namespace
 
 // q, out: [rows][Hq * hd] bfloat16; k_cache / v_cache: this layer call's K and V planes of page 0 in a
 // cache [page][...][kv head][position][head dim] with `page_stride` elements from page to page;
 // items: n_items x (first row, tokens <= 128 / (Hq / Hkv), request slot, first position).
+// n_pages: pages of the cache; when positive and the pages hold a power of two of at least 32
+// positions, K and V are fetched by TMA, else (or with n_pages 0) by cp.async copies.
 LLM_EXPORT int llm_attention_tcgen05(const void* q, void* out, int rows, const void* k_cache,
-                                     const void* v_cache, long long page_stride, const int* block_table,
+                                     const void* v_cache, long long page_stride, long long n_pages,
+                                     const int* block_table,
                                      int table_stride, const int* items, int n_items, int Hq, int Hkv,
                                      int hd, int page_size, float scale, int window, int* status,
                                      cudaStream_t stream) {
@@ -470,9 +516,24 @@ LLM_EXPORT int llm_attention_tcgen05(const void* q, void* out, int rows, const v
   if ((page_stride * 2) % 16) return LLM_ERR_UNSUPPORTED;
   CUtensorMap mq;
   if (!q_tensor_map(q, rows, Hq, hd, G, &mq)) return LLM_ERR_UNSUPPORTED;
+  // The cache seen from this layer call's K plane as rows of hd elements: page p, KV head h,
+  // position i is row p * rows_per_page + h * page_size + i; the V plane lies v_row_off rows on.
+  CUtensorMap mkv = mq;
+  int tma_kv = 0, v_row_off = 0;
+  long long rows_per_page = 0;
+  const long long v_off = (const bf16*)v_cache - (const bf16*)k_cache;
+  if (n_pages > 0 && page_size >= 32 && (page_size & (page_size - 1)) == 0 && page_stride % hd == 0 &&
+      v_off > 0 && v_off % hd == 0 && n_pages * (page_stride / hd) < (1LL << 31)) {
+    rows_per_page = page_stride / hd;
+    v_row_off = (int)(v_off / hd);
+    tma_kv = llm_tensor_map(k_cache, n_pages * rows_per_page, hd, hd, page_size < KT ? page_size : KT, 64, 0, &mkv)
+                 ? 1 : 0;
+  }
   if (hd == 128)
-    return launch<128>(mq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, (bf16*)out, block_table,
-                       table_stride, items, n_items, Hq, Hkv, page_size, scale, window, status, stream);
-  return launch<64>(mq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, (bf16*)out, block_table,
-                    table_stride, items, n_items, Hq, Hkv, page_size, scale, window, status, stream);
+    return launch<128>(mq, mkv, tma_kv, rows_per_page, v_row_off, (const bf16*)k_cache, (const bf16*)v_cache,
+                       page_stride, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size, scale,
+                       window, status, stream);
+  return launch<64>(mq, mkv, tma_kv, rows_per_page, v_row_off, (const bf16*)k_cache, (const bf16*)v_cache,
+                    page_stride, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size, scale,
+                    window, status, stream);
 }

@@ -57,7 +57,7 @@ def _signatures():
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
         "llm_attention_decode_tma": [P, P, P, P, P, L, I, I, P, I, P, P, P, I, I, I, I, I, F, I,
                                      I, P, P],
-        "llm_attention_tcgen05": [P, P, I, P, P, L, P, I, P, I, I, I, I, I, F, I, P, P],
+        "llm_attention_tcgen05": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
 
@@ -471,14 +471,17 @@ def attention_decode_tma(q: torch.Tensor, out: torch.Tensor, storage: torch.Tens
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       v_cache: torch.Tensor, page_stride: int, block_table: torch.Tensor,
                       items: torch.Tensor, n_items: int, num_heads: int, num_kv_heads: int,
-                      head_dim: int, page_size: int, scale: float, window: Optional[int]) -> None:
+                      head_dim: int, page_size: int, scale: float, window: Optional[int],
+                      n_pages: int = 0) -> None:
     """Attention of prompt portions on tcgen05: items of at most 128 / (heads per KV head)
-    tokens; scores and output accumulate in tensor memory."""
+    tokens; scores and output accumulate in tensor memory.  ``n_pages``: pages of the cache that
+    ``k_cache`` / ``v_cache`` are planes of; given it, pages of 32 positions or more are
+    fetched by TMA."""
     _cuda(q, out, k_cache, v_cache, block_table, items)
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
     assert q.is_contiguous() and out.is_contiguous()
     _check(lib().llm_attention_tcgen05(
-        _ptr(q), _ptr(out), q.shape[0], _ptr(k_cache), _ptr(v_cache), page_stride,
+        _ptr(q), _ptr(out), q.shape[0], _ptr(k_cache), _ptr(v_cache), page_stride, int(n_pages),
         _ptr(block_table), block_table.stride(0), _ptr(items), n_items, num_heads, num_kv_heads,
         head_dim, page_size, float(scale), int(window or 0), _ptr(tc_status(q.device)),
         _stream()), f"attention_tcgen05 (head_dim {head_dim})")
@@ -563,8 +566,10 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
             attention_merge(part_o, part_ml, out, plan.small_rows, plan.n_small, num_heads,
                             head_dim, splits)
     if plan.n_large and tc:
+        storage = getattr(view, "storage", None)
         attention_tcgen05(q, out, *common, plan.large, plan.n_large, num_heads, num_kv_heads,
-                          head_dim, view.page_size, scale, window)
+                          head_dim, view.page_size, scale, window,
+                          storage.shape[0] if storage is not None else 0)
     elif plan.n_large:
         attention_flash(q, out, *common, plan.large, plan.n_large, 64, num_heads, num_kv_heads,
                         head_dim, view.page_size, scale, window)

@@ -441,7 +441,9 @@ def test_attention_decode(Hq, Hkv, hd, page, window, tma):
 
 @pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (4, 4, 64, 8, 70),
                                                    (16, 2, 128, 32, None), (2, 2, 64, 64, None),
-                                                   (32, 8, 128, 16, 300), (8, 4, 128, 4, None)])
+                                                   (32, 8, 128, 16, 300), (8, 4, 128, 4, None),
+                                                   (8, 2, 128, 64, 200), (4, 2, 64, 128, None),
+                                                   (8, 8, 128, 256, None)])
 def test_attention_tcgen05(Hq, Hkv, hd, page, window):
     """The tcgen05 kernel for prompt portions: items of up to 128 / G tokens at the end of a long
     request (several key tiles, the diagonal tile, a window's edge), short items, and an item at
@@ -468,11 +470,14 @@ def test_attention_tcgen05(Hq, Hkv, hd, page, window):
     qd = q.reshape(len(rows), -1).to(DEV).contiguous()
     out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
     dev_items = torch.tensor(items, dtype=torch.int32, device=DEV).reshape(-1)
-    kernels.attention_tcgen05(qd, out, storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table,
-                              dev_items, len(items), Hq, Hkv, hd, page, scale, window)
-    kernels.check_tc_status(DEV)
-    for i, (r, p) in enumerate(rows):
-        ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
-        got = out[i].reshape(Hq, hd).double().cpu()
-        assert torch.isfinite(got).all(), (i, r, p)
-        assert (got - ref).abs().max() <= 2e-2, (i, r, p, (got - ref).abs().max())
+    # with the number of pages given, pages of 32 positions or more come by TMA; without, by copies
+    for n_pages in (storage.shape[0], 0):
+        out.zero_()
+        kernels.attention_tcgen05(qd, out, storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table,
+                                  dev_items, len(items), Hq, Hkv, hd, page, scale, window, n_pages)
+        kernels.check_tc_status(DEV)
+        for i, (r, p) in enumerate(rows):
+            ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
+            got = out[i].reshape(Hq, hd).double().cpu()
+            assert torch.isfinite(got).all(), (i, r, p)
+            assert (got - ref).abs().max() <= 2e-2, (i, r, p, (got - ref).abs().max())

@@ -17,12 +17,12 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def run_in_process(name, dtype, steps, max_tokens, max_requests=8):
+def run_in_process(name, dtype, steps, max_tokens, max_requests=8, page=None):
     """Drive the engine's own step function the way bin/trace_run does."""
     from llmario_b200.engine import Model, ModelRunner, StepEntry
 
     model = Model.from_folder(model_dir(name, dtype), dtype, "cuda:0")
-    page = TINY[name]["page_size"]
+    page = page or TINY[name]["page_size"]
     n_pages = -(-max_tokens // page)
     runner = ModelRunner(model, page_size=page, n_pages=n_pages, max_requests=max_requests,
                          max_context=min(model.spec.max_positions, n_pages * page))
@@ -66,6 +66,25 @@ def test_mixed_with_page_reuse(name, dtype):
     # so few pages that they are used again: more were handed out than the pool holds
     assert runner.cache.counters["pages_allocated"] > runner.cache.groups[0].n_pages
     assert runner.cache.counters["pages_allocated"] >= total
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("page", [32, 64])
+def test_larger_pages(page, dtype):
+    """Config D (head size 64, four heads per KV head, a window on one layer) with pages of 32
+    and 64 positions: in bfloat16 these are fetched by TMA in the attention of prompt portions
+    and in decode attention.  Portions of changing size, then a mixed batch with pages used
+    again."""
+    name = "D"
+    reqs = requests_for(name, (45, 170, 300), seed=7)
+    steps = traces.portions(reqs)
+    out, _ = run_in_process(name, dtype, steps, traces.peak_tokens(steps), page=page)
+    traces.check(steps, out, reqs, name, dtype, f"{name} {dtype} portions, pages of {page}")
+    reqs = requests_for(name, (40, 23, 75, 7, 1, 110, 64, 33, 90), seed=11)
+    steps = traces.mixed(reqs, live=4, seed=3)
+    out, runner = run_in_process(name, dtype, steps, traces.peak_tokens(steps), page=page)
+    traces.check(steps, out, reqs, name, dtype, f"{name} {dtype} mixed, pages of {page}")
+    assert runner.cache.counters["pages_allocated"] > runner.cache.groups[0].n_pages
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
