@@ -215,7 +215,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--page-size", type=int, default=32)
+    ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     args = ap.parse_args()

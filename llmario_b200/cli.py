@@ -68,7 +68,7 @@ def _common(p: argparse.ArgumentParser) -> None:
     p.add_argument("--context", "--ctx", type=int, default=None,
                    help="per-request context tokens (default: the model's)")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
-    p.add_argument("--page-size", type=int, default=32, help="tokens in a cache page")
+    p.add_argument("--page-size", type=int, default=64, help="tokens in a cache page")
     p.add_argument("--batch", type=int, default=512, help="token budget of one step")
     p.add_argument("--weights-seed", type=int, default=0,
                    help="seed of the random weights when the model is a preset name")

@@ -371,11 +371,14 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
         m_used = m_tile;
         l *= factor;
       }
-      if (j > 0) {
-        // the product P V of the tile before must be complete before O is touched
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // Rare once the maximum has settled: the rows of this warp in O are rescaled.  Only then
+        // must the product P V of the tile before be complete (it writes O); otherwise the
+        // exponentials below run while it is still going.  (That product cannot be more than
+        // one phase behind: it needs this warp's P of the tile before.)
         bool done = mbar_wait(&sm.o_done, (uint32_t)((j - 1) & 1));
         if (!done) { if (lane == 0) atomicExch(status, 7); sm.dead = 1; }
-        if (__any_sync(0xffffffffu, grow)) {
+        {
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < HD; c += 32) {

@@ -30,7 +30,7 @@ class _Launched:
 
 class Engine:
     def __init__(self, model: Union[str, Model, None] = None, *, config=None, seed: int = 0,
-                 dtype="bfloat16", device: str = "cuda:0", page_size: int = 32,
+                 dtype="bfloat16", device: str = "cuda:0", page_size: int = 64,
                  num_pages: Optional[int] = None, cache_tokens: Optional[int] = None,
                  token_budget: int = 512, max_requests: int = 64,
                  context: Optional[int] = None, num_layers: Optional[int] = None,

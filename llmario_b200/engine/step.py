@@ -46,7 +46,7 @@ GRAPH_UPDATES_PER_ROW = 4      # room for block-table changes per row in a recor
 class ModelRunner:
     """Owns the model, its cache and the per-step device buffers."""
 
-    def __init__(self, model: Model, page_size: int = 32, n_pages: Optional[int] = None,
+    def __init__(self, model: Model, page_size: int = 64, n_pages: Optional[int] = None,
                  max_requests: int = 64, max_context: Optional[int] = None,
                  token_budget: int = 2048, cache_tokens: Optional[int] = None,
                  use_graphs: bool = True):

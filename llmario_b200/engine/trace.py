@@ -30,7 +30,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each request's "
                          "count rounded up to a multiple of 64)")
-    ap.add_argument("--page-size", type=int, default=32, help="tokens in a cache page")
+    ap.add_argument("--page-size", type=int, default=64, help="tokens in a cache page")
     ap.add_argument("--max-requests", type=int, default=8, help="request slots")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)

@@ -374,7 +374,8 @@ def test_attention_flash(Hq, Hkv, hd, page, window):
 
 @pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (6, 3, 64, 8, 50),
                                                    (4, 4, 32, 4, None), (8, 1, 128, 16, 200),
-                                                   (3, 1, 64, 32, None), (32, 8, 128, 16, None)])
+                                                   (3, 1, 64, 32, None), (32, 8, 128, 16, None),
+                                                   (8, 2, 128, 64, None), (4, 4, 64, 128, 100)])
 @pytest.mark.parametrize("tma", [False, True])
 def test_attention_decode(Hq, Hkv, hd, page, window, tma):
     """The decode kernels (keys on the M side; loads by cp.async or by TMA tiles): one-token
