@@ -5,9 +5,10 @@
 
 A "step" is one decode step of a batch of requests.  The default run has the layer sizes of
 Qwen3-8B with seeded random bfloat16 weights, 8 requests with 1,024-token prompts of uniform
-random ids, context 8,192, pages of 16 tokens.  ``value`` is decoded tokens per second timed on
-the device around K consecutive steps of the step function plus the sampling kernel; ``e2e`` is
-the same through ``Engine.step`` with host token lists in and out.  The weights (about 15 GB)
+random ids, context 8,192, pages of 16 tokens (the named configuration).  ``value`` is decoded
+tokens per second timed on the device around K consecutive steps of the step function plus the
+sampling kernel; ``e2e`` is the same through ``Engine.step`` with host token lists in and out.
+``engine_page`` repeats prefill, ``value`` and ``e2e`` with the engine's default page of 64 tokens.  The weights (about 15 GB)
 are larger than the L2 cache, so no flush is needed between steps.
 """
 from __future__ import annotations
@@ -215,7 +216,10 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--page-size", type=int, default=16,
+                    help="tokens in a cache page for the headline numbers (the named configuration "
+                         "has 16; the engine's own default, 64, is measured too and reported "
+                         "under `engine_page`)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     args = ap.parse_args()
@@ -273,6 +277,23 @@ def main() -> int:
             k = min(steps, 64)
             pms, _, _ = decode_bench(runner, sampler, model, b, args.prompt_len, k, warmup, rng)
             points[f"decode_b{b}"] = b / (pms / 1e3)
+    # the same with the page size the engine uses when it is not told one
+    engine_page = None
+    own = Engine.__init__.__kwdefaults__["page_size"]
+    if own != args.page_size and not args.skip_points:
+        del engine, runner
+        torch.cuda.empty_cache()
+        per_req = args.prompt_len + warmup + steps + own
+        eng2 = Engine(model, page_size=own,
+                      cache_tokens=max(args.batch * per_req, args.prefill_tokens + own),
+                      token_budget=max(2048, args.prefill_tokens), max_requests=args.batch,
+                      context=args.context)
+        p_ms = prefill_bench(eng2.runner, model, args.prefill_tokens, rng)
+        d_ms, _, _ = decode_bench(eng2.runner, sampler, model, args.batch, args.prompt_len, steps,
+                                  warmup, rng)
+        e2 = e2e_bench(eng2, args.batch, args.prompt_len, steps, warmup, rng)
+        engine_page = {"page_size": own, "value": args.batch / (d_ms / 1e3), "ms_per_step": d_ms,
+                       "e2e": e2, "prefill_value": T / (p_ms / 1e3), "prefill_ms": p_ms}
 
     line = {
         "metric": "decode tok/s at batch %d (Qwen3-8B sizes, random bf16 weights); prefill and "
@@ -288,17 +309,20 @@ def main() -> int:
                    "context": args.context, "page_size": args.page_size,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 15 GB)",
                    "peaks": pk["source"]},
-        # per step the engine copies one int32 array (header, token id, position, request slot
-        # and wanted row per request, block-table changes) and the sampler's options
+        # per step the engine copies one int32 array (header, token id, position, request slot,
+        # wanted row and the index of the token drawn on the device per request, block-table
+        # changes) and the sampler's options
         # (10 float32 words per row capacity of 64), and reads back one token id per request
         "e2e": {"value": e2e, "unit": "tokens/s",
-                "h2d_bytes_per_step": 4 * (16 + 4 * ((args.batch + 3) // 4 * 4)) + 4 * 10 * 64,
+                "h2d_bytes_per_step": 4 * (16 + 5 * ((args.batch + 3) // 4 * 4)) + 4 * 10 * 64,
                 "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": launches, "clocks": clk, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},
         "points": points,
     }
+    if engine_page:
+        line["engine_page"] = engine_page
     print(json.dumps(line))
     return 0
 
