@@ -163,7 +163,9 @@ def e2e_bench(engine, batch, prompt_len, steps, warmup, rng):
     from llmario_b200.sampling import SamplingParams
 
     vocab = engine.model.vocab_size
-    params = SamplingParams(temperature=0.0, max_tokens=warmup + steps + 1, ignore_eos=True)
+    # (no request may end inside the timed region: the first ones to finish their prompts decode
+    # while the others are still being prefilled, so they are ahead by a few tokens)
+    params = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
     ids = [engine.add_request([rng.randrange(vocab) for _ in range(prompt_len)], params)
            for _ in range(batch)]
     while not all(engine.request(i).output for i in ids):
@@ -244,10 +246,14 @@ def main() -> int:
     rng = random.Random(0)
     model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     max_batch = args.batch if args.skip_points else max(args.batch, 64)
-    per_req = args.prompt_len + warmup + steps + args.page_size
+    budget = max(2048, args.prefill_tokens)
+    # room for the prompt, the decoded tokens and the tokens a request decodes while the prompts
+    # of the others are still being prefilled
+    ahead = args.batch * -(-args.prompt_len // budget) + 2
+    per_req = args.prompt_len + warmup + steps + ahead + args.page_size
     cache_tokens = max(max_batch * per_req, args.prefill_tokens + args.page_size)
     engine = Engine(model, page_size=args.page_size, cache_tokens=cache_tokens,
-                    token_budget=max(2048, args.prefill_tokens), max_requests=max_batch,
+                    token_budget=budget, max_requests=max_batch,
                     context=args.context)
     runner = engine.runner
     sampler = DeviceSampler(model.device)
@@ -283,10 +289,10 @@ def main() -> int:
     if own != args.page_size and not args.skip_points:
         del engine, runner
         torch.cuda.empty_cache()
-        per_req = args.prompt_len + warmup + steps + own
+        per_req = args.prompt_len + warmup + steps + ahead + own
         eng2 = Engine(model, page_size=own,
                       cache_tokens=max(args.batch * per_req, args.prefill_tokens + own),
-                      token_budget=max(2048, args.prefill_tokens), max_requests=args.batch,
+                      token_budget=budget, max_requests=args.batch,
                       context=args.context)
         p_ms = prefill_bench(eng2.runner, model, args.prefill_tokens, rng)
         d_ms, _, _ = decode_bench(eng2.runner, sampler, model, args.batch, args.prompt_len, steps,
