@@ -80,22 +80,32 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[Any, torch.Tensor] = {}     # (name, dtype, shape) -> view of the buffer
         self.generation = 0     # grows whenever a buffer moves: recorded launches are stale then
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype, zero: bool = False
             ) -> torch.Tensor:
         """``zero``: the buffer is created holding zeros (its users keep it that way)."""
+        key = (name, dtype, tuple(shape))
+        view = self._views.get(key)
+        if view is not None:
+            return view
         n = 1
         for d in shape:
             n *= int(d)
-        key = (name, dtype)
-        buf = self._bufs.get(key)
+        buf = self._bufs.get((name, dtype))
         if buf is None or buf.numel() < n:
             make = torch.zeros if zero else torch.empty
             buf = make(max(n, 1), dtype=dtype, device=self.device)
-            self._bufs[key] = buf
+            self._bufs[(name, dtype)] = buf
             self.generation += 1
-        return buf[:n].view(*shape)
+            # views of the buffer that was replaced are stale
+            self._views = {k: v for k, v in self._views.items() if k[:2] != (name, dtype)}
+        view = buf[:n].view(*shape)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[key] = view
+        return view
 
 
 @dataclass
