@@ -69,14 +69,14 @@ def test_mixed_with_page_reuse(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("page", [32, 64])
-def test_larger_pages(page, dtype):
-    """Config D (head size 64, four heads per KV head, a window on one layer) with pages of 32
-    and 64 positions: in bfloat16 these are fetched by TMA in the attention of prompt portions
-    and in decode attention.  Portions of changing size, then a mixed batch with pages used
-    again."""
-    name = "D"
-    reqs = requests_for(name, (45, 170, 300), seed=7)
+@pytest.mark.parametrize("name,page", [("D", 32), ("D", 64), ("A", 64), ("B", 64), ("C", 64)])
+def test_larger_pages(name, page, dtype):
+    """Pages of 32 and 64 positions (64 is what the engine and bin/trace_run use when they are
+    not told a size).  With config D (head size 64, four heads per KV head, a window on one
+    layer) in bfloat16 they are fetched by TMA in the attention of prompt portions and in decode
+    attention; the other configurations take the kernels for other head sizes.  Portions of
+    changing size, then a mixed batch with pages used again."""
+    reqs = requests_for(name, (45, 170, 300) if name == "D" else (45, 97, 130), seed=7)
     steps = traces.portions(reqs)
     out, _ = run_in_process(name, dtype, steps, traces.peak_tokens(steps), page=page)
     traces.check(steps, out, reqs, name, dtype, f"{name} {dtype} portions, pages of {page}")
