@@ -440,6 +440,85 @@ def test_attention_decode(Hq, Hkv, hd, page, window, tma):
         check(rows, out, q)
 
 
+@pytest.mark.parametrize("page,window", [(16, None), (64, None), (16, 200), (64, 130)])
+@pytest.mark.parametrize("kernel", ["decode", "decode_tma", "tcgen05"])
+def test_tensor_core_attention_finds_the_key_that_stands_out(kernel, page, window):
+    """Random keys would hide a tile, a page or a window's edge read wrongly.  Here single keys
+    are made to dominate single query rows: far back among hundreds, on the last and the first
+    slot of a page, on both sides of the edge between key tiles, on the first key a window still
+    sees and (it must have no weight) on the last one it no longer sees.  The row's output must
+    be that key's value."""
+    from llmario_b200 import kernels
+    Hq, Hkv, hd, n = 8, 2, 128, 700
+    G = Hq // Hkv
+    dtype = torch.bfloat16
+    storage, table, ks, vs = paged_setup([n], page, Hkv, hd, dtype, seed=4)
+    scale = 1 / math.sqrt(hd)
+    last = n - 1
+    lo = max(0, last + 1 - window) if window else 0
+    targets = [t for t in (13, page - 1, page, 127, 128, 511, 512, 639, 640, last - 1, last) if t >= lo]
+    if window:
+        targets += [lo, lo + 1, lo - 1]          # lo - 1 is outside the window of the last position
+    cap = 128 // G if kernel == "tcgen05" else 1
+    # rows: for the decode kernels one row per target, all at the last position; for the prompt
+    # kernel one item of `cap` tokens that ends at the last position, a target for each of its
+    # last rows (a row sees a target only if it lies at or before its own position)
+    g = torch.Generator().manual_seed(9)
+    if kernel == "tcgen05":
+        rows = [(0, last - cap + 1 + i) for i in range(cap)]
+        aim = {cap - 1 - j: t for j, t in enumerate(targets) if t <= last - j and
+               (not window or t >= last - j + 1 - window or t == lo - 1)}
+    else:
+        rows = [(0, last)] * len(targets)
+        aim = dict(enumerate(targets))
+    q = torch.randn(len(rows), Hq, hd, generator=g)
+    k = ks[0].float()
+    for i, t in aim.items():      # head 0 of row i points at key t of KV head 0
+        u = q[i, 0] / q[i, 0].norm()
+        k[t, 0] = 60 * u
+    ks[0] = k.to(dtype)
+    for t in set(aim.values()):
+        pg, sl = table[0, t // page].item(), t % page
+        storage[pg, 1, 0, 0, sl] = ks[0][t, 0].to(DEV)
+    q = q.to(dtype)
+    qd = q.reshape(len(rows), -1).to(DEV).contiguous()
+    out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
+    common = (storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table)
+    if kernel == "tcgen05":
+        items = torch.tensor([[0, cap, 0, rows[0][1]]], dtype=torch.int32, device=DEV).reshape(-1)
+        kernels.attention_tcgen05(qd, out, *common, items, 1, Hq, Hkv, hd, page, scale, window,
+                                  storage.shape[0])
+    else:
+        slot = torch.zeros(len(rows), dtype=torch.int32, device=DEV)
+        pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+        splits = 3
+        po = torch.empty(len(rows) * Hq * splits * hd, dtype=torch.float32, device=DEV)
+        pml = torch.empty(len(rows) * Hq * splits * 2, dtype=torch.float32, device=DEV)
+        if kernel == "decode_tma":
+            kernels.attention_decode_tma(qd, out, storage, 1, table, None, len(rows), Hq, Hkv, hd,
+                                         page, scale, window, splits, po, pml, slot, pos)
+        else:
+            kernels.attention_decode(qd, out, *common, None, len(rows), Hq, Hkv, hd, page, scale,
+                                     window, splits, po, pml, slot, pos)
+        kernels.attention_merge(po, pml, out, None, len(rows), Hq, hd, splits)
+    kernels.check_tc_status(DEV)
+    seen = 0
+    for i, (r, p) in enumerate(rows):
+        ref = attention_ref(q[i].float(), ks[0].float(), vs[0].float(), p, window, scale)
+        got = out[i].reshape(Hq, hd).double().cpu()
+        assert (got - ref).abs().max() <= 2e-2, (i, p, aim.get(i), (got - ref).abs().max())
+        t = aim.get(i)
+        if t is None:
+            continue
+        row_lo = max(0, p + 1 - window) if window else 0
+        if row_lo <= t <= p:      # visible: the output of head 0 is the value at the target
+            assert (got[0] - vs[0][t, 0].double()).abs().max() < 2e-2, (i, p, t)
+            seen += 1
+        else:                     # outside the window: it has no weight at all
+            assert (got[0] - vs[0][t, 0].double()).abs().max() > 0.5, (i, p, t)
+    assert seen >= 5
+
+
 @pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (4, 4, 64, 8, 70),
                                                    (16, 2, 128, 32, None), (2, 2, 64, 64, None),
                                                    (32, 8, 128, 16, 300), (8, 4, 128, 4, None),
