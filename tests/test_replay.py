@@ -88,6 +88,23 @@ def test_larger_pages(name, page, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_no_tensor_core_path_takes(dtype):
+    """Config E: a width of 100, a feed-forward size of 76, five query heads on one KV head, a
+    vocabulary of 333.  The products and the attention fall back to kernels that take these
+    sizes; the logits are right all the same."""
+    name = "E"
+    reqs = requests_for(name, (45, 97, 130), seed=7)
+    for mode in ("whole", "bulk_then_tail", "portions"):
+        steps = getattr(traces, mode)(reqs)
+        out, _ = run_in_process(name, dtype, steps, traces.peak_tokens(steps))
+        traces.check(steps, out, reqs, name, dtype, f"{name} {dtype} {mode}")
+    reqs = requests_for(name, (40, 23, 75, 7, 1, 110, 64, 33, 90), seed=11)
+    steps = traces.mixed(reqs, live=4, seed=3)
+    out, _ = run_in_process(name, dtype, steps, traces.peak_tokens(steps))
+    traces.check(steps, out, reqs, name, dtype, f"{name} {dtype} mixed")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(dtype):
     """The program itself: standard input to files, `done` lines, exit code."""
     name = "B"

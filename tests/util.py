@@ -38,6 +38,12 @@ TINY = {
               rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=2048,
               use_sliding_window=True, sliding_window=150,
               layer_types=["full_attention", "sliding_attention"], page_size=16, seed=4),
+    # E has sizes that no tensor-core path takes as they are: a width and a feed-forward size
+    # that are no multiple of eight, five query heads on one KV head, an odd vocabulary
+    "E": dict(num_hidden_layers=2, hidden_size=100, num_attention_heads=5, num_key_value_heads=1,
+              head_dim=32, intermediate_size=76, vocab_size=333, rope_theta=777.0,
+              rms_norm_eps=2e-5, tie_word_embeddings=False, max_position_embeddings=512,
+              use_sliding_window=False, sliding_window=None, page_size=8, seed=6),
 }
 
 
