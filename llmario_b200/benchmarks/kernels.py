@@ -132,6 +132,39 @@ def cmd_prefill_attention(a) -> None:
           f"{flops / ms / 1e9:.1f} TFLOP/s (causal flops)")
 
 
+def cmd_step(a) -> None:
+    """Decode steps of a whole model, for a list of the kernels a step launches: prompts are
+    prefilled, then ``--steps`` decode steps run between cudaProfilerStart and cudaProfilerStop."""
+    import random
+
+    from ..cli import preset_config
+    from ..engine import Model, ModelRunner, StepEntry
+
+    model = Model.random(preset_config(a.model, a.layers), 0, "bfloat16", DEV)
+    runner = ModelRunner(model, page_size=a.page_size, cache_tokens=a.batch * (a.context + 256),
+                         max_requests=max(a.batch, 8), max_context=8192, use_graphs=not a.eager)
+    rng, vocab = random.Random(0), model.vocab_size
+    for i in range(a.batch):
+        runner.step([StepEntry(i, [rng.randrange(vocab) for _ in range(a.context)], [])])
+
+    def decode():
+        runner.step([StepEntry(i, [rng.randrange(vocab)], [0]) for i in range(a.batch)])
+
+    for _ in range(3):
+        decode()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()          # for a profiler run with --profile-from-start off
+    start.record()
+    for _ in range(a.steps):
+        decode()
+    end.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(f"decode step {a.model} layers={len(model.blocks)} "
+          f"batch={a.batch} context={a.context}: {start.elapsed_time(end) / a.steps * 1e3:.1f} us/step")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -164,6 +197,15 @@ def main(argv=None) -> int:
     p.add_argument("--cp-async", action="store_true",
                    help="K and V by cp.async copies even where the pages are large enough for TMA")
     p.set_defaults(fn=cmd_prefill_attention)
+    st = sub.add_parser("step")
+    st.add_argument("--model", default="qwen3-8b")
+    st.add_argument("--layers", type=int, default=None)
+    st.add_argument("--batch", type=int, default=8)
+    st.add_argument("--context", type=int, default=1024)
+    st.add_argument("--steps", type=int, default=4)
+    st.add_argument("--page-size", type=int, default=16)
+    st.add_argument("--eager", action="store_true", help="no CUDA graphs")
+    st.set_defaults(fn=cmd_step)
     for s in (g, d, p):
         s.add_argument("--reps", type=int, default=20)
         s.add_argument("--no-flush", action="store_true")
