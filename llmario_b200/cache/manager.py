@@ -13,17 +13,23 @@ table.  A group whose layers only look back ``window`` keys gives a page back as
 key in it is out of reach of any later query.  Fixed-size state lives in one tensor per
 run-order entry, indexed by the request's slot.
 
-All bookkeeping is host-side Python and runs without a GPU; storage is allocated separately by
-:meth:`CacheManager.allocate_storage`.
+The bookkeeping itself (free pages, the pages of every request, what a window has passed, which
+table cells have changed) is C++ (``csrc/host/cache_core.cpp``, compiled by the system's C++
+compiler on first use, no GPU needed); this module owns the device tensors, names requests by
+whatever hashable id the caller uses, and turns the core's codes into exceptions.  Storage is
+allocated separately by :meth:`CacheManager.allocate_storage`.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
+import itertools
 from dataclasses import dataclass, field
-from typing import Any, Deque, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
+
+from ..csrc.build import load_host_library
 
 
 class CacheFull(Exception):
@@ -57,36 +63,93 @@ class FixedState:
     dtype: torch.dtype = torch.float32
 
 
+_lib = None
+
+
+def _core():
+    """The host library with its functions declared."""
+    global _lib
+    if _lib is None:
+        l = load_host_library()
+        P, I, K = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+        IP = ctypes.POINTER(ctypes.c_int)
+        sigs = {
+            "llm_cache_new": (P, [I, IP, IP, I, I, I, I]),
+            "llm_cache_delete": (None, [P]),
+            "llm_cache_open": (I, [P, K]),
+            "llm_cache_has": (I, [P, K]),
+            "llm_cache_info": (I, [P, K, IP, IP]),
+            "llm_cache_info_many": (I, [P, I, P, P, P]),
+            "llm_cache_free_slots": (I, [P]),
+            "llm_cache_free_pages": (None, [P, IP]),
+            "llm_cache_pages_needed": (I, [P, K, I, IP]),
+            "llm_cache_reserve": (I, [P, I, P, P, IP]),
+            "llm_cache_advance": (I, [P, K, I]),
+            "llm_cache_truncate": (I, [P, K, I, IP]),
+            "llm_cache_close": (I, [P, K]),
+            "llm_cache_pending_updates": (I, [P, I]),
+            "llm_cache_take_updates": (I, [P, I, P]),
+            "llm_cache_take_fresh": (I, [P, IP, I]),
+            "llm_cache_pages_of": (I, [P, K, I, IP, I]),
+            "llm_cache_live": (I, [P, P, I]),
+            "llm_cache_counters": (None, [P, P]),
+            "llm_cache_check": (I, [P, IP]),
+            "llm_pool_new": (P, [I]),
+            "llm_pool_delete": (None, [P]),
+            "llm_pool_free": (I, [P]),
+            "llm_pool_held": (I, [P]),
+            "llm_pool_alloc": (I, [P, I, IP]),
+            "llm_pool_release": (I, [P, IP, I]),
+        }
+        for name, (res, args) in sigs.items():
+            fn = getattr(l, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = l
+    return _lib
+
+
+# what the core's negative codes mean (csrc/host/cache_core.cpp)
+_E_UNKNOWN, _E_OPEN_TWICE, _E_NO_SLOT, _E_TWICE, _E_EMPTY, _E_CONTEXT = -1, -2, -3, -4, -5, -6
+_E_PAST, _E_LENGTHEN, _E_STATE, _E_WINDOW, _E_NOT_HELD = -7, -8, -9, -10, -11
+_CHECK = {-20: "a page is held twice", -21: "a page is both free and held",
+          -22: "a page is in the free queue twice", -23: "pages lost",
+          -24: "the pool's own count of held pages is off",
+          -25: "a request slot is held twice or both free and held",
+          -26: "a request slot was lost"}
+
+
 class PagePool:
     """Page ids 0..n-1.  ``alloc`` is all-or-nothing; a freed page goes to the back of the
     queue, so the page freed longest ago is handed out first (lib.rs:36-128)."""
 
     def __init__(self, n_pages: int):
         self.n_pages = n_pages
-        self._free: Deque[int] = deque(range(n_pages))
-        self._held = [False] * n_pages
+        self._p = _core().llm_pool_new(n_pages)
+        if not self._p:
+            raise CacheError("a pool needs at least one page")
+
+    def __del__(self):
+        if getattr(self, "_p", None) and _lib is not None:
+            _lib.llm_pool_delete(self._p)
+            self._p = None
 
     @property
     def free(self) -> int:
-        return len(self._free)
+        return _core().llm_pool_free(self._p)
 
     def alloc(self, n: int) -> Optional[List[int]]:
-        if n > len(self._free):
+        out = (ctypes.c_int * max(n, 1))()
+        if _core().llm_pool_alloc(self._p, n, out) < 0:
             return None
-        out = [self._free.popleft() for _ in range(n)]
-        for p in out:
-            self._held[p] = True
-        return out
+        return list(out[:n])
 
     def release(self, pages: Sequence[int]) -> None:
-        for p in pages:
-            if not 0 <= p < self.n_pages or not self._held[p]:
-                raise CacheError(f"page {p} released but not held")
-            self._held[p] = False
-            self._free.append(p)
+        arr = (ctypes.c_int * max(len(pages), 1))(*pages)
+        if _core().llm_pool_release(self._p, arr, len(pages)) != 0:
+            raise CacheError(f"a page of {list(pages)} released but not held")
 
     def held(self) -> int:
-        return sum(self._held)
+        return _core().llm_pool_held(self._p)
 
 
 @dataclass
@@ -94,11 +157,8 @@ class _Group:
     need: PagedKV
     n_pages: int
     entries: List[int] = field(default_factory=list)   # run-order entries stored here
-    pool: PagePool = None                               # type: ignore[assignment]
     storage: Optional[torch.Tensor] = None              # [page, slot, 2, Hkv, page_size, hd]
     table: Optional[torch.Tensor] = None                # device int32 [requests, pages/request]
-    # (request slot, page index) -> page id, changes not yet sent to the device table
-    updates: Dict[Tuple[int, int], int] = field(default_factory=dict)
 
 
 @dataclass
@@ -113,16 +173,6 @@ class CacheView:
     group: int
     storage: Optional[torch.Tensor] = None   # the group's whole tensor, for kernels that tile it
     slot: int = 0                            # this call's cache slot inside the group
-
-
-class _Request:
-    __slots__ = ("slot", "length", "pages", "first_live")
-
-    def __init__(self, slot: int, n_groups: int):
-        self.slot = slot
-        self.length = 0
-        self.pages: List[List[int]] = [[] for _ in range(n_groups)]   # -1 = given back
-        self.first_live = [0] * n_groups
 
 
 class CacheManager:
@@ -150,7 +200,7 @@ class CacheManager:
                 if g is None:
                     g = len(self.groups)
                     by_need[need] = g
-                    self.groups.append(_Group(need, n_pages, pool=PagePool(n_pages)))
+                    self.groups.append(_Group(need, n_pages))
                 self._where[i] = (g, len(self.groups[g].entries))
                 self.groups[g].entries.append(i)
             elif isinstance(need, FixedState):
@@ -165,13 +215,33 @@ class CacheManager:
                     raise CacheError(f"entry {i} cannot read the fixed-size state of {src}")
                 else:
                     raise CacheError(f"entry {i} reads the cache of {src}, which has none")
-        self._requests: Dict[Any, _Request] = {}
-        self._free_slots: Deque[int] = deque(range(max_requests))
-        self._fresh_slots: List[int] = []      # slots whose state must be zeroed before use
+        G = len(self.groups)
+        self._lib = _core()
+        pages = (ctypes.c_int * max(G, 1))(*[g.n_pages for g in self.groups])
+        windows = (ctypes.c_int * max(G, 1))(*[g.need.window or 0 for g in self.groups])
+        self._c = self._lib.llm_cache_new(G, pages, windows, page_size, max_requests, max_context,
+                                          int(bool(self._state_need)))
+        if not self._c:
+            raise CacheError("the cache core refused these sizes")
+        self._keys: Dict[Any, int] = {}            # request id -> the core's 64-bit key
+        self._ids: Dict[int, Any] = {}
+        self._next_key = itertools.count(1)
+        self._info = (ctypes.c_int * 4)()
+        self._per_group = (ctypes.c_int * max(G, 1))()
         self.device: Optional[torch.device] = None
         self.dtype: Optional[torch.dtype] = None
-        self.counters = {"pages_allocated": 0, "pages_released": 0, "window_releases": 0,
-                         "refusals": 0}
+
+    def __del__(self):
+        if getattr(self, "_c", None) and getattr(self, "_lib", None) is not None:
+            self._lib.llm_cache_delete(self._c)
+            self._c = None
+
+    @property
+    def counters(self) -> Dict[str, int]:
+        out = (ctypes.c_longlong * 4)()
+        self._lib.llm_cache_counters(self._c, out)
+        return {"pages_allocated": out[0], "pages_released": out[1], "window_releases": out[2],
+                "refusals": out[3]}
 
     # ------------------------------------------------------------------ storage
     def allocate_storage(self, dtype: torch.dtype, device) -> None:
@@ -209,182 +279,159 @@ class CacheManager:
         return self.state.get(entry)
 
     # ------------------------------------------------------------------ requests
-    def open(self, request_id: Any) -> int:
-        if request_id in self._requests:
-            raise CacheError(f"request {request_id!r} is already open")
-        if not self._free_slots:
-            raise CacheError("no free request slot")
-        slot = self._free_slots.popleft()
-        self._requests[request_id] = _Request(slot, len(self.groups))
-        self._fresh_slots.append(slot)
-        return slot
-
-    def has(self, request_id: Any) -> bool:
-        return request_id in self._requests
-
-    def slot(self, request_id: Any) -> int:
-        return self._req(request_id).slot
-
-    def length(self, request_id: Any) -> int:
-        return self._req(request_id).length
-
-    def free_slots(self) -> int:
-        return len(self._free_slots)
-
-    def free_pages(self) -> List[int]:
-        return [g.pool.free for g in self.groups]
-
-    def live_requests(self) -> List[Any]:
-        return list(self._requests)
-
-    def _req(self, request_id: Any) -> _Request:
+    def _key(self, request_id: Any) -> int:
         try:
-            return self._requests[request_id]
+            return self._keys[request_id]
         except KeyError:
             raise CacheError(f"unknown request {request_id!r}") from None
 
-    def _first_needed_page(self, g: _Group, length: int) -> int:
-        """First page that a query at position >= length can still reach."""
-        w = g.need.window
-        if w is None:
-            return 0
-        return max(0, length - w + 1) // self.page_size
+    def open(self, request_id: Any) -> int:
+        if request_id in self._keys:
+            raise CacheError(f"request {request_id!r} is already open")
+        key = next(self._next_key)
+        slot = self._lib.llm_cache_open(self._c, key)
+        if slot == _E_NO_SLOT:
+            raise CacheError("no free request slot")
+        if slot < 0:
+            raise CacheError(f"request {request_id!r}: the cache core answered {slot}")
+        self._keys[request_id] = key
+        self._ids[key] = request_id
+        return slot
+
+    def has(self, request_id: Any) -> bool:
+        return request_id in self._keys
+
+    def info(self, request_id: Any) -> Tuple[int, int]:
+        """(request slot, tokens held)."""
+        s, n = ctypes.c_int(), ctypes.c_int()
+        if self._lib.llm_cache_info(self._c, self._key(request_id), s, n) != 0:
+            raise CacheError(f"unknown request {request_id!r}")
+        return s.value, n.value
+
+    def info_many(self, request_ids: Sequence[Any]) -> Tuple[np.ndarray, np.ndarray]:
+        """Request slots and lengths of several requests as int32 arrays."""
+        n = len(request_ids)
+        keys = np.fromiter((self._key(r) for r in request_ids), dtype=np.int64, count=n)
+        slots, lengths = np.empty(n, dtype=np.int32), np.empty(n, dtype=np.int32)
+        rc = self._lib.llm_cache_info_many(self._c, n, keys.ctypes.data, slots.ctypes.data,
+                                           lengths.ctypes.data)
+        if rc != 0:
+            raise CacheError(f"unknown request {request_ids[-rc - 100]!r}")
+        return slots, lengths
+
+    def slot(self, request_id: Any) -> int:
+        return self.info(request_id)[0]
+
+    def length(self, request_id: Any) -> int:
+        return self.info(request_id)[1]
+
+    def free_slots(self) -> int:
+        return self._lib.llm_cache_free_slots(self._c)
+
+    def free_pages(self) -> List[int]:
+        self._lib.llm_cache_free_pages(self._c, self._per_group)
+        return list(self._per_group[:len(self.groups)])
+
+    def live_requests(self) -> List[Any]:
+        return list(self._keys)
 
     def pages_needed(self, request_id: Any, new_tokens: int) -> List[int]:
         """Pages each group must add so that the request can grow by ``new_tokens``."""
-        r = self._req(request_id)
-        new_len = r.length + new_tokens
-        want = -(-new_len // self.page_size)
-        return [max(0, want - len(r.pages[gi])) for gi in range(len(self.groups))]
+        self._lib.llm_cache_pages_needed(self._c, self._key(request_id), new_tokens,
+                                         self._per_group)
+        return list(self._per_group[:len(self.groups)])
 
     def reserve(self, growth: Sequence[Tuple[Any, int]]) -> None:
         """Make room for every (request, new tokens) of a step, or change nothing and raise
         :class:`CacheFull` (crates/engine/model/src/forward.rs:245-259)."""
-        need = [0] * len(self.groups)
+        n = len(growth)
         seen = set()
-        for rid, n in growth:
+        for rid, _ in growth:
             if rid in seen:
                 raise CacheError(f"request {rid!r} appears twice in one step")
             seen.add(rid)
-            r = self._req(rid)
-            if n <= 0:
-                raise CacheError(f"request {rid!r}: a step entry needs at least one token")
-            if r.length + n > self.max_context:
-                raise CacheError(f"request {rid!r}: {r.length} + {n} tokens exceed the context "
-                                 f"of {self.max_context}")
-            for gi, k in enumerate(self.pages_needed(rid, n)):
-                need[gi] += k
-        for gi, g in enumerate(self.groups):
-            if need[gi] > g.pool.free:
-                self.counters["refusals"] += 1
-                raise CacheFull(gi, need[gi], g.pool.free)
-        if not any(need):
+        keys = np.fromiter((self._key(rid) for rid, _ in growth), dtype=np.int64, count=n)
+        counts = np.fromiter((k for _, k in growth), dtype=np.int32, count=n)
+        rc = self._lib.llm_cache_reserve(self._c, n, keys.ctypes.data, counts.ctypes.data,
+                                         self._info)
+        if rc == 0:
             return
-        for rid, n in growth:
-            r = self._req(rid)
-            for gi, k in enumerate(self.pages_needed(rid, n)):
-                if k == 0:
-                    continue
-                g = self.groups[gi]
-                pages = g.pool.alloc(k)
-                assert pages is not None
-                self.counters["pages_allocated"] += k
-                for p in pages:
-                    g.updates[(r.slot, len(r.pages[gi]))] = p
-                    r.pages[gi].append(p)
+        i = self._info
+        if rc == 1:
+            raise CacheFull(i[0], i[1], i[2])
+        rid = growth[i[0]][0] if 0 <= i[0] < n else None
+        if rc == _E_EMPTY:
+            raise CacheError(f"request {rid!r}: a step entry needs at least one token")
+        if rc == _E_CONTEXT:
+            raise CacheError(f"request {rid!r}: {i[1]} + {i[2]} tokens exceed the context of "
+                             f"{self.max_context}")
+        if rc == _E_TWICE:
+            raise CacheError(f"request {rid!r} appears twice in one step")
+        raise CacheError(f"request {rid!r}: the cache core answered {rc}")
 
     def advance(self, request_id: Any, n: int) -> None:
         """The request now holds ``n`` more tokens; pages that a window has passed go back."""
-        r = self._req(request_id)
-        r.length += n
-        for gi in range(len(self.groups)):
-            if r.length > len(r.pages[gi]) * self.page_size:
-                raise CacheError(f"request {request_id!r} advanced past its reserved pages")
-        for gi, g in enumerate(self.groups):
-            keep_from = min(self._first_needed_page(g, r.length), len(r.pages[gi]))
-            if keep_from > r.first_live[gi]:
-                gone = r.pages[gi][r.first_live[gi]:keep_from]
-                g.pool.release(gone)
-                self.counters["pages_released"] += len(gone)
-                self.counters["window_releases"] += len(gone)
-                for j in range(r.first_live[gi], keep_from):
-                    r.pages[gi][j] = -1
-                    g.updates[(r.slot, j)] = -1
-                r.first_live[gi] = keep_from
+        rc = self._lib.llm_cache_advance(self._c, self._key(request_id), n)
+        if rc == _E_PAST:
+            raise CacheError(f"request {request_id!r} advanced past its reserved pages")
+        if rc != 0:
+            raise CacheError(f"request {request_id!r}: the cache core answered {rc}")
 
     def truncate(self, request_id: Any, length: int) -> None:
         """Forget everything past ``length`` tokens (kv.rs:792-816).  A group that has given
         pages back to its window cannot be rewound into them."""
-        r = self._req(request_id)
-        if length > r.length:
+        rc = self._lib.llm_cache_truncate(self._c, self._key(request_id), length, self._info)
+        if rc == 0:
+            return
+        if rc == _E_LENGTHEN:
             raise CacheError("truncate cannot lengthen a request")
-        if self._state_need and length < r.length:
+        if rc == _E_STATE:
             raise CacheError("a request with fixed-size state cannot be rewound; close it")
-        keep = -(-length // self.page_size)
-        for gi, g in enumerate(self.groups):
-            if self._first_needed_page(g, length) < r.first_live[gi]:
-                raise CacheError(f"group {gi}: the window has already given back pages that a "
-                                 f"request of {length} tokens needs")
-            gone = [p for p in r.pages[gi][keep:] if p >= 0]
-            g.pool.release(gone)
-            self.counters["pages_released"] += len(gone)
-            for j in range(keep, len(r.pages[gi])):
-                g.updates[(r.slot, j)] = -1
-            del r.pages[gi][keep:]
-        r.length = length
+        if rc == _E_WINDOW:
+            raise CacheError(f"group {self._info[0]}: the window has already given back pages "
+                             f"that a request of {length} tokens needs")
+        raise CacheError(f"request {request_id!r}: the cache core answered {rc}")
 
     def close(self, request_id: Any) -> None:
         """The request is over: its pages, its slot and its state go back."""
-        r = self._req(request_id)
-        for gi, g in enumerate(self.groups):
-            gone = [p for p in r.pages[gi] if p >= 0]
-            g.pool.release(gone)
-            self.counters["pages_released"] += len(gone)
-            for j, p in enumerate(r.pages[gi]):
-                if p >= 0:
-                    g.updates[(r.slot, j)] = -1
-        del self._requests[request_id]
-        self._free_slots.append(r.slot)
-        if r.slot in self._fresh_slots:
-            self._fresh_slots.remove(r.slot)
+        key = self._key(request_id)
+        rc = self._lib.llm_cache_close(self._c, key)
+        if rc != 0:
+            raise CacheError(f"request {request_id!r}: the cache core answered {rc}")
+        del self._keys[request_id]
+        del self._ids[key]
 
     # ------------------------------------------------------------------ device mirror
     def take_table_updates(self) -> List[np.ndarray]:
         """Per group, the (request slot, page index, page id) triples since the last call; one
         triple per table cell (the last value wins), so they may be applied in any order."""
         out = []
-        for g in self.groups:
-            out.append(np.asarray([(s, j, p) for (s, j), p in g.updates.items()],
-                                  dtype=np.int32).reshape(-1, 3))
-            g.updates = {}
+        for gi in range(len(self.groups)):
+            n = self._lib.llm_cache_pending_updates(self._c, gi)
+            arr = np.empty((n, 3), dtype=np.int32)
+            if n:
+                self._lib.llm_cache_take_updates(self._c, gi, arr.ctypes.data)
+            out.append(arr)
         return out
 
     def take_fresh_slots(self) -> List[int]:
-        out, self._fresh_slots = self._fresh_slots, []
-        return out
+        buf = (ctypes.c_int * self.max_requests)()
+        n = self._lib.llm_cache_take_fresh(self._c, buf, self.max_requests)
+        return list(buf[:n])
 
     def pages_of(self, request_id: Any, group: int = 0) -> List[int]:
-        return list(self._req(request_id).pages[group])
+        buf = (ctypes.c_int * self.pages_per_request)()
+        n = self._lib.llm_cache_pages_of(self._c, self._key(request_id), group, buf,
+                                         self.pages_per_request)
+        if n < 0:
+            raise CacheError(f"request {request_id!r}, group {group}: the cache core answered {n}")
+        return list(buf[:n])
 
     def check_invariants(self) -> None:
         """No page lost, none held twice, none both free and held."""
-        for gi, g in enumerate(self.groups):
-            held: List[int] = []
-            for r in self._requests.values():
-                held += [p for p in r.pages[gi] if p >= 0]
-            if len(held) != len(set(held)):
-                raise CacheError(f"group {gi}: a page is held twice")
-            free = list(g.pool._free)
-            if set(free) & set(held):
-                raise CacheError(f"group {gi}: a page is both free and held")
-            if len(free) != len(set(free)):
-                raise CacheError(f"group {gi}: a page is in the free queue twice")
-            if len(free) + len(held) != g.n_pages:
-                raise CacheError(f"group {gi}: {g.n_pages - len(free) - len(held)} pages lost")
-            if g.pool.held() != len(held):
-                raise CacheError(f"group {gi}: the pool's own count of held pages is off")
-        slots = [r.slot for r in self._requests.values()]
-        if len(slots) != len(set(slots)) or set(slots) & set(self._free_slots):
-            raise CacheError("a request slot is held twice or both free and held")
-        if len(slots) + len(self._free_slots) != self.max_requests:
+        rc = self._lib.llm_cache_check(self._c, self._info)
+        if rc != 0:
+            where = f"group {self._info[0]}: " if rc > -25 else ""
+            raise CacheError(where + _CHECK.get(rc, f"the cache core answered {rc}"))
+        if len(self._keys) + self.free_slots() != self.max_requests:
             raise CacheError("a request slot was lost")

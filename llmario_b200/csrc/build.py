@@ -25,6 +25,10 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", "-Xcudafe", "--diag_suppress=177"]
 
+HOST_DIR = os.path.join(HERE, "host")
+HOST_PREFIX = "libllmario_host_"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-Wall"]
+
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}
 
@@ -130,7 +134,7 @@ def build_library(verbose: bool = True, extra_flags: Sequence[str] = ()) -> str:
     os.replace(tmp, lib)
     keep = {os.path.basename(lib)} | {os.path.basename(o) for o in objs}
     for f in os.listdir(out_dir):           # objects and libraries of older sources
-        if f.endswith((".so", ".o")) and f not in keep:
+        if f.endswith((".so", ".o")) and f not in keep and not f.startswith(HOST_PREFIX):
             try:
                 os.remove(os.path.join(out_dir, f))
             except OSError:
@@ -158,3 +162,52 @@ def load_library(verbose: bool = True) -> ctypes.CDLL:
 
 def library_path() -> Optional[str]:
     return _loaded.get("path")  # type: ignore[return-value]
+
+
+def _cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"),
+                 shutil.which("clang++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return cand
+    raise BuildError("no C++ compiler found (looked at $CXX, g++, c++, clang++): the host "
+                     "library of llmario_b200 cannot be compiled")
+
+
+def build_host_library(verbose: bool = True) -> str:
+    """Compile the host-side C++ sources (``host/*.cpp``: cache bookkeeping) into one shared
+    library with the system's C++ compiler and return its path.  No CUDA toolkit is needed."""
+    srcs = sorted(f for f in os.listdir(HOST_DIR) if f.endswith(".cpp"))
+    if not srcs:
+        raise BuildError(f"no .cpp sources in {HOST_DIR}")
+    h = hashlib.sha256()
+    for f in srcs + sorted(f for f in os.listdir(HOST_DIR) if f.endswith((".h", ".hpp"))):
+        h.update(f.encode())
+        with open(os.path.join(HOST_DIR, f), "rb") as fh:
+            h.update(fh.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    out_dir = _build_dir()
+    lib = os.path.join(out_dir, f"{HOST_PREFIX}{h.hexdigest()[:16]}.so")
+    if os.path.isfile(lib):
+        return lib
+    t0 = time.time()
+    tmp = lib + f".{os.getpid()}.tmp"
+    _run([_cxx(), *HOST_FLAGS, "-o", tmp, *[os.path.join(HOST_DIR, f) for f in srcs]],
+         "compiling the host library")
+    os.replace(tmp, lib)
+    for f in os.listdir(out_dir):
+        if f.startswith(HOST_PREFIX) and f.endswith(".so") and f != os.path.basename(lib):
+            try:
+                os.remove(os.path.join(out_dir, f))
+            except OSError:
+                pass
+    if verbose:
+        _say(f"built {os.path.basename(lib)} in {time.time() - t0:.0f} s")
+    return lib
+
+
+def load_host_library() -> ctypes.CDLL:
+    with _lock:
+        path = build_host_library()
+        if path not in _loaded:
+            _loaded[path] = ctypes.CDLL(path)
+        return _loaded[path]

@@ -169,14 +169,12 @@ class ModelRunner:
         segments: List[Segment] = []
         want: List[int] = []
         if rows == len(entries):      # single tokens only: no per-entry array work
-            reqs = [cache._req(e.request) for e in entries]
+            slot, pos = cache.info_many([e.request for e in entries])
             tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=rows)
-            pos = np.fromiter((r.length for r in reqs), dtype=np.int32, count=rows)
-            slot = np.fromiter((r.slot for r in reqs), dtype=np.int32, count=rows)
-            for i, (e, r) in enumerate(zip(entries, reqs)):
+            for i, e in enumerate(entries):
                 if e.want:
                     want.append(i)
-                segments.append(Segment(e.request, r.slot, i, 1, r.length))
+                segments.append(Segment(e.request, int(slot[i]), i, 1, int(pos[i])))
         else:
             tokens = np.empty(rows, dtype=np.int32)
             pos = np.empty(rows, dtype=np.int32)
@@ -184,7 +182,7 @@ class ModelRunner:
             r0 = 0
             for e in entries:
                 n = len(e.tokens)
-                s, p0 = cache.slot(e.request), cache.length(e.request)
+                s, p0 = cache.info(e.request)
                 tokens[r0:r0 + n] = np.asarray(e.tokens, dtype=np.int32)
                 pos[r0:r0 + n] = np.arange(p0, p0 + n, dtype=np.int32)
                 slot[r0:r0 + n] = s

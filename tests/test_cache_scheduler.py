@@ -402,3 +402,89 @@ def test_no_step_ahead_when_someone_waits_or_pages_are_short():
     p = s2.plan()
     launch(s2, p)
     assert pen.params.penalties_active and s2.plan_ahead(p) is None
+
+
+# ------------------------------------------------------------------------------ native core vs plain model
+@pytest.mark.parametrize("seed", range(6))
+def test_native_bookkeeping_agrees_with_the_plain_model(seed):
+    """The C++ core and the plain Python model under ``tests/plain`` are driven with the same
+    random operations (open, grow in mixed steps, truncate, close, misuse) and must give the
+    same answers at every turn: slots, page ids in order, free pages, refusals with their
+    numbers, table changes, slots to be zeroed."""
+    import random
+
+    from llmario_b200.cache import CacheError, CacheFull
+    from plain.cache_plain import PlainCache, PlainError, PlainFull
+
+    rng = random.Random(seed)
+    page = rng.choice([1, 4, 8])
+    windows = [None, rng.choice([5, 9, 17])] if seed % 2 else [None]
+    n_pages = rng.choice([6, 14, 30])
+    ctx = rng.choice([24, 50])
+    max_req = rng.choice([2, 4])
+    needs = [PagedKV(2, 16, w) for w in windows]
+    native = CacheManager(needs, [None] * len(needs), page, n_pages, max_req, ctx)
+    plain = PlainCache([n_pages] * len(windows), windows, page, max_req, ctx)
+    live = []
+    names = iter(range(10 ** 6))
+
+    def both(op_native, op_plain):
+        """Run an operation on both; they succeed together or fail together."""
+        try:
+            a, ea = op_native(), None
+        except (CacheError, CacheFull) as e:
+            a, ea = None, e
+        try:
+            b, eb = op_plain(), None
+        except (PlainError, PlainFull) as e:
+            b, eb = None, e
+        assert (ea is None) == (eb is None), (ea, eb)
+        if isinstance(ea, CacheFull) or isinstance(eb, PlainFull):
+            assert isinstance(ea, CacheFull) and isinstance(eb, PlainFull)
+            assert (ea.group, ea.needed, ea.free) == (eb.group, eb.needed, eb.free)
+        return a, b, ea is None
+
+    for step in range(400):
+        op = rng.random()
+        if op < 0.2:
+            rid = f"r{next(names)}"
+            a, b, ok = both(lambda: native.open(rid), lambda: plain.open(rid))
+            if ok:
+                assert a == b
+                live.append(rid)
+        elif op < 0.7 and live:
+            k = rng.randint(1, min(3, len(live)))
+            chosen = rng.sample(live, k)
+            if rng.random() < 0.05:
+                chosen.append(chosen[0])                     # misuse: twice in one step
+            growth = [(r, rng.choice([0, 1, 1, 2, 5, 11]) if rng.random() < 0.9 else 40)
+                      for r in chosen]
+            _, _, ok = both(lambda: native.reserve(growth), lambda: plain.reserve(growth))
+            if ok:
+                for r, n in growth:
+                    both(lambda: native.advance(r, n), lambda: plain.advance(r, n))
+        elif op < 0.8 and live:
+            r = rng.choice(live)
+            to = rng.randint(0, plain.requests[r]["length"] + 1)
+            both(lambda: native.truncate(r, to), lambda: plain.truncate(r, to))
+        elif op < 0.95 and live:
+            r = live.pop(rng.randrange(len(live)))
+            both(lambda: native.close(r), lambda: plain.close(r))
+        else:
+            both(lambda: native.advance("nobody", 1), lambda: plain.advance("nobody", 1))
+        # the same state after every operation
+        assert native.free_pages() == [len(f) for f in plain.free]
+        assert native.free_slots() == len(plain.free_slots)
+        for r in live:
+            assert native.info(r) == (plain.requests[r]["slot"], plain.requests[r]["length"])
+            for g in range(len(windows)):
+                assert native.pages_of(r, g) == plain.requests[r]["pages"][g]
+                assert native.pages_needed(r, 3) == plain.pages_needed(r, 3)
+        if step % 7 == 0:
+            got = [sorted(map(tuple, u.tolist())) for u in native.take_table_updates()]
+            assert got == plain.take_updates()
+            assert native.take_fresh_slots() == plain.take_fresh()
+        native.check_invariants()
+    for r in live:
+        native.close(r), plain.close(r)
+    assert native.free_pages() == [n_pages] * len(windows)
