@@ -359,7 +359,17 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
            "gemm_tcgen05")
 
 
-SM_COUNT = 148
+_sm_count: Optional[int] = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the device in use (148 on a B200; asked once)."""
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = (torch.cuda.get_device_properties(torch.cuda.current_device())
+                     .multi_processor_count if torch.cuda.is_available() else 148)
+    return _sm_count
+
 # Up to this many rows a caller may keep a split-K destination at zero itself (the kernel that
 # consumes it clears it) instead of having it cleared before every product.
 SPLIT_K_MAX_ROWS = 256
@@ -368,10 +378,10 @@ SPLIT_K_MAX_ROWS = 256
 def k_splits(rows: int, out_features: int, in_features: int) -> int:
     """How many ways to split K so that a product with few output tiles still fills the GPU."""
     tiles = -(-out_features // 128) * -(-rows // token_tile(rows))
-    if tiles >= 2 * SM_COUNT - 40:
+    if tiles >= 2 * sm_count() - 40:
         return 1
-    # two CTAs fit an SM: aim at one full wave of 2 * SM_COUNT CTAs, at least 256 of K each
-    return max(1, min(16, round(2 * SM_COUNT / tiles), in_features // 256))
+    # two CTAs fit an SM: aim at one full wave of two CTAs per SM, at least 256 of K each
+    return max(1, min(16, round(2 * sm_count() / tiles), in_features // 256))
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
@@ -521,8 +531,7 @@ def attention_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tens
                                      num_heads, head_dim, splits, _stream()), "attention_merge")
 
 
-def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int = 3 * SM_COUNT
-                  ) -> int:
+def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int = 444) -> int:
     """Parts into which the keys of a one-token item are cut.  ``resident``: how many CTAs of
     the kernel the GPU holds at once.  The cost of a choice is modelled as waves of CTAs times
     the length of one CTA's walk (its tiles of 32 keys plus a fixed start-up of about three
@@ -558,7 +567,7 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
         reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
         tma = group <= 8 and decode_tma_ok(view, head_dim)
         splits = decode_splits(plan.n_small, num_kv_heads, reach,
-                               (3 if tma else 6) * SM_COUNT) if plan.small_single else 1
+                               (3 if tma else 6) * sm_count()) if plan.small_single else 1
         part_o = part_ml = None
         if splits > 1:
             part_o = ctx.buffer("attn.part_o", (ctx.rows * num_heads * splits * head_dim,),
