@@ -112,7 +112,8 @@ def cmd_prefill_attention(a) -> None:
     storage, table = _paged(1, T, Hkv, hd, page)
     q = torch.randn(T, Hq * hd, device=DEV).bfloat16()
     out = torch.empty_like(q)
-    cap = max(1, (64 if a.mma_sync else 128) // (Hq // Hkv))
+    x2 = not (a.mma_sync or a.cp_async or a.one_tile) and page >= 32
+    cap = max(1, (64 if a.mma_sync else 256 if x2 else 128) // (Hq // Hkv))
     items = torch.tensor([[s, min(cap, T - s), 0, s] for s in range(0, T, cap)],
                          dtype=torch.int32, device=DEV).reshape(-1)
     n = items.numel() // 4
@@ -120,6 +121,10 @@ def cmd_prefill_attention(a) -> None:
         fn = lambda: kernels.attention_flash(q, out, storage[0, 0, 0], storage[0, 0, 1],
                                              storage.stride(0), table, items, n, 64, Hq, Hkv, hd,
                                              page, hd ** -0.5, None)
+    elif x2:
+        fn = lambda: kernels.attention_tcgen05_x2(q, out, storage[0, 0, 0], storage[0, 0, 1],
+                                                  storage.stride(0), table, items, n, Hq, Hkv, hd,
+                                                  page, hd ** -0.5, None, storage.shape[0])
     else:
         fn = lambda: kernels.attention_tcgen05(q, out, storage[0, 0, 0], storage[0, 0, 1],
                                                storage.stride(0), table, items, n, Hq, Hkv, hd,
@@ -196,6 +201,8 @@ def main(argv=None) -> int:
                    help="the mma.sync kernel of attention_flash.cu instead of the tcgen05 kernel")
     p.add_argument("--cp-async", action="store_true",
                    help="K and V by cp.async copies even where the pages are large enough for TMA")
+    p.add_argument("--one-tile", action="store_true",
+                   help="one query tile per CTA even where the pages allow two")
     p.set_defaults(fn=cmd_prefill_attention)
     st = sub.add_parser("step")
     st.add_argument("--model", default="qwen3-8b")

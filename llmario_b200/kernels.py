@@ -58,6 +58,7 @@ def _signatures():
         "llm_attention_decode_tma": [P, P, P, P, P, L, I, I, P, I, P, P, P, I, I, I, I, I, F, I,
                                      I, P, P],
         "llm_attention_tcgen05": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, P, P],
+        "llm_attention_tcgen05_x2": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
 
@@ -512,6 +513,30 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         _stream()), f"attention_tcgen05 (head_dim {head_dim})")
 
 
+def attention_tcgen05_x2(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
+                         v_cache: torch.Tensor, page_stride: int, block_table: torch.Tensor,
+                         items: torch.Tensor, n_items: int, num_heads: int, num_kv_heads: int,
+                         head_dim: int, page_size: int, scale: float, window: Optional[int],
+                         n_pages: int) -> None:
+    """As :func:`attention_tcgen05` with two query tiles per CTA: items of at most
+    2 * 128 / (heads per KV head) tokens.  Pages of a power of two of at least 32 positions."""
+    _cuda(q, out, k_cache, v_cache, block_table, items)
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous()
+    _check(lib().llm_attention_tcgen05_x2(
+        _ptr(q), _ptr(out), q.shape[0], _ptr(k_cache), _ptr(v_cache), page_stride, int(n_pages),
+        _ptr(block_table), block_table.stride(0), _ptr(items), n_items, num_heads, num_kv_heads,
+        head_dim, page_size, float(scale), int(window or 0), _ptr(tc_status(q.device)),
+        _stream()), f"attention_tcgen05_x2 (head_dim {head_dim})")
+
+
+def prefill_x2_ok(view, head_dim: int, group: int) -> bool:
+    """Whether prompt portions can run two query tiles per CTA (keys and values by TMA)."""
+    ps = view.page_size
+    return (prefill_tcgen05_ok(view, head_dim, group) and ps >= 32 and ps & (ps - 1) == 0
+            and getattr(view, "storage", None) is not None)
+
+
 def prefill_tcgen05_ok(view, head_dim: int, group: int) -> bool:
     return head_dim in (64, 128) and 128 % group == 0 and (view.page_stride * 2) % 16 == 0
 
@@ -561,7 +586,11 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
                           view.page_size, scale, window)
         return
     tc = prefill_tcgen05_ok(view, head_dim, group)
-    plan = ctx.attention_plan(group, (128 if tc else 64) // group)
+    # two query tiles per CTA pay once there are CTAs enough to fill the GPU several times over
+    # (with fewer, the longer CTAs end less evenly than the gain is worth)
+    x2 = (tc and prefill_x2_ok(view, head_dim, group)
+          and ctx.rows * num_kv_heads >= 4 * sm_count() * (128 // group))
+    plan = ctx.attention_plan(group, (256 if x2 else 128 if tc else 64) // group)
     common = (view.k, view.v, view.page_stride, view.block_table)
     if plan.n_small:
         reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
@@ -589,7 +618,10 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
         if splits > 1:
             attention_merge(part_o, part_ml, out, plan.small_rows, plan.n_small, num_heads,
                             head_dim, splits)
-    if plan.n_large and tc:
+    if plan.n_large and x2:
+        attention_tcgen05_x2(q, out, *common, plan.large, plan.n_large, num_heads, num_kv_heads,
+                             head_dim, view.page_size, scale, window, view.storage.shape[0])
+    elif plan.n_large and tc:
         storage = getattr(view, "storage", None)
         attention_tcgen05(q, out, *common, plan.large, plan.n_large, num_heads, num_kv_heads,
                           head_dim, view.page_size, scale, window,

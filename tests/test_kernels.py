@@ -441,7 +441,7 @@ def test_attention_decode(Hq, Hkv, hd, page, window, tma):
 
 
 @pytest.mark.parametrize("page,window", [(16, None), (64, None), (16, 200), (64, 130)])
-@pytest.mark.parametrize("kernel", ["decode", "decode_tma", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["decode", "decode_tma", "tcgen05", "tcgen05_x2"])
 def test_tensor_core_attention_finds_the_key_that_stands_out(kernel, page, window):
     """Random keys would hide a tile, a page or a window's edge read wrongly.  Here single keys
     are made to dominate single query rows: far back among hundreds, on the last and the first
@@ -459,12 +459,14 @@ def test_tensor_core_attention_finds_the_key_that_stands_out(kernel, page, windo
     targets = [t for t in (13, page - 1, page, 127, 128, 511, 512, 639, 640, last - 1, last) if t >= lo]
     if window:
         targets += [lo, lo + 1, lo - 1]          # lo - 1 is outside the window of the last position
-    cap = 128 // G if kernel == "tcgen05" else 1
+    if kernel == "tcgen05_x2" and page < 32:
+        pytest.skip("two query tiles per CTA need pages of 32 positions or more")
+    cap = {"tcgen05": 128 // G, "tcgen05_x2": 256 // G}.get(kernel, 1)
     # rows: for the decode kernels one row per target, all at the last position; for the prompt
     # kernel one item of `cap` tokens that ends at the last position, a target for each of its
     # last rows (a row sees a target only if it lies at or before its own position)
     g = torch.Generator().manual_seed(9)
-    if kernel == "tcgen05":
+    if kernel.startswith("tcgen05"):
         rows = [(0, last - cap + 1 + i) for i in range(cap)]
         aim = {cap - 1 - j: t for j, t in enumerate(targets) if t <= last - j and
                (not window or t >= last - j + 1 - window or t == lo - 1)}
@@ -484,10 +486,10 @@ def test_tensor_core_attention_finds_the_key_that_stands_out(kernel, page, windo
     qd = q.reshape(len(rows), -1).to(DEV).contiguous()
     out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
     common = (storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table)
-    if kernel == "tcgen05":
+    if kernel.startswith("tcgen05"):
         items = torch.tensor([[0, cap, 0, rows[0][1]]], dtype=torch.int32, device=DEV).reshape(-1)
-        kernels.attention_tcgen05(qd, out, *common, items, 1, Hq, Hkv, hd, page, scale, window,
-                                  storage.shape[0])
+        fn = kernels.attention_tcgen05 if kernel == "tcgen05" else kernels.attention_tcgen05_x2
+        fn(qd, out, *common, items, 1, Hq, Hkv, hd, page, scale, window, storage.shape[0])
     else:
         slot = torch.zeros(len(rows), dtype=torch.int32, device=DEV)
         pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
@@ -550,6 +552,28 @@ def test_attention_tcgen05(Hq, Hkv, hd, page, window):
     qd = q.reshape(len(rows), -1).to(DEV).contiguous()
     out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
     dev_items = torch.tensor(items, dtype=torch.int32, device=DEV).reshape(-1)
+    if page >= 32:
+        # two query tiles per CTA: the same rows as items of up to twice as many tokens
+        rows2, items2 = [], []
+        for r, a, b in spans:
+            at = a
+            while at < b:
+                n = min(2 * cap, b - at)
+                items2.append((len(rows2), n, r, at))
+                rows2 += [(r, p) for p in range(at, at + n)]
+                at += n
+        assert rows2 == rows
+        out2 = torch.zeros_like(out)
+        kernels.attention_tcgen05_x2(qd, out2, storage[0, 1, 0], storage[0, 1, 1], storage.stride(0),
+                                     table, torch.tensor(items2, dtype=torch.int32, device=DEV)
+                                     .reshape(-1), len(items2), Hq, Hkv, hd, page, scale, window,
+                                     storage.shape[0])
+        kernels.check_tc_status(DEV)
+        for i, (r, p) in enumerate(rows):
+            ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
+            got = out2[i].reshape(Hq, hd).double().cpu()
+            assert torch.isfinite(got).all(), (i, r, p)
+            assert (got - ref).abs().max() <= 2e-2, ("x2", i, r, p, (got - ref).abs().max())
     # with the number of pages given, pages of 32 positions or more come by TMA; without, by copies
     for n_pages in (storage.shape[0], 0):
         out.zero_()
