@@ -217,6 +217,34 @@ def test_steps_queued_ahead_give_the_same_tokens(dtype):
     assert stop_plain[0][1] == "stop" and first[-1] == eos and len(first) <= 18
 
 
+def test_many_requests_with_few_pages_give_the_same_tokens_either_way():
+    """Forty requests of mixed lengths through a cache that holds a fraction of them, so that
+    requests wait, run beside prompt portions, are preempted and recomputed: with and without a
+    step queued ahead the generated tokens are the same, every page comes back, and steps were
+    in fact queued ahead and requests in fact preempted."""
+    from llmario_b200 import Engine, SamplingParams
+    name, dtype = "D", "float32"
+    rng = random.Random(5)
+    prompts = [random_tokens(name, rng.randint(3, 90), 300 + i) for i in range(40)]
+    params = [SamplingParams(temperature=0.0 if i % 3 else 0.9, seed=100 + i,
+                             max_tokens=rng.randint(4, 60)) for i in range(40)]
+
+    def run(lookahead):
+        eng = Engine(model_dir(name, dtype), dtype=dtype, page_size=16, cache_tokens=352,
+                     max_requests=6, context=256, token_budget=48, lookahead=lookahead)
+        outs = eng.generate(prompts, params)
+        cache = eng.runner.cache
+        cache.check_invariants()
+        assert min(cache.free_pages()) == cache.groups[0].n_pages and not cache.live_requests()
+        return outs, eng.stats()
+
+    plain_run, st0 = run(False)
+    ahead_run, st1 = run(True)
+    assert ahead_run == plain_run
+    assert [len(o) for o in plain_run] == [p.max_tokens for p in params]
+    assert st1.get("steps_planned_ahead", 0) > 10 and st0["preemptions"] > 0 and st1["preemptions"] > 0
+
+
 def test_patch_tokens_kernel():
     from llmario_b200 import kernels
     tokens = torch.arange(10, 20, dtype=torch.int32, device=DEV)
