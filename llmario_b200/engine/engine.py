@@ -39,7 +39,8 @@ class Engine:
         :class:`Model`; or give ``config`` (a typed configuration) and ``seed`` for random
         weights.  ``context``: most tokens of one request; ``max_requests``: requests running at
         once; ``token_budget``: most tokens in one step; ``num_pages`` / ``cache_tokens``: size
-        of the cache (default: room for every request slot at full context).  ``lookahead``:
+        of the cache (default: room for every request slot at full context, or what nine tenths
+        of the free device memory hold, whichever is less).  ``lookahead``:
         while a step of decoding requests runs, the next one is already queued on the device
         with its input tokens taken from the sampler's output there, so that the device does
         not wait for the host between steps; the tokens a caller sees are the same."""

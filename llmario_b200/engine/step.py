@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 from .. import kernels
-from ..cache import CacheError, CacheFull, CacheManager
+from ..cache import CacheError, CacheFull, CacheManager, PagedKV
 from ..parts import Segment, StepContext, Workspace
 from .model import Model
 
@@ -60,11 +60,21 @@ class ModelRunner:
         self.max_context = int(max_context or model.spec.max_positions)
         self.max_requests = int(max_requests)
         self.token_budget = int(token_budget)
-        if n_pages is None:
-            tokens = cache_tokens if cache_tokens is not None else \
-                self.max_requests * self.max_context
-            n_pages = -(-int(tokens) // self.page_size)
         needs, reads = model.cache_needs()
+        if n_pages is None:
+            if cache_tokens is not None:
+                tokens = int(cache_tokens)
+            else:
+                # room for every request slot at full context, or what nine tenths of the free
+                # device memory hold, whichever is less
+                tokens = self.max_requests * self.max_context
+                per_token = sum(2 * n.num_kv_heads * n.head_dim for n, r in zip(needs, reads)
+                                if isinstance(n, PagedKV) and r is None) * \
+                    torch.empty((), dtype=model.dtype).element_size()
+                if per_token:
+                    free = torch.cuda.mem_get_info(self.device)[0]
+                    tokens = max(self.page_size, min(tokens, int(0.9 * free) // per_token))
+            n_pages = -(-int(tokens) // self.page_size)
         self.cache = CacheManager(needs, reads, self.page_size, int(n_pages), self.max_requests,
                                   self.max_context)
         self.cache.allocate_storage(model.dtype, self.device)
