@@ -48,9 +48,6 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
 
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  // values of rows that no load fills are multiplied by zero weights: they must be finite
-  for (int i = lane; i < STAGES * 2 * TILE_BYTES / 16; i += 32)
-    reinterpret_cast<uint4*>(kv_tiles)[i] = make_uint4(0, 0, 0, 0);
   if (lane == 0) {
     for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -131,7 +128,20 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
       if (lane == 0) atomicExch(status, 4);
       break;
     }
-    const uint8_t* tile = kv_tiles + stage * 2 * TILE_BYTES;
+    uint8_t* tile = kv_tiles + stage * 2 * TILE_BYTES;
+    // A page without a key of the item is not fetched (only the first tile under a window and
+    // the last tile have such pages).  Its values meet zero weights and must be finite, and
+    // shared memory starts with whatever it held: clear them.  (Its keys may be anything: their
+    // scores are replaced by -inf.)
+    {
+      const int base = tb * KT;
+      for (int p = base; p < base + KT; p += R)
+        if (p > hi || p + R - 1 < lo) {
+          uint4* vz = reinterpret_cast<uint4*>(tile + ((p - base) >> lgR) * (2 * R * HD * 2) + R * HD * 2);
+          for (int i = lane; i < R * HD * 2 / 16; i += 32) vz[i] = make_uint4(0, 0, 0, 0);
+        }
+      __syncwarp();
+    }
 
     // ---- S^T = K Q^T
     float s[MT][4];
