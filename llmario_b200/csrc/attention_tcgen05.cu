@@ -45,7 +45,9 @@ struct alignas(1024) AttnStorage {
   int dead;
 };
 
-template <int HD>
+// SPLIT: two threads per row, each with 64 of a tile's 128 score columns (warps 2-5 the first
+// half, warps 6-9 the second); used when warps 6-9 have no copying to do (K/V by TMA).
+template <int HD, bool SPLIT>
 __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, int tma_kv,
     long long rows_per_page, int v_row_off, const bf16* __restrict__ k_cache,
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.s_full[b], 1);
-      mbar_init(&sm.p_full[b], 4);           // one arrival per softmax warp
+      mbar_init(&sm.p_full[b], SPLIT ? 8 : 4);   // one arrival per softmax warp
     }
     mbar_init(&sm.o_done, 1);
     sm.dead = 0;
@@ -149,7 +151,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
             mbar_wait(&sm.kv_full[j % KV_STAGES], (uint32_t)((j / KV_STAGES) & 1));
       }
     }
-  } else if (warp >= 6 && !tma_kv) {
+  } else if (warp >= 6 && !SPLIT) {
     // ------------------------------------------------------------------ K and V tiles
     // Thread p of the 128 copies the 16-byte piece (p % CPR) of rows (p / CPR), + 128 / CPR, ...
     // of every tile: its column and its row inside a group of eight never change, so the
@@ -254,8 +256,16 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
         tc_commit(&sm.o_done);
       }
     }
-  } else if (warp >= 2 && warp < 6) {
-    // ------------------------------------------------------------------ softmax, one row per thread
+  } else if (warp >= 2 && (warp < 6 || SPLIT)) {
+    // ------------------------------------------------------------------ softmax
+    // One thread per row, or (SPLIT) two: the thread of warps 2-5 takes the first 64 score columns
+    // of a tile and the first half of the output columns, its partner in warps 6-9 (same TMEM
+    // lane) the second; they exchange the maxima of their halves through shared memory once per
+    // tile, decide alike, and add their sums at the end.
+    constexpr int COLS = SPLIT ? KT / 2 : KT;           // score columns of this thread
+    constexpr int OC = SPLIT ? HD / 2 : HD;             // output columns of this thread
+    const int half = SPLIT && warp >= 6 ? 1 : 0;
+    const int c0 = half * COLS, oc0 = half * OC;
     const int q4 = warp & 3;
     const int row = q4 * 32 + lane;
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
@@ -263,6 +273,8 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
     const bool rvalid = tok < it.tokens;
     const int rpos = it.pos_start + tok;
     const int rlo = (window > 0 && rpos + 1 > window) ? rpos + 1 - window : 0;
+    const uint32_t pair_bar = 2 + q4;                    // named barrier of the two warps of a quarter
+    const uint32_t x_addr = tmem + lane_base + O_COL + HD;   // spare columns: maxima and sums exchanged
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     pdl_wait();
@@ -270,7 +282,8 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
       const int b = j & 1;
       ok = mbar_wait(&sm.s_full[b], (uint32_t)((j >> 1) & 1));
       if (!ok) { if (lane == 0) atomicExch(status, 7); sm.dead = 1; }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (SPLIT) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 1, 128;" ::: "memory");
       if (sm.dead) { ok = false; break; }
       tc_fence_after();
       const uint32_t s_addr = tmem + lane_base + (uint32_t)b * S_COLS;
@@ -281,26 +294,39 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
       // a tile that every row of the CTA sees completely needs no per-key tests
       const bool interior = it.tokens * G >= ROWS && base + KT - 1 <= it.pos_start &&
                             (window <= 0 || base >= hi + 1 - window);
-      // ---- the whole row of scores into registers (one round trip to tensor memory)
-      uint32_t v[KT];
+      // ---- this thread's scores into registers (one round trip to tensor memory)
+      uint32_t v[COLS];
 #pragma unroll
-      for (int c = 0; c < KT; c += 32) tmem_ld32(s_addr + c, v + c);
+      for (int c = 0; c < COLS; c += 32) tmem_ld32(s_addr + c0 + c, v + c);
       tmem_ld_wait();
       if (!interior) {
 #pragma unroll
-        for (int i = 0; i < KT; ++i)
-          if (i < c_lo || i > c_hi) v[i] = 0xff800000u;      // -inf: the key is not visible
+        for (int i = 0; i < COLS; ++i)
+          if (c0 + i < c_lo || c0 + i > c_hi) v[i] = 0xff800000u;      // -inf: the key is not visible
       }
       // four independent chains, so that a comparison does not wait for the one before it
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < KT; i += 4) {
+      for (int i = 0; i < COLS; i += 4) {
         mx[0] = fmaxf(mx[0], __uint_as_float(v[i]));
         mx[1] = fmaxf(mx[1], __uint_as_float(v[i + 1]));
         mx[2] = fmaxf(mx[2], __uint_as_float(v[i + 2]));
         mx[3] = fmaxf(mx[3], __uint_as_float(v[i + 3]));
       }
       float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      if (SPLIT) {
+        // The two threads of a row share a TMEM lane: they pass their maxima through spare
+        // columns behind the output.  (The column of parity b is written again two tiles on,
+        // after the barrier of the tile between, by which time the partner has read it.)
+        tmem_st1(x_addr + (uint32_t)(b * 2 + half), __float_as_uint(m_tile));
+        tmem_st_wait();
+        tc_fence_before();
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        tc_fence_after();
+        const uint32_t other = tmem_ld1(x_addr + (uint32_t)(b * 2 + (half ^ 1)));
+        tmem_ld_wait();
+        m_tile = fmaxf(m_tile, __uint_as_float(other));
+      }
       m_tile *= scale_log2;
       // the scale in use is replaced only when the maximum has grown by more than 2^8
       const bool grow = m_tile > m_used + 8.0f;
@@ -311,35 +337,34 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
         l *= factor;
       }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // Rare once the maximum has settled: the rows of this warp in O are rescaled.  Only then
-        // must the product P V of the tile before be complete (it writes O); otherwise the
-        // exponentials below run while it is still going.  (That product cannot be more than
-        // one phase behind: it needs this warp's P of the tile before.)
+        // Rare once the maximum has settled: the rows of this warp in O are rescaled (with two
+        // threads per row each its half of the columns; both see the same maxima and decide
+        // alike).  Only then must the product P V of the tile before be complete (it writes O);
+        // otherwise the exponentials below run while it is still going.  (That product cannot
+        // be more than one phase behind: it needs this warp's P of the tile before.)
         bool done = mbar_wait(&sm.o_done, (uint32_t)((j - 1) & 1));
         if (!done) { if (lane == 0) atomicExch(status, 7); sm.dead = 1; }
-        {
-          tc_fence_after();
+        tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < HD; c += 32) {
-            uint32_t v[32];
-            tmem_ld32(tmem + lane_base + O_COL + c, v);
-            tmem_ld_wait();
+        for (int c = 0; c < OC; c += 32) {
+          uint32_t w[32];
+          tmem_ld32(tmem + lane_base + O_COL + oc0 + c, w);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
-            tmem_st32(tmem + lane_base + O_COL + c, v);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * factor);
+          tmem_st32(tmem + lane_base + O_COL + oc0 + c, w);
         }
+        tmem_st_wait();
       }
       // ---- exponentials, sum, P as bfloat16 over the scores (masked scores are -inf: weight 0)
       const float muse = m_used == -INFINITY ? 0.f : m_used;
       // all exponentials first (independent of one another), then the sums, then the packing
 #pragma unroll
-      for (int i = 0; i < KT; ++i)
+      for (int i = 0; i < COLS; ++i)
         v[i] = __float_as_uint(ex2(fmaf(__uint_as_float(v[i]), scale_log2, -muse)));
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < KT; i += 4) {
+      for (int i = 0; i < COLS; i += 4) {
         sum[0] += __uint_as_float(v[i]);
         sum[1] += __uint_as_float(v[i + 1]);
         sum[2] += __uint_as_float(v[i + 2]);
@@ -347,12 +372,12 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
       }
       l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
 #pragma unroll
-      for (int c = 0; c < KT; c += 32) {
+      for (int c = 0; c < COLS; c += 32) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2)
           pk[i >> 1] = pack2(__uint_as_float(v[c + i]), __uint_as_float(v[c + i + 1]));
-        tmem_st16(s_addr + (c >> 1), pk);
+        tmem_st16(s_addr + ((c0 + c) >> 1), pk);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -364,24 +389,34 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
       bool done = mbar_wait(&sm.o_done, (uint32_t)((ntiles - 1) & 1));
       if (!done) { if (lane == 0) atomicExch(status, 7); }
       done = __all_sync(0xffffffffu, done);
+      if (SPLIT) {      // the row's sum is the sum of the two halves' sums
+        tmem_st1(x_addr + (uint32_t)(4 + half), __float_as_uint(l));
+        tmem_st_wait();
+        tc_fence_before();
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        tc_fence_after();
+        const uint32_t other = tmem_ld1(x_addr + (uint32_t)(4 + (half ^ 1)));
+        tmem_ld_wait();
+        l += __uint_as_float(other);
+      }
       if (done) {
         tc_fence_after();
         const float inv = 1.0f / l;
-        bf16* dst = out + ((size_t)(it.row_start + tok) * Hq + head) * HD;
+        bf16* dst = out + ((size_t)(it.row_start + tok) * Hq + head) * HD + oc0;
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + O_COL + c, v);
+        for (int c = 0; c < OC; c += 32) {
+          uint32_t w[32];
+          tmem_ld32(tmem + lane_base + O_COL + oc0 + c, w);
           tmem_ld_wait();
           if (rvalid) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
-              uint4 w;
-              w.x = pack2(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-              w.y = pack2(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-              w.z = pack2(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-              w.w = pack2(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + c + i) = w;
+              uint4 u;
+              u.x = pack2(__uint_as_float(w[i]) * inv, __uint_as_float(w[i + 1]) * inv);
+              u.y = pack2(__uint_as_float(w[i + 2]) * inv, __uint_as_float(w[i + 3]) * inv);
+              u.z = pack2(__uint_as_float(w[i + 4]) * inv, __uint_as_float(w[i + 5]) * inv);
+              u.w = pack2(__uint_as_float(w[i + 6]) * inv, __uint_as_float(w[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c + i) = u;
             }
           }
         }
@@ -428,13 +463,14 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long 
            const bf16* kc, const bf16* vc, long long page_stride, bf16* out,
            const int* table, int table_stride, const int* items, int n_items, int Hq, int Hkv, int page_size,
            float scale, int window, int* status, cudaStream_t s) {
-  auto kernel = attention_tcgen05_kernel<HD>;
+  // keys and values by TMA leave warps 6-9 free: they take half of every row's softmax
+  auto kernel = tma_kv ? attention_tcgen05_kernel<HD, true> : attention_tcgen05_kernel<HD, false>;
   constexpr int smem = (int)sizeof(AttnStorage<HD>) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[2] = {false, false};
+  if (!configured[tma_kv ? 1 : 0]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[tma_kv ? 1 : 0] = true;
   }
   dim3 grid(n_items, Hkv);
   return launch_pdl(kernel, grid, 320, smem, s, mq, mkv, tma_kv, rows_per_page, v_row_off, kc, vc, page_stride, out,

@@ -586,9 +586,10 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
                           view.page_size, scale, window)
         return
     tc = prefill_tcgen05_ok(view, head_dim, group)
-    # two query tiles per CTA pay once there are CTAs enough to fill the GPU several times over
-    # (with fewer, the longer CTAs end less evenly than the gain is worth)
-    x2 = (tc and prefill_x2_ok(view, head_dim, group)
+    # Two query tiles per CTA halve the TMA copies of keys and values: that pays where the copies
+    # bind (pages of 32) and there are CTAs enough to fill the GPU several times over.  With
+    # pages of 64 and more the one-tile kernel, two softmax threads to a row, is as fast or faster.
+    x2 = (tc and prefill_x2_ok(view, head_dim, group) and view.page_size < 64
           and ctx.rows * num_kv_heads >= 4 * sm_count() * (128 // group))
     plan = ctx.attention_plan(group, (256 if x2 else 128 if tc else 64) // group)
     common = (view.k, view.v, view.page_stride, view.block_table)

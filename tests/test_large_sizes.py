@@ -88,7 +88,7 @@ def test_benchmark_sizes_bfloat16_against_float32(models):
 
 def test_long_portion_with_two_query_tiles_per_cta(models, monkeypatch):
     """A prompt portion long enough for the attention kernel with two query tiles per CTA
-    (pages of 64 positions), against the same step with the one-tile kernel: logits at several
+    (pages of 32 positions, where it is chosen), against the same step with the one-tile kernel: logits at several
     places of the portion and a portion that continues a request."""
     from llmario_b200 import kernels
     from llmario_b200.engine import ModelRunner, StepEntry
@@ -109,7 +109,7 @@ def test_long_portion_with_two_query_tiles_per_cta(models, monkeypatch):
         if not two_tiles:
             monkeypatch.setattr(kernels, "prefill_x2_ok", lambda *a: False)
         monkeypatch.setattr(kernels, "attention_tcgen05_x2", counted)
-        runner = ModelRunner(m16, page_size=64, cache_tokens=8192, max_requests=2,
+        runner = ModelRunner(m16, page_size=32, cache_tokens=8192, max_requests=2,
                              max_context=8192, token_budget=4096)
         a = runner.step([StepEntry("r", toks[:2600], want)]).float().cpu().numpy()
         b = runner.step([StepEntry("r", toks[2600:], [0, 1234, 2499])]).float().cpu().numpy()
