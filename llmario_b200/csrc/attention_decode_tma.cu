@@ -54,8 +54,11 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncwarp();
-  pdl_wait();
 
+  // Before the wait on the kernels ahead in the stream, only what none of them writes is read:
+  // the work items, rows and block tables (complete before the step's first layer starts: the
+  // embedding kernel waits before it lets its dependents start) and the keys and values of
+  // positions below the item's first one, which earlier steps wrote.
   const Item it = items ? reinterpret_cast<const Item*>(items)[blockIdx.x]
                         : Item{(int)blockIdx.x, 1, row_slot[blockIdx.x], row_pos[blockIdx.x]};
   const int kvh = blockIdx.y, z = blockIdx.z;
@@ -69,6 +72,31 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
   const int tb0 = tile_first + z * per;
   const int tb1 = min(tile_last + 1, tb0 + per);
   const int* table = block_table + (size_t)it.slot * table_stride;
+
+  // lane 0 asks for the pages of a tile: R = min(page_size, KT) positions per load, K and V of
+  // them in one box
+  const int R = page_size < KT ? page_size : KT;
+  const int lgR = 31 - __clz(R);
+  auto load_tile = [&](int tb, int stage) {
+    const int base = tb * KT;
+    uint32_t bytes = 0;
+    for (int p = base; p < base + KT; p += R)
+      if (p <= hi && p + R - 1 >= lo) bytes += (uint32_t)R * HD * 2 * 2;
+    mbar_expect_tx(&full[stage], bytes);
+    for (int p = base; p < base + KT; p += R) {
+      if (p > hi || p + R - 1 < lo) continue;       // no key of the item here: the page may be gone
+      const int plane = (table[p / page_size] * n_slots + slot) * 2;
+      tma_load_5d(kv_tiles + stage * 2 * TILE_BYTES + ((p - base) >> lgR) * (2 * R * HD * 2), &map_kv, 0, 0,
+                  p % page_size, kvh, plane, &full[stage]);
+    }
+  };
+  int early = 0;          // tiles asked for before the wait: those wholly below the new positions
+  if (lane == 0)
+    for (; early < STAGES && tb0 + early < tb1 && (tb0 + early + 1) * KT <= it.pos_start; ++early)
+      load_tile(tb0 + early, early);
+  pdl_wait();
+  if (lane == 0)
+    for (int i = early; i < STAGES && tb0 + i < tb1; ++i) load_tile(tb0 + i, i);
 
   int cpos[2], clo[2];
   bool cvalid[2];
@@ -98,26 +126,6 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
   for (int d = 0; d < DM; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  // lane 0 asks for the pages of a tile: R = min(page_size, KT) positions per load, K and V of
-  // them in one box
-  const int R = page_size < KT ? page_size : KT;
-  const int lgR = 31 - __clz(R);
-  auto load_tile = [&](int tb, int stage) {
-    const int base = tb * KT;
-    uint32_t bytes = 0;
-    for (int p = base; p < base + KT; p += R)
-      if (p <= hi && p + R - 1 >= lo) bytes += (uint32_t)R * HD * 2 * 2;
-    mbar_expect_tx(&full[stage], bytes);
-    for (int p = base; p < base + KT; p += R) {
-      if (p > hi || p + R - 1 < lo) continue;       // no key of the item here: the page may be gone
-      const int plane = (table[p / page_size] * n_slots + slot) * 2;
-      tma_load_5d(kv_tiles + stage * 2 * TILE_BYTES + ((p - base) >> lgR) * (2 * R * HD * 2), &map_kv, 0, 0,
-                  p % page_size, kvh, plane, &full[stage]);
-    }
-  };
-
-  if (lane == 0)
-    for (int i = 0; i < STAGES && tb0 + i < tb1; ++i) load_tile(tb0 + i, i);
   bool alive = true;
   for (int tb = tb0; tb < tb1; ++tb) {
     const int n_it = tb - tb0;

@@ -8,8 +8,12 @@ LLM_EXPORT void llm_set_pdl(int on) { g_llm_pdl = on ? 1 : 0; }
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ x, int width, int vocab, int* __restrict__ err) {
-  pdl_trigger();
+  // The first kernel of a step's layers waits BEFORE it lets its dependents start: no kernel
+  // after it can begin, not even the part before its own wait, until everything ahead of the
+  // embedding (the step's token, position and block-table updates) is complete.  Kernels of the
+  // layers rely on that when they read block tables and old cache pages before their wait.
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int tok = tokens[t];
   if (tok < 0 || tok >= vocab) {
