@@ -31,13 +31,29 @@ template <int HD> __device__ __forceinline__ int tile_off(int kv, int r, int c, 
   return lin + (((c & 7) ^ ((lin >> 7) & 7)) << 4);
 }
 
-template <int HD, int KT, int STAGES>
+// What the fused form needs beside the attention's own arguments: it starts from the output of
+// the q/k/v product and does the per-head norm, the rotation and the cache write of the new
+// token itself, so that a decode step has no kernel between that product and attention.
+struct Fused {
+  float* proj;              // [rows][proj_stride] 32-bit: Hq heads of q, then Hkv of k and Hkv of v
+  int proj_stride;
+  const float* q_norm_w;    // [HD] each; null: heads are not normed
+  const float* k_norm_w;
+  const float2* cos_sin;    // [rows][HD/2] (cos, sin) of the row's position, scale factor included
+  bf16* k_cache;            // planes of this call's cache slot; null: the cache belongs to
+  bf16* v_cache;            // another call, there is no k or v in proj
+  long long page_stride;
+  float eps;
+  int clear;                // clear what was read of proj (q only when keys are not split: with
+};                          // split keys several CTAs read it and the merge clears it)
+
+template <int HD, int KT, int STAGES, bool FUSED>
 __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, bf16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ items, const int* __restrict__ row_slot,
     const int* __restrict__ row_pos, int Hq, int Hkv, int page_size, int n_slots, int slot,
-    float scale_log2, int window, int splits, int* __restrict__ status) {
+    float scale_log2, int window, int splits, int* __restrict__ status, const Fused fu) {
   constexpr int KS = HD / 16, MT = KT / 16, DM = HD / 16;
   constexpr int TILE_BYTES = KT * HD * 2;            // one K or V tile
   extern __shared__ uint8_t raw[];
@@ -111,7 +127,7 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
     crow[j] = (size_t)(it.row_start + tok) * Hq + head;
   }
   uint32_t qf[KS][2];
-  {
+  if constexpr (!FUSED) {
     const bool valid = g < pairs;
     const int tok = valid ? g / G : 0, head = kvh * G + (valid ? g % G : 0);
     const bf16* src = q + ((size_t)(it.row_start + tok) * Hq + head) * HD + 2 * t;
@@ -119,6 +135,129 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
     for (int k = 0; k < KS; ++k) {
       qf[k][0] = valid ? *reinterpret_cast<const uint32_t*>(src + k * 16) : 0u;
       qf[k][1] = valid ? *reinterpret_cast<const uint32_t*>(src + k * 16 + 8) : 0u;
+    }
+  }
+  // The fused form (items of one token): the lane's 2 * KS pairs of query values are made here
+  // from the projection, in the layout of the fragments: norm over the head (the four lanes of
+  // a pair hold it), rotation of (c, c + HD/2), which lie in the same lane, rounding once.
+  uint32_t k_new[2] = {0u, 0u}, v_new[2] = {0u, 0u};    // this lane's part of the new key and value
+  bool writer = false;
+  if constexpr (FUSED) {
+    constexpr int NP = HD / 64;              // new key and value: lane l has elements NP*l .. and those + HD/2
+    const bool valid = g < G;
+    float* row = fu.proj + (size_t)it.row_start * fu.proj_stride;
+    float* src = row + (kvh * G + (valid ? g : 0)) * HD + 2 * t;
+    float* ks = row + (Hq + kvh) * HD;
+    float* vs = row + (Hq + Hkv + kvh) * HD;
+    const float2* cs_row = fu.cos_sin + (size_t)it.row_start * (HD / 2);
+    // The CTA whose keys end with the new position makes the new key and value, writes them to
+    // the cache and keeps them: its last tile comes from memory without them.
+    writer = fu.k_cache != nullptr && tb0 <= tile_last && tb1 == tile_last + 1;
+    // every load first, so that they are in flight together; then the clearing stores; then the sums
+    float2 x[KS][2], w[KS][2];
+    float4 cs[KS / 2][2];
+    float a[NP], b[NP], va[NP], vb[NP], wa[NP], wb[NP];
+    float2 kcs[NP];
+#pragma unroll
+    for (int k = 0; k < KS; ++k)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        x[k][j] = valid ? *reinterpret_cast<const float2*>(src + 16 * k + 8 * j) : make_float2(0.f, 0.f);
+    if (writer) {
+#pragma unroll
+      for (int e = 0; e < NP; ++e) {
+        a[e] = ks[NP * lane + e], b[e] = ks[HD / 2 + NP * lane + e];
+        va[e] = vs[NP * lane + e], vb[e] = vs[HD / 2 + NP * lane + e];
+        kcs[e] = cs_row[NP * lane + e];
+        wa[e] = fu.k_norm_w ? fu.k_norm_w[NP * lane + e] : 1.f;
+        wb[e] = fu.k_norm_w ? fu.k_norm_w[HD / 2 + NP * lane + e] : 1.f;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < KS; ++k)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        if (fu.q_norm_w) w[k][j] = *reinterpret_cast<const float2*>(fu.q_norm_w + 16 * k + 8 * j + 2 * t);
+        if (k < KS / 2) cs[k][j] = *reinterpret_cast<const float4*>(cs_row + 16 * k + 8 * j + 2 * t);   // (cos, sin) x 2
+      }
+    if (fu.clear) {
+      if (splits == 1 && valid) {
+#pragma unroll
+        for (int k = 0; k < KS; ++k)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) *reinterpret_cast<float2*>(src + 16 * k + 8 * j) = make_float2(0.f, 0.f);
+      }
+      if (writer) {
+#pragma unroll
+        for (int e = 0; e < NP; ++e) {
+          ks[NP * lane + e] = 0.f, ks[HD / 2 + NP * lane + e] = 0.f;
+          vs[NP * lane + e] = 0.f, vs[HD / 2 + NP * lane + e] = 0.f;
+        }
+      }
+    }
+    if (fu.q_norm_w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < KS; ++k)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) ss += x[k][j].x * x[k][j].x + x[k][j].y * x[k][j].y;
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      const float sc = 1.0f / sqrtf(ss / (float)HD + fu.eps);
+#pragma unroll
+      for (int k = 0; k < KS; ++k)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          x[k][j].x = x[k][j].x * sc * w[k][j].x;
+          x[k][j].y = x[k][j].y * sc * w[k][j].y;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < KS / 2; ++k)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float4 c = cs[k][j];
+        const float2 lo2 = x[k][j], hi2 = x[k + KS / 2][j];
+        qf[k][j] = pack_bf16(lo2.x * c.x - hi2.x * c.y, lo2.y * c.z - hi2.y * c.w);
+        qf[k + KS / 2][j] = pack_bf16(lo2.x * c.y + hi2.x * c.x, lo2.y * c.w + hi2.y * c.z);
+      }
+    if (writer) {
+      if (fu.k_norm_w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < NP; ++e) ss += a[e] * a[e];
+#pragma unroll
+        for (int e = 0; e < NP; ++e) ss += b[e] * b[e];
+        ss = warp_sum(ss);
+        const float sc = 1.0f / sqrtf(ss / (float)HD + fu.eps);
+#pragma unroll
+        for (int e = 0; e < NP; ++e) {
+          a[e] = a[e] * sc * wa[e];
+          b[e] = b[e] * sc * wb[e];
+        }
+      }
+      float ra[2] = {0.f, 0.f}, rb[2] = {0.f, 0.f};
+#pragma unroll
+      for (int e = 0; e < NP; ++e) {
+        ra[e] = a[e] * kcs[e].x - b[e] * kcs[e].y;
+        rb[e] = a[e] * kcs[e].y + b[e] * kcs[e].x;
+      }
+      k_new[0] = pack_bf16(ra[0], ra[1]), k_new[1] = pack_bf16(rb[0], rb[1]);
+      v_new[0] = pack_bf16(va[0], NP > 1 ? va[NP - 1] : 0.f);
+      v_new[1] = pack_bf16(vb[0], NP > 1 ? vb[NP - 1] : 0.f);
+      const size_t at = (size_t)table[hi / page_size] * fu.page_stride +
+                        (size_t)(kvh * page_size + hi % page_size) * HD;
+      if (NP == 2) {
+        *reinterpret_cast<uint32_t*>(fu.k_cache + at + 2 * lane) = k_new[0];
+        *reinterpret_cast<uint32_t*>(fu.k_cache + at + HD / 2 + 2 * lane) = k_new[1];
+        *reinterpret_cast<uint32_t*>(fu.v_cache + at + 2 * lane) = v_new[0];
+        *reinterpret_cast<uint32_t*>(fu.v_cache + at + HD / 2 + 2 * lane) = v_new[1];
+      } else {
+        reinterpret_cast<uint16_t*>(fu.k_cache + at)[lane] = (uint16_t)k_new[0];
+        reinterpret_cast<uint16_t*>(fu.k_cache + at)[HD / 2 + lane] = (uint16_t)k_new[1];
+        reinterpret_cast<uint16_t*>(fu.v_cache + at)[lane] = (uint16_t)v_new[0];
+        reinterpret_cast<uint16_t*>(fu.v_cache + at)[HD / 2 + lane] = (uint16_t)v_new[1];
+      }
     }
   }
   float o[DM][4];
@@ -148,6 +287,21 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
           uint4* vz = reinterpret_cast<uint4*>(tile + ((p - base) >> lgR) * (2 * R * HD * 2) + R * HD * 2);
           for (int i = lane; i < R * HD * 2 / 16; i += 32) vz[i] = make_uint4(0, 0, 0, 0);
         }
+      if (FUSED && writer && tb == tile_last) {      // the new key and value, over what memory held there
+        constexpr int NP = HD / 64;
+        const int r = hi - base, c0 = NP * lane, c1 = HD / 2 + NP * lane;
+        uint8_t* k0 = tile + tile_off<HD>(0, r, c0 >> 3, lgR) + (c0 & 7) * 2;
+        uint8_t* k1 = tile + tile_off<HD>(0, r, c1 >> 3, lgR) + (c1 & 7) * 2;
+        uint8_t* v0 = tile + tile_off<HD>(1, r, c0 >> 3, lgR) + (c0 & 7) * 2;
+        uint8_t* v1 = tile + tile_off<HD>(1, r, c1 >> 3, lgR) + (c1 & 7) * 2;
+        if (NP == 2) {
+          *reinterpret_cast<uint32_t*>(k0) = k_new[0], *reinterpret_cast<uint32_t*>(k1) = k_new[1];
+          *reinterpret_cast<uint32_t*>(v0) = v_new[0], *reinterpret_cast<uint32_t*>(v1) = v_new[1];
+        } else {
+          *reinterpret_cast<uint16_t*>(k0) = (uint16_t)k_new[0], *reinterpret_cast<uint16_t*>(k1) = (uint16_t)k_new[1];
+          *reinterpret_cast<uint16_t*>(v0) = (uint16_t)v_new[0], *reinterpret_cast<uint16_t*>(v1) = (uint16_t)v_new[1];
+        }
+      }
       __syncwarp();
     }
 
@@ -261,13 +415,13 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
   }
 }
 
-template <int HD>
+template <int HD, bool FUSED>
 int launch(const CUtensorMap& map, const bf16* q, bf16* out, float* part_o, float* part_ml, const int* table,
            int table_stride, const int* items, const int* row_slot, const int* row_pos, int n_items, int Hq,
            int Hkv, int page_size, int n_slots, int slot, float scale, int window, int splits, int* status,
-           cudaStream_t s) {
+           const Fused& fu, cudaStream_t s) {
   constexpr int KT = 32, STAGES = 4;
-  auto kernel = flash_decode_tma_kernel<HD, KT, STAGES>;
+  auto kernel = flash_decode_tma_kernel<HD, KT, STAGES, FUSED>;
   constexpr int smem = 2 * STAGES * KT * HD * 2 + STAGES * 8 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -278,20 +432,11 @@ int launch(const CUtensorMap& map, const bf16* q, bf16* out, float* part_o, floa
   dim3 grid(n_items, Hkv, splits);
   return launch_pdl(kernel, grid, 32, smem, s, map, q, out, part_o, part_ml, table, table_stride, items,
                     row_slot, row_pos, Hq, Hkv, page_size, n_slots, slot, scale * 1.4426950408889634f, window,
-                    splits, status);
+                    splits, status, fu);
 }
-}  // namespace
 
-// storage: the group's whole cache [n_pages][n_slots][2][Hkv][page_size][hd] bfloat16, contiguous;
-// slot: the cache slot of this layer call.  page_size must divide 32 or be a multiple of it.
-// Other arguments as llm_attention_decode.
-LLM_EXPORT int llm_attention_decode_tma(const void* q, void* out, float* part_o, float* part_ml,
-                                        const void* storage, long long n_pages, int n_slots, int slot,
-                                        const int* block_table, int table_stride, const int* items,
-                                        const int* row_slot, const int* row_pos, int n_items, int Hq,
-                                        int Hkv, int hd, int page_size, float scale, int window,
-                                        int splits, int* status, cudaStream_t stream) {
-  if (n_items <= 0) return 0;
+int check_and_map(const void* storage, long long n_pages, int n_slots, int slot, int Hq, int Hkv, int hd,
+                  int page_size, int splits, const float* part_o, const float* part_ml, CUtensorMap* map) {
   if (Hkv <= 0 || Hq % Hkv || splits < 1) return LLM_ERR_ARGUMENT;
   if (splits > 1 && (!part_o || !part_ml)) return LLM_ERR_ARGUMENT;
   if (hd != 64 && hd != 128) return LLM_ERR_UNSUPPORTED;
@@ -306,12 +451,66 @@ LLM_EXPORT int llm_attention_decode_tma(const void* q, void* out, float* part_o,
   const long long strides[4] = {128, (long long)hd * 2, (long long)page_size * hd * 2,
                                 (long long)Hkv * page_size * hd * 2};
   const int box[5] = {64, hd / 64, R, 1, 2};
+  return llm_tensor_map_tiled(storage, 5, dims, strides, box, map) ? 0 : LLM_ERR_UNSUPPORTED;
+}
+}  // namespace
+
+// storage: the group's whole cache [n_pages][n_slots][2][Hkv][page_size][hd] bfloat16, contiguous;
+// slot: the cache slot of this layer call.  page_size must divide 32 or be a multiple of it.
+// Other arguments as llm_attention_decode.
+LLM_EXPORT int llm_attention_decode_tma(const void* q, void* out, float* part_o, float* part_ml,
+                                        const void* storage, long long n_pages, int n_slots, int slot,
+                                        const int* block_table, int table_stride, const int* items,
+                                        const int* row_slot, const int* row_pos, int n_items, int Hq,
+                                        int Hkv, int hd, int page_size, float scale, int window,
+                                        int splits, int* status, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
   CUtensorMap map;
-  if (!llm_tensor_map_tiled(storage, 5, dims, strides, box, &map)) return LLM_ERR_UNSUPPORTED;
+  if (int e = check_and_map(storage, n_pages, n_slots, slot, Hq, Hkv, hd, page_size, splits, part_o, part_ml, &map))
+    return e;
+  const Fused none = {};
 #define GO(HD)                                                                                          \
-  return launch<HD>(map, (const bf16*)q, (bf16*)out, part_o, part_ml, block_table, table_stride, items,  \
-                    row_slot, row_pos, n_items, Hq, Hkv, page_size, (int)n_slots, slot, scale, window, splits,  \
-                    status, stream)
+  return launch<HD, false>(map, (const bf16*)q, (bf16*)out, part_o, part_ml, block_table, table_stride,  \
+                           items, row_slot, row_pos, n_items, Hq, Hkv, page_size, (int)n_slots, slot, scale, \
+                           window, splits, status, none, stream)
+  if (hd == 128) GO(128);
+  GO(64);
+#undef GO
+}
+
+// The decode step's form: every row is one new token of its own request (row_slot, row_pos).
+// proj [rows][proj_stride] is the 32-bit output of the q/k/v product (Hq heads of q, then, with
+// k_cache given, Hkv heads of k and Hkv of v).  The kernel norms each head of q and k
+// (q_norm_w / k_norm_w, 32-bit [hd], both or neither), rotates them whole by cos_sin
+// [rows][hd/2] (cos, sin), writes the new key and value into k_cache / v_cache (the planes of
+// this call's cache slot, pages page_stride elements apart) and attends.  With clear it zeroes
+// what it consumed of proj, except the queries when splits > 1: several CTAs read those, and
+// llm_attention_merge_clear zeroes them after all have.  The arithmetic of norm and rotation is
+// that of llm_qk_norm_rope_store.
+LLM_EXPORT int llm_attention_decode_fused(float* proj, int proj_stride, void* out, float* part_o,
+                                          float* part_ml, const void* storage, long long n_pages,
+                                          int n_slots, int slot, void* k_cache, void* v_cache,
+                                          long long page_stride, const int* block_table,
+                                          int table_stride, const int* row_slot, const int* row_pos,
+                                          int rows, const float* q_norm_w, const float* k_norm_w,
+                                          const float* cos_sin, float eps, int clear, int Hq, int Hkv,
+                                          int hd, int page_size, float scale, int window, int splits,
+                                          int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!proj || !cos_sin || !row_slot || !row_pos || (q_norm_w == nullptr) != (k_norm_w == nullptr) ||
+      (k_cache == nullptr) != (v_cache == nullptr))
+    return LLM_ERR_ARGUMENT;
+  if (Hkv > 0 && Hq / Hkv > 8) return LLM_ERR_UNSUPPORTED;      // one token's heads are the eight columns
+  if (proj_stride & 1) return LLM_ERR_UNSUPPORTED;               // 8-byte loads
+  CUtensorMap map;
+  if (int e = check_and_map(storage, n_pages, n_slots, slot, Hq, Hkv, hd, page_size, splits, part_o, part_ml, &map))
+    return e;
+  const Fused fu = {proj, proj_stride, q_norm_w, k_norm_w, reinterpret_cast<const float2*>(cos_sin),
+                    (bf16*)k_cache, (bf16*)v_cache, page_stride, eps, clear};
+#define GO(HD)                                                                                          \
+  return launch<HD, true>(map, nullptr, (bf16*)out, part_o, part_ml, block_table, table_stride, nullptr,  \
+                          row_slot, row_pos, rows, Hq, Hkv, page_size, (int)n_slots, slot, scale, window,   \
+                          splits, status, fu, stream)
   if (hd == 128) GO(128);
   GO(64);
 #undef GO

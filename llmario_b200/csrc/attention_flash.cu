@@ -260,10 +260,15 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 6) flash_paged_ke
 // out[row][head] = sum_z 2^(m_z - m*) o_z / sum_z 2^(m_z - m*) l_z   over the parts of a row
 template <int HD>
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                             bf16* __restrict__ out, const int* __restrict__ rows, int Hq, int splits) {
+                             bf16* __restrict__ out, const int* __restrict__ rows, int Hq, int splits,
+                             float* __restrict__ clear, int clear_stride) {
   pdl_trigger();
   pdl_wait();
-  const size_t rowhead = (size_t)(rows ? rows[blockIdx.x] : (int)blockIdx.x) * Hq + blockIdx.y;
+  const int row = rows ? rows[blockIdx.x] : (int)blockIdx.x;
+  const size_t rowhead = (size_t)row * Hq + blockIdx.y;
+  if (clear)      // the head's queries in the projection buffer, which every part has read by now
+    for (int d = threadIdx.x; d < HD; d += blockDim.x)
+      clear[(size_t)row * clear_stride + blockIdx.y * HD + d] = 0.f;
   float mstar = -INFINITY;
   for (int z = 0; z < splits; ++z) mstar = fmaxf(mstar, part_ml[(rowhead * splits + z) * 2]);
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
@@ -332,15 +337,24 @@ LLM_EXPORT int llm_attention_flash(const void* q, void* out, float* part_o, floa
   return LLM_ERR_UNSUPPORTED;
 }
 
+// Merge of the parts of split keys.  With clear given, also clear[row][head * hd .. + hd) = 0 for
+// every merged (row, head): the queries that llm_attention_decode_fused leaves in the projection
+// buffer when it splits the keys.
+LLM_EXPORT int llm_attention_merge_clear(const float* part_o, const float* part_ml, void* out,
+                                         const int* rows, int n_rows, int Hq, int hd, int splits,
+                                         float* clear, int clear_stride, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  dim3 grid(n_rows, Hq);
+  if (hd == 128) return launch_pdl(merge_kernel<128>, grid, 128, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride);
+  if (hd == 64) return launch_pdl(merge_kernel<64>, grid, 64, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride);
+  if (hd == 32) return launch_pdl(merge_kernel<32>, grid, 32, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride);
+  return LLM_ERR_UNSUPPORTED;
+}
+
 LLM_EXPORT int llm_attention_merge(const float* part_o, const float* part_ml, void* out,
                                    const int* rows, int n_rows, int Hq, int hd, int splits,
                                    cudaStream_t stream) {
-  if (n_rows <= 0) return 0;
-  dim3 grid(n_rows, Hq);
-  if (hd == 128) return launch_pdl(merge_kernel<128>, grid, 128, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits);
-  if (hd == 64) return launch_pdl(merge_kernel<64>, grid, 64, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits);
-  if (hd == 32) return launch_pdl(merge_kernel<32>, grid, 32, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits);
-  return LLM_ERR_UNSUPPORTED;
+  return llm_attention_merge_clear(part_o, part_ml, out, rows, n_rows, Hq, hd, splits, nullptr, 0, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

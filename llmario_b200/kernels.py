@@ -54,6 +54,9 @@ def _signatures():
         "llm_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "llm_attention_flash": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "llm_attention_merge": [P, P, P, P, I, I, I, I, P],
+        "llm_attention_merge_clear": [P, P, P, P, I, I, I, I, P, I, P],
+        "llm_attention_decode_fused": [P, I, P, P, P, P, L, I, I, P, P, L, P, I, P, P, I, P, P, P,
+                                       F, I, I, I, I, I, F, I, I, P, P],
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
         "llm_attention_decode_tma": [P, P, P, P, P, L, I, I, P, I, P, P, P, I, I, I, I, I, F, I,
                                      I, P, P],
@@ -550,10 +553,70 @@ def decode_tma_ok(view, head_dim: int) -> bool:
 
 def attention_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor,
                     rows: Optional[torch.Tensor], n_rows: int, num_heads: int, head_dim: int,
-                    splits: int) -> None:
-    _cuda(part_o, part_ml, out, rows)
-    _check(lib().llm_attention_merge(_ptr(part_o), _ptr(part_ml), _ptr(out), _ptr(rows), n_rows,
-                                     num_heads, head_dim, splits, _stream()), "attention_merge")
+                    splits: int, clear: Optional[torch.Tensor] = None) -> None:
+    """Merge the parts of split keys.  ``clear`` (float32 [rows, >= heads * head_dim]): the
+    first heads * head_dim values of every merged row of it are zeroed as well."""
+    _cuda(part_o, part_ml, out, rows, clear)
+    _check(lib().llm_attention_merge_clear(
+        _ptr(part_o), _ptr(part_ml), _ptr(out), _ptr(rows), n_rows, num_heads, head_dim, splits,
+        _ptr(clear), clear.stride(0) if clear is not None else 0, _stream()), "attention_merge")
+
+
+FUSE_DECODE = "few waves"     # or "always" / "never": for measurements
+
+
+def decode_fusion_ok(ctx, view, num_heads: int, num_kv_heads: int, head_dim: int, rot_dim: int,
+                     cos_sin: Optional[torch.Tensor], window: Optional[int] = None) -> bool:
+    """Whether the step runs norm, rotation, cache write and attention as one kernel: every
+    row a single new token, 16-bit, whole heads rotated by the step's table of cosines and
+    sines, a cache the TMA decode kernel takes, and at most two waves of CTAs (every wave pays
+    the longer start of the fused kernel; from about four waves on that costs more than the
+    separate rotation kernel: Qwen3-8B sizes at batch 64, 5.71 against 5.67 ms a step)."""
+    if FUSE_DECODE == "never":
+        return False
+    ok = (ctx.dtype == torch.bfloat16 and cos_sin is not None and rot_dim == head_dim
+          and num_heads // num_kv_heads <= 8 and decode_tma_ok(view, head_dim)
+          and all(s.rows == 1 for s in ctx.segments))
+    if not ok or FUSE_DECODE == "always":
+        return ok
+    reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
+    resident = 3 * sm_count()
+    return ctx.rows * num_kv_heads * decode_splits(ctx.rows, num_kv_heads, reach, resident) <= 2 * resident
+
+
+def attention_decode_fused(ctx, proj: torch.Tensor, out: torch.Tensor, view, writes_cache: bool,
+                           q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor],
+                           cos_sin: torch.Tensor, eps: float, clear: bool, num_heads: int,
+                           num_kv_heads: int, head_dim: int, scale: float,
+                           window: Optional[int], splits: Optional[int] = None) -> None:
+    """A decode step's attention from the output of the q/k/v product ``proj`` (float32
+    [rows, (heads + 2 kv heads) * head_dim], or only the queries when another call owns the
+    cache): per-head norm, rotation, write of the new key and value, attention over the cache
+    and, with split keys, the merge.  With ``clear`` what was consumed of ``proj`` is zeroed."""
+    _cuda(proj, out, view.storage, view.block_table, ctx.row_slot, ctx.row_pos, q_norm_w,
+          k_norm_w, cos_sin)
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and out.dtype == torch.bfloat16
+    assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+    rows = ctx.rows
+    reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
+    if splits is None:
+        splits = decode_splits(rows, num_kv_heads, reach, 3 * sm_count())
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = ctx.buffer("attn.part_o", (rows * num_heads * splits * head_dim,), torch.float32)
+        part_ml = ctx.buffer("attn.part_ml", (rows * num_heads * splits * 2,), torch.float32)
+    st = view.storage
+    _check(lib().llm_attention_decode_fused(
+        _ptr(proj), proj.stride(0), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(st), st.shape[0],
+        st.shape[1], view.slot, _ptr(view.k if writes_cache else None),
+        _ptr(view.v if writes_cache else None), view.page_stride, _ptr(view.block_table),
+        view.block_table.stride(0), _ptr(ctx.row_slot), _ptr(ctx.row_pos), rows, _ptr(q_norm_w),
+        _ptr(k_norm_w), _ptr(cos_sin), float(eps), int(clear), num_heads, num_kv_heads, head_dim,
+        view.page_size, float(scale), int(window or 0), splits, _ptr(tc_status(proj.device)),
+        _stream()), f"attention_decode_fused (head_dim {head_dim})")
+    if splits > 1:
+        attention_merge(part_o, part_ml, out, None, rows, num_heads, head_dim, splits,
+                        clear=proj if clear else None)
 
 
 def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int = 444) -> int:

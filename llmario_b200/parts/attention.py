@@ -58,7 +58,6 @@ class Attention:
         proj = ctx.buffer("attn.proj.%s%d" % ("z" if kept_zero else "", width), (rows, width),
                           torch.float32, zero=kept_zero)
         (self.qkv_proj if call.writes_cache else self.q_proj)(h, proj, out_is_zero=kept_zero)
-        q = ctx.buffer("attn.q", (rows, self.q_width))
         tables = self.position.rotary_tables() if self.position is not None else None
         if self.position is not None and tables is None:
             raise NotImplementedError("a position encoding that is not a rotation needs its own "
@@ -66,6 +65,19 @@ class Attention:
         inv_freq, rot_dim, attn_factor = tables if tables else (None, 0, 1.0)
         angles = self.position.step_angles(ctx) if tables and hasattr(self.position, "step_angles") \
             else None
+        out = ctx.buffer("attn.out", (rows, self.q_width))
+        q = ctx.buffer("attn.q", (rows, self.q_width))
+        if kernels.decode_fusion_ok(ctx, view, self.num_heads, self.num_kv_heads, self.head_dim,
+                                    rot_dim, angles, self.window):
+            # a step of single new tokens: norm, rotation, cache write and attention in one kernel
+            kernels.attention_decode_fused(
+                ctx, proj, out, view, call.writes_cache,
+                self.q_norm.weight if self.q_norm is not None else None,
+                self.k_norm.weight if self.k_norm is not None else None, angles,
+                self.q_norm.eps if self.q_norm is not None else 0.0, kept_zero, self.num_heads,
+                self.num_kv_heads, self.head_dim, self.scale, self.window)
+            self.o_proj(out, x, accumulate=True)
+            return
         kernels.qk_norm_rope_store(
             proj, q, view.k if call.writes_cache else None,
             view.v if call.writes_cache else None, view.page_stride, view.block_table,
@@ -75,7 +87,6 @@ class Attention:
             inv_freq, attn_factor, self.num_heads, self.num_kv_heads, self.head_dim, rot_dim,
             view.page_size, self.q_norm.eps if self.q_norm is not None else 0.0, angles,
             clear_proj=kept_zero)
-        out = ctx.buffer("attn.out", (rows, self.q_width))
         kernels.attention(ctx, q, out, view, self.num_heads, self.num_kv_heads, self.head_dim,
                           self.scale, self.window)
         self.o_proj(out, x, accumulate=True)

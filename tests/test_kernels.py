@@ -465,6 +465,80 @@ def test_attention_decode(Hq, Hkv, hd, page, window, tma):
         check(rows, out, q)
 
 
+@pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (6, 3, 64, 8, 50),
+                                                   (8, 1, 128, 16, 200), (3, 1, 64, 32, None),
+                                                   (32, 8, 128, 64, None), (4, 4, 64, 128, 100)])
+@pytest.mark.parametrize("norm", [True, False])
+def test_attention_decode_fused(Hq, Hkv, hd, page, window, norm):
+    """Norm, rotation, cache write and decode attention in one kernel, against the two kernels
+    it stands for (and so, through their tests, against the plain formulas): outputs, the new
+    keys and values in the cache, and the cleared projection; keys whole and split; a call that
+    reads a cache it does not own."""
+    from types import SimpleNamespace
+    from llmario_b200 import kernels
+    dtype = torch.bfloat16
+    lengths = [1, 33, 150, 64, 700, 385, 32, 65]     # new tokens at the start and end of pages too
+    rows = len(lengths)
+    base, table, _, _ = paged_setup(lengths, page, Hkv, hd, dtype)
+    scale, eps = 1 / math.sqrt(hd), 1e-5
+    slot = torch.arange(rows, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    width = (Hq + 2 * Hkv) * hd
+    proj = rnd(rows, width, scale=2.0, seed=3)
+    qw = (1 + 0.1 * rnd(hd, seed=1)) if norm else None
+    kw = (1 + 0.1 * rnd(hd, seed=2)) if norm else None
+    inv_freq = torch.tensor(np.power(np.float32(1e4), -(np.arange(hd // 2, dtype=np.float32) * 2) / hd)
+                            .astype(np.float32), device=DEV)
+    cs = torch.empty(rows, hd // 2, 2, dtype=torch.float32, device=DEV)
+    kernels.rope_table(pos, inv_freq, cs, 1.0)
+    bufs = {}
+
+    def buffer(name, shape, dt=torch.bfloat16, zero=False):
+        return bufs.setdefault((name, tuple(shape)), torch.empty(*shape, dtype=dt, device=DEV))
+
+    ctx = SimpleNamespace(rows=rows, max_pos=max(lengths) - 1, row_slot=slot, row_pos=pos,
+                          buffer=buffer, dtype=dtype,
+                          segments=[SimpleNamespace(rows=1) for _ in range(rows)])
+
+    def view_of(storage):
+        return SimpleNamespace(storage=storage, slot=1, k=storage[0, 1, 0], v=storage[0, 1, 1],
+                               page_stride=storage.stride(0), block_table=table, page_size=page)
+
+    for writes in (True, False):
+        w = width if writes else Hq * hd
+        for splits in (1, 3, 5):
+            # the two kernels
+            st_a, used_a = base.clone(), proj[:, :w].clone()
+            q = torch.empty(rows, Hq * hd, dtype=dtype, device=DEV)
+            kernels.qk_norm_rope_store(used_a, q, st_a[0, 1, 0] if writes else None,
+                                       st_a[0, 1, 1] if writes else None, st_a.stride(0), table, slot,
+                                       pos, qw, kw, inv_freq, 1.0, Hq, Hkv, hd, hd, page, eps, cs,
+                                       clear_proj=True)
+            ref = torch.zeros(rows, Hq * hd, dtype=dtype, device=DEV)
+            po = torch.empty(rows * Hq * splits * hd, dtype=torch.float32, device=DEV)
+            pml = torch.empty(rows * Hq * splits * 2, dtype=torch.float32, device=DEV)
+            kernels.attention_decode_tma(q, ref, st_a, 1, table, None, rows, Hq, Hkv, hd, page, scale,
+                                         window, splits, po, pml, slot, pos)
+            if splits > 1:
+                kernels.attention_merge(po, pml, ref, None, rows, Hq, hd, splits)
+            # the one kernel
+            st_b, used_b = base.clone(), proj[:, :w].clone()
+            got = torch.zeros(rows, Hq * hd, dtype=dtype, device=DEV)
+            assert kernels.decode_fusion_ok(ctx, view_of(st_b), Hq, Hkv, hd, hd, cs, window)
+            kernels.attention_decode_fused(ctx, used_b, got, view_of(st_b), writes, qw, kw, cs, eps,
+                                           True, Hq, Hkv, hd, scale, window, splits=splits)
+            kernels.check_tc_status(DEV)
+            assert int((used_b != 0).sum()) == 0 and int((used_a != 0).sum()) == 0
+            # the cache: bit for bit what the rotation kernel wrote, or the neighbouring bfloat16
+            # value where the two kernels' sums rounded differently
+            diff = (st_b.float() - st_a.float()).abs()
+            assert (diff <= 2.0 ** -7 * st_a.float().abs() + 1e-6).all()
+            if writes:
+                assert not torch.equal(st_a, base)
+            else:
+                assert torch.equal(st_b, base)
+            assert (got.float() - ref.float()).abs().max() <= 2e-2, (writes, splits)
+
 @pytest.mark.parametrize("page,window", [(16, None), (64, None), (16, 200), (64, 130)])
 @pytest.mark.parametrize("kernel", ["decode", "decode_tma", "tcgen05", "tcgen05_x2"])
 def test_tensor_core_attention_finds_the_key_that_stands_out(kernel, page, window):
