@@ -20,20 +20,31 @@ from .. import kernels
 DEV = "cuda:0"
 
 
-def timed(fn, reps: int, flush) -> float:
+def timed(fn, reps: int, flush, chain: int = 1) -> float:
+    """Median time of a launch in ms.  ``chain`` > 1: that many launches, recorded as a CUDA
+    graph, between the two events (time per launch): the host's own time to issue a launch, tens
+    of microseconds from Python, is then out of the picture, as it is inside a recorded step."""
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
+    if chain > 1:      # recorded once and replayed: Python cannot issue launches as fast as they run
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(chain):
+                fn()
+        run = graph.replay
+    else:
+        run = fn
     times = []
     for _ in range(reps):
         if flush is not None:
             flush.zero_()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        fn()
+        run()
         b.record()
         torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
+        times.append(a.elapsed_time(b) / chain)
     times.sort()
     return times[len(times) // 2]
 
@@ -101,7 +112,7 @@ def cmd_attention(a) -> None:
         if splits > 1:
             kernels.attention_merge(po, pml, out, None, B, Hq, hd, splits)
 
-    ms = timed(fn, a.reps, flush)
+    ms = timed(fn, a.reps, flush, a.chain)
     nbytes = B * S * Hkv * hd * 2 * 2
     print(f"decode attention batch={B} context={S} heads={Hq}/{Hkv} hd={hd} splits={splits}: "
           f"{ms * 1e3:.1f} us, cache {nbytes / ms / 1e6:.0f} GB/s")
@@ -124,13 +135,13 @@ def cmd_prefill_attention(a) -> None:
     elif x2:
         fn = lambda: kernels.attention_tcgen05_x2(q, out, storage[0, 0, 0], storage[0, 0, 1],
                                                   storage.stride(0), table, items, n, Hq, Hkv, hd,
-                                                  page, hd ** -0.5, None, storage.shape[0])
+                                                  page, hd ** -0.5, a.window, storage.shape[0])
     else:
         fn = lambda: kernels.attention_tcgen05(q, out, storage[0, 0, 0], storage[0, 0, 1],
                                                storage.stride(0), table, items, n, Hq, Hkv, hd,
-                                               page, hd ** -0.5, None,
+                                               page, hd ** -0.5, a.window,
                                                0 if a.cp_async else storage.shape[0])
-    ms = timed(fn, a.reps, None)
+    ms = timed(fn, a.reps, None, a.chain)
     kernels.check_tc_status(DEV)
     flops = 2.0 * T * T * Hq * hd          # causal: half of QK^T and PV
     print(f"prefill attention tokens={T} heads={Hq}/{Hkv} hd={hd}: {ms * 1e3:.1f} us, "
@@ -192,6 +203,8 @@ def main(argv=None) -> int:
     d.add_argument("--splits", type=int, default=0)
     d.add_argument("--cp-async", action="store_true",
                    help="the decode kernel that loads with cp.async instead of TMA tiles")
+    d.add_argument("--chain", type=int, default=1,
+                   help="launches per timed interval (hides the host's launch time)")
     d.add_argument("--row-major", action="store_true",
                    help="the 16-row kernel of attention_flash.cu instead of the decode kernel")
     d.set_defaults(fn=cmd_attention)
@@ -203,6 +216,9 @@ def main(argv=None) -> int:
                    help="K and V by cp.async copies even where the pages are large enough for TMA")
     p.add_argument("--one-tile", action="store_true",
                    help="one query tile per CTA even where the pages allow two")
+    p.add_argument("--window", type=int, default=None, help="attend to this many last keys only")
+    p.add_argument("--chain", type=int, default=1,
+                   help="launches per timed interval (hides the host's launch time)")
     p.set_defaults(fn=cmd_prefill_attention)
     st = sub.add_parser("step")
     st.add_argument("--model", default="qwen3-8b")

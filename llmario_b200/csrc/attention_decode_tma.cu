@@ -89,30 +89,39 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
   const int tb1 = min(tile_last + 1, tb0 + per);
   const int* table = block_table + (size_t)it.slot * table_stride;
 
-  // lane 0 asks for the pages of a tile: R = min(page_size, KT) positions per load, K and V of
-  // them in one box
+  // The pages of a tile are asked for R = min(page_size, KT) positions at a time, K and V of
+  // them in one box.  The warp keeps 32 entries of the block table in its lanes (one load for
+  // every 32 pages walked), so that no tile waits on a load of a page number.
   const int R = page_size < KT ? page_size : KT;
   const int lgR = 31 - __clz(R);
-  auto load_tile = [&](int tb, int stage) {
+  const int lgP = 31 - __clz(page_size);            // pages hold a power of two of positions here
+  const int last_page = hi >> lgP;
+  int held_from = (tb0 * KT) >> lgP;
+  int held = held_from + lane <= last_page ? table[held_from + lane] : 0;
+  auto load_tile = [&](int tb, int stage) {         // the whole warp calls it; lane 0 issues
     const int base = tb * KT;
     uint32_t bytes = 0;
     for (int p = base; p < base + KT; p += R)
       if (p <= hi && p + R - 1 >= lo) bytes += (uint32_t)R * HD * 2 * 2;
-    mbar_expect_tx(&full[stage], bytes);
+    if (lane == 0) mbar_expect_tx(&full[stage], bytes);
     for (int p = base; p < base + KT; p += R) {
       if (p > hi || p + R - 1 < lo) continue;       // no key of the item here: the page may be gone
-      const int plane = (table[p / page_size] * n_slots + slot) * 2;
-      tma_load_5d(kv_tiles + stage * 2 * TILE_BYTES + ((p - base) >> lgR) * (2 * R * HD * 2), &map_kv, 0, 0,
-                  p % page_size, kvh, plane, &full[stage]);
+      const int pi = p >> lgP;
+      if (pi < held_from || pi >= held_from + 32) {
+        held_from = pi;
+        held = pi + lane <= last_page ? table[pi + lane] : 0;
+      }
+      const int plane = (__shfl_sync(0xffffffffu, held, pi - held_from) * n_slots + slot) * 2;
+      if (lane == 0)
+        tma_load_5d(kv_tiles + stage * 2 * TILE_BYTES + ((p - base) >> lgR) * (2 * R * HD * 2), &map_kv, 0, 0,
+                    p & (page_size - 1), kvh, plane, &full[stage]);
     }
   };
   int early = 0;          // tiles asked for before the wait: those wholly below the new positions
-  if (lane == 0)
-    for (; early < STAGES && tb0 + early < tb1 && (tb0 + early + 1) * KT <= it.pos_start; ++early)
-      load_tile(tb0 + early, early);
+  for (; early < STAGES && tb0 + early < tb1 && (tb0 + early + 1) * KT <= it.pos_start; ++early)
+    load_tile(tb0 + early, early);
   pdl_wait();
-  if (lane == 0)
-    for (int i = early; i < STAGES && tb0 + i < tb1; ++i) load_tile(tb0 + i, i);
+  for (int i = early; i < STAGES && tb0 + i < tb1; ++i) load_tile(tb0 + i, i);
 
   int cpos[2], clo[2];
   bool cvalid[2];
@@ -373,8 +382,8 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
       }
     }
     __syncwarp();                  // every lane has read this stage
-    if (lane == 0 && tb + STAGES < tb1) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (tb + STAGES < tb1) {
+      if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       load_tile(tb + STAGES, stage);
     }
   }
