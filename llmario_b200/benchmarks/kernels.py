@@ -92,7 +92,9 @@ def cmd_attention(a) -> None:
     out = torch.empty_like(q)
     slot = torch.arange(B, dtype=torch.int32, device=DEV)
     pos = torch.full((B,), S - 1, dtype=torch.int32, device=DEV)
-    splits = a.splits or kernels.decode_splits(B, Hkv, S)
+    tma = not (a.row_major or a.cp_async)
+    splits = a.splits or kernels.decode_splits(B, Hkv, S, (3 if tma else 6) * kernels.sm_count(),
+                                               kernels.DECODE_TMA_TILE if tma else 32)
     po = torch.empty(B * Hq * splits * hd, dtype=torch.float32, device=DEV)
     pml = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=DEV)
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=DEV)

@@ -6,15 +6,16 @@
 // layers is one tensor [page][cache slot][K|V][kv head][position][head dim].  One tensor map of
 // five dimensions describes it (64 columns of a row, the 64-column halves of a row, the
 // positions of a page, the KV heads, the K and V planes of all pages and cache slots), and ONE
-// tile load brings the keys and the values of a page and KV head: up to 32 positions, 8 KB for a
+// tile load brings the keys and the values of a page and KV head: up to 64 positions, 8 KB for a
 // page of 16 at head size 128.  The TMA unit spends about the same time on a load whatever its
 // size, so few large loads are what lets a warp stream at the memory's speed.  The bytes are
-// counted on an mbarrier per stage of a four-stage ring; the warp spends its instructions on the
-// products and not on addresses.  Head sizes 64 and 128; other sizes use attention_decode.cu.
+// counted on an mbarrier per stage of a ring of two tiles of 64 keys; the warp spends its
+// instructions on the products and not on addresses.  Head sizes 64 and 128; other sizes use attention_decode.cu.
 #include "attention_common.cuh"
 #include "tcgen05.cuh"
 
 namespace {
+constexpr int DECODE_KT = 64, DECODE_STAGES = 2;   // keys of a tile, tiles in flight per warp
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
   uint32_t r;
@@ -429,7 +430,7 @@ int launch(const CUtensorMap& map, const bf16* q, bf16* out, float* part_o, floa
            int table_stride, const int* items, const int* row_slot, const int* row_pos, int n_items, int Hq,
            int Hkv, int page_size, int n_slots, int slot, float scale, int window, int splits, int* status,
            const Fused& fu, cudaStream_t s) {
-  constexpr int KT = 32, STAGES = 4;
+  constexpr int KT = DECODE_KT, STAGES = DECODE_STAGES;
   auto kernel = flash_decode_tma_kernel<HD, KT, STAGES, FUSED>;
   constexpr int smem = 2 * STAGES * KT * HD * 2 + STAGES * 8 + 1024;
   static bool configured = false;
@@ -449,13 +450,13 @@ int check_and_map(const void* storage, long long n_pages, int n_slots, int slot,
   if (Hkv <= 0 || Hq % Hkv || splits < 1) return LLM_ERR_ARGUMENT;
   if (splits > 1 && (!part_o || !part_ml)) return LLM_ERR_ARGUMENT;
   if (hd != 64 && hd != 128) return LLM_ERR_UNSUPPORTED;
-  if (!(32 % page_size == 0 || page_size % 32 == 0)) return LLM_ERR_UNSUPPORTED;
+  if (!(DECODE_KT % page_size == 0 || page_size % DECODE_KT == 0)) return LLM_ERR_UNSUPPORTED;
   if (page_size & (page_size - 1)) return LLM_ERR_UNSUPPORTED;
   const long long planes = n_pages * n_slots * 2;
   if (planes >= (1LL << 31) || slot < 0 || slot >= n_slots) return LLM_ERR_UNSUPPORTED;
   // innermost first: 64 columns, the halves of a row, the positions of a page, the KV heads, the
   // K and V planes of every (page, cache slot)
-  const int R = page_size < 32 ? page_size : 32;
+  const int R = page_size < DECODE_KT ? page_size : DECODE_KT;
   const long long dims[5] = {64, hd / 64, page_size, Hkv, planes};
   const long long strides[4] = {128, (long long)hd * 2, (long long)page_size * hd * 2,
                                 (long long)Hkv * page_size * hd * 2};
@@ -465,7 +466,7 @@ int check_and_map(const void* storage, long long n_pages, int n_slots, int slot,
 }  // namespace
 
 // storage: the group's whole cache [n_pages][n_slots][2][Hkv][page_size][hd] bfloat16, contiguous;
-// slot: the cache slot of this layer call.  page_size must divide 32 or be a multiple of it.
+// slot: the cache slot of this layer call.  page_size: a power of two.
 // Other arguments as llm_attention_decode.
 LLM_EXPORT int llm_attention_decode_tma(const void* q, void* out, float* part_o, float* part_ml,
                                         const void* storage, long long n_pages, int n_slots, int slot,

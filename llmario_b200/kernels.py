@@ -581,7 +581,8 @@ def decode_fusion_ok(ctx, view, num_heads: int, num_kv_heads: int, head_dim: int
         return ok
     reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
     resident = 3 * sm_count()
-    return ctx.rows * num_kv_heads * decode_splits(ctx.rows, num_kv_heads, reach, resident) <= 2 * resident
+    return (ctx.rows * num_kv_heads * decode_splits(ctx.rows, num_kv_heads, reach, resident,
+                                                   DECODE_TMA_TILE) <= 2 * resident)
 
 
 def attention_decode_fused(ctx, proj: torch.Tensor, out: torch.Tensor, view, writes_cache: bool,
@@ -600,7 +601,7 @@ def attention_decode_fused(ctx, proj: torch.Tensor, out: torch.Tensor, view, wri
     rows = ctx.rows
     reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
     if splits is None:
-        splits = decode_splits(rows, num_kv_heads, reach, 3 * sm_count())
+        splits = decode_splits(rows, num_kv_heads, reach, 3 * sm_count(), DECODE_TMA_TILE)
     part_o = part_ml = None
     if splits > 1:
         part_o = ctx.buffer("attn.part_o", (rows * num_heads * splits * head_dim,), torch.float32)
@@ -619,21 +620,26 @@ def attention_decode_fused(ctx, proj: torch.Tensor, out: torch.Tensor, view, wri
                         clear=proj if clear else None)
 
 
-def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int = 444) -> int:
+def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int = 444,
+                  tile: int = 32) -> int:
     """Parts into which the keys of a one-token item are cut.  ``resident``: how many CTAs of
-    the kernel the GPU holds at once.  The cost of a choice is modelled as waves of CTAs times
-    the length of one CTA's walk (its tiles of 32 keys plus a fixed start-up of about three
-    tiles), plus the merge, which grows with the number of parts; measured step times at batch
-    1, 8 and 64 and contexts of 1024 and 4096 keys rank the choices the same way."""
+    the kernel the GPU holds at once; ``tile``: keys of the kernel's tiles (parts are whole
+    tiles).  The cost of a choice is modelled as waves of CTAs times the length of one CTA's
+    walk (its keys, in units of 32, plus a fixed start-up worth about 96 keys), plus the merge,
+    which grows with the number of parts; measured step times at batch 1, 8 and 64 and contexts
+    of 1024 and 4096 keys rank the choices the same way."""
     ctas = max(1, n_items * num_kv_heads)
-    tiles = max(1, -(-max_len // 32))
+    tiles = max(1, -(-max_len // tile))
     best, best_cost = 1, None
     for s in range(1, min(32, max(1, max_len // 64)) + 1):
         waves = -(-ctas * s // resident)
-        cost = waves * (-(-tiles // s) + 3) + 0.1 * s
+        cost = waves * (-(-tiles // s) * (tile // 32) + 3) + 0.1 * s
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
+
+
+DECODE_TMA_TILE = 64      # keys of a tile of attention_decode_tma.cu
 
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
@@ -659,8 +665,8 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
     if plan.n_small:
         reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
         tma = group <= 8 and decode_tma_ok(view, head_dim)
-        splits = decode_splits(plan.n_small, num_kv_heads, reach,
-                               (3 if tma else 6) * sm_count()) if plan.small_single else 1
+        splits = decode_splits(plan.n_small, num_kv_heads, reach, (3 if tma else 6) * sm_count(),
+                               DECODE_TMA_TILE if tma else 32) if plan.small_single else 1
         part_o = part_ml = None
         if splits > 1:
             part_o = ctx.buffer("attn.part_o", (ctx.rows * num_heads * splits * head_dim,),
