@@ -142,7 +142,8 @@ def cmd_prefill_attention(a) -> None:
         fn = lambda: kernels.attention_tcgen05(q, out, storage[0, 0, 0], storage[0, 0, 1],
                                                storage.stride(0), table, items, n, Hq, Hkv, hd,
                                                page, hd ** -0.5, a.window,
-                                               0 if a.cp_async else storage.shape[0])
+                                               0 if a.cp_async else storage.shape[0],
+                                               persistent=not a.one_cta_per_item)
     ms = timed(fn, a.reps, None, a.chain)
     kernels.check_tc_status(DEV)
     flops = 2.0 * T * T * Hq * hd          # causal: half of QK^T and PV
@@ -218,6 +219,8 @@ def main(argv=None) -> int:
                    help="K and V by cp.async copies even where the pages are large enough for TMA")
     p.add_argument("--one-tile", action="store_true",
                    help="one query tile per CTA even where the pages allow two")
+    p.add_argument("--one-cta-per-item", action="store_true",
+                   help="with --one-tile: a CTA per (item, KV head) instead of a persistent CTA per SM")
     p.add_argument("--window", type=int, default=None, help="attend to this many last keys only")
     p.add_argument("--chain", type=int, default=1,
                    help="launches per timed interval (hides the host's launch time)")

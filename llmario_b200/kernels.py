@@ -60,7 +60,7 @@ def _signatures():
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
         "llm_attention_decode_tma": [P, P, P, P, P, L, I, I, P, I, P, P, P, I, I, I, I, I, F, I,
                                      I, P, P],
-        "llm_attention_tcgen05": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, P, P],
+        "llm_attention_tcgen05": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, I, P, P],
         "llm_attention_tcgen05_x2": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
     }
@@ -501,19 +501,20 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       v_cache: torch.Tensor, page_stride: int, block_table: torch.Tensor,
                       items: torch.Tensor, n_items: int, num_heads: int, num_kv_heads: int,
                       head_dim: int, page_size: int, scale: float, window: Optional[int],
-                      n_pages: int = 0) -> None:
+                      n_pages: int = 0, persistent: bool = True) -> None:
     """Attention of prompt portions on tcgen05: items of at most 128 / (heads per KV head)
     tokens; scores and output accumulate in tensor memory.  ``n_pages``: pages of the cache that
     ``k_cache`` / ``v_cache`` are planes of; given it, pages of 32 positions or more are
-    fetched by TMA."""
+    fetched by TMA, and with ``persistent`` and more (item, KV head) pairs than SMs one CTA per
+    SM walks its share of the pairs."""
     _cuda(q, out, k_cache, v_cache, block_table, items)
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
     assert q.is_contiguous() and out.is_contiguous()
     _check(lib().llm_attention_tcgen05(
         _ptr(q), _ptr(out), q.shape[0], _ptr(k_cache), _ptr(v_cache), page_stride, int(n_pages),
         _ptr(block_table), block_table.stride(0), _ptr(items), n_items, num_heads, num_kv_heads,
-        head_dim, page_size, float(scale), int(window or 0), _ptr(tc_status(q.device)),
-        _stream()), f"attention_tcgen05 (head_dim {head_dim})")
+        head_dim, page_size, float(scale), int(window or 0), int(persistent),
+        _ptr(tc_status(q.device)), _stream()), f"attention_tcgen05 (head_dim {head_dim})")
 
 
 def attention_tcgen05_x2(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
@@ -640,6 +641,7 @@ def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int =
 
 
 DECODE_TMA_TILE = 64      # keys of a tile of attention_decode_tma.cu
+PERSISTENT_ATTENTION_MAX_KEYS = 6144
 
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
@@ -693,9 +695,13 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
                              head_dim, view.page_size, scale, window, view.storage.shape[0])
     elif plan.n_large and tc:
         storage = getattr(view, "storage", None)
+        # one persistent CTA per SM saves about 3 us per (item, KV head) pair; with long items
+        # (positions beyond some 6,000) that is little and the fixed deal of pairs costs more
+        reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
         attention_tcgen05(q, out, *common, plan.large, plan.n_large, num_heads, num_kv_heads,
                           head_dim, view.page_size, scale, window,
-                          storage.shape[0] if storage is not None else 0)
+                          storage.shape[0] if storage is not None else 0,
+                          persistent=reach <= PERSISTENT_ATTENTION_MAX_KEYS)
     elif plan.n_large:
         attention_flash(q, out, *common, plan.large, plan.n_large, 64, num_heads, num_kv_heads,
                         head_dim, view.page_size, scale, window)

@@ -1,6 +1,7 @@
 """Each kernel alone against a plain float32/float64 torch statement of the same operation, at
 sizes other than the engine's tiny configurations."""
 import math
+import random
 
 import numpy as np
 import pytest
@@ -684,3 +685,48 @@ def test_attention_tcgen05(Hq, Hkv, hd, page, window):
             got = out[i].reshape(Hq, hd).double().cpu()
             assert torch.isfinite(got).all(), (i, r, p)
             assert (got - ref).abs().max() <= 2e-2, (i, r, p, (got - ref).abs().max())
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(32, 4, 128, 64, None), (32, 8, 64, 32, 200),
+                                                   (16, 8, 128, 128, 150)])
+def test_attention_tcgen05_persistent(Hq, Hkv, hd, page, window):
+    """More (item, KV head) pairs than the GPU has SMs: the kernel then runs as one persistent
+    CTA per SM that walks several pairs, its rings of tiles running on from one to the next.
+    Whole prompts from their first position; against the plain formula on a sample of rows and,
+    bit for bit, against the same kernel with one CTA per pair."""
+    from llmario_b200 import kernels
+    dtype = torch.bfloat16
+    G = Hq // Hkv
+    cap = 128 // G
+    lengths = [900, 333, 64]
+    storage, table, ks, vs = paged_setup(lengths, page, Hkv, hd, dtype)
+    scale = 1 / math.sqrt(hd)
+    g = torch.Generator().manual_seed(17)
+    rows, items = [], []
+    for r, n in enumerate(lengths):
+        for at in range(0, n, cap):
+            m = min(cap, n - at)
+            items.append((len(rows), m, r, at))
+            rows += [(r, p) for p in range(at, at + m)]
+    assert len(items) * Hkv > kernels.sm_count()
+    q = torch.randn(len(rows), Hq, hd, generator=g).to(dtype)
+    qd = q.reshape(len(rows), -1).to(DEV).contiguous()
+    dev_items = torch.tensor(items, dtype=torch.int32, device=DEV).reshape(-1)
+    outs = []
+    for persistent in (True, False):
+        out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
+        kernels.attention_tcgen05(qd, out, storage[0, 1, 0], storage[0, 1, 1], storage.stride(0),
+                                  table, dev_items, len(items), Hq, Hkv, hd, page, scale, window,
+                                  storage.shape[0], persistent=persistent)
+        kernels.check_tc_status(DEV)
+        outs.append(out)
+    assert torch.isfinite(outs[0].float()).all()
+    assert torch.equal(outs[0], outs[1])
+    rng = random.Random(3)
+    sample = sorted(set([0, 1, cap - 1, cap, len(rows) - 1, 899, 900, 901] +
+                        [rng.randrange(len(rows)) for _ in range(40)]))
+    for i in sample:
+        r, p = rows[i]
+        ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
+        got = outs[0][i].reshape(Hq, hd).double().cpu()
+        assert (got - ref).abs().max() <= 2e-2, (i, r, p, (got - ref).abs().max())
