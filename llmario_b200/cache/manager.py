@@ -223,8 +223,9 @@ class CacheManager:
                                           int(bool(self._state_need)))
         if not self._c:
             raise CacheError("the cache core refused these sizes")
-        self._keys: Dict[Any, int] = {}            # request id -> the core's 64-bit key
+        self._keys: Dict[Any, int] = {}            # open requests: id -> the core's 64-bit key
         self._ids: Dict[int, Any] = {}
+        self._names: Dict[Any, int] = {}           # keys promised before a request is opened
         self._next_key = itertools.count(1)
         self._info = (ctypes.c_int * 4)()
         self._per_group = (ctypes.c_int * max(G, 1))()
@@ -285,10 +286,39 @@ class CacheManager:
         except KeyError:
             raise CacheError(f"unknown request {request_id!r}") from None
 
+    def name(self, request_id: Any) -> int:
+        """The 64-bit key under which the core will know this request whenever it is open, now
+        or later (a request that loses its pages and is opened again keeps it), until
+        :meth:`unname`.  The native scheduler asks the core about requests by these keys."""
+        key = self._names.get(request_id)
+        if key is None:
+            key = self._keys.get(request_id)
+            if key is None:
+                key = next(self._next_key)
+            self._names[request_id] = key
+        return key
+
+    def unname(self, request_id: Any) -> None:
+        self._names.pop(request_id, None)
+
+    @property
+    def core(self):
+        """The native core's handle (for the native scheduler, which lives in the same library)."""
+        return self._c
+
+    def closed_in_core(self, request_id: Any) -> None:
+        """The native scheduler has closed this request in the core (preempted, failed or
+        finished it): forget it here as well."""
+        key = self._keys.pop(request_id, None)
+        if key is not None:
+            self._ids.pop(key, None)
+
     def open(self, request_id: Any) -> int:
         if request_id in self._keys:
             raise CacheError(f"request {request_id!r} is already open")
-        key = next(self._next_key)
+        key = self._names.get(request_id)
+        if key is None:
+            key = next(self._next_key)
         slot = self._lib.llm_cache_open(self._c, key)
         if slot == _E_NO_SLOT:
             raise CacheError("no free request slot")

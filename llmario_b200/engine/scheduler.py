@@ -1,5 +1,8 @@
 """The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
-finishes and frees.  Host-side only; it asks the cache manager how many pages a plan needs.
+finishes and frees.  The decisions are made in native code
+(``llmario_b200/csrc/host/sched_core.cpp``, in the same library as the cache bookkeeping, which
+it asks directly); this module holds what the native side has no use for, the requests' token
+ids and sampling parameters, and mirrors its queues as Python objects.
 
 Rules, after the reference's step loop (crates/engine/server/src/engine.rs:621-710, 780-994):
 
@@ -20,15 +23,21 @@ even alone is failed with "KV cache full".
 """
 from __future__ import annotations
 
+import ctypes
 import itertools
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Any, Deque, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Deque, Dict, List, Optional, Sequence
 
 from ..cache import CacheManager
+from ..csrc.build import load_host_library
 from ..sampling import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+_REASONS = {1: "stop", 2: "length", 3: "error", 4: "aborted"}
+_COUNTERS = ("admitted", "finished", "preemptions", "failed", "steps_planned", "prompt_tokens",
+             "decode_tokens", "steps_planned_ahead")
+_TOO_LARGE = "KV cache full: the request does not fit the cache even alone"
 
 
 @dataclass
@@ -81,6 +90,37 @@ class StepPlan:
         return sum(e.count for e in self.entries)
 
 
+_declared = False
+
+
+def _native():
+    """The host library with the scheduler's functions declared."""
+    global _declared
+    lib = load_host_library()
+    if not _declared:
+        P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+        sigs = {
+            "llm_sched_new": ([P, I, I, I, I], P),
+            "llm_sched_delete": ([P], None),
+            "llm_sched_set_eos": ([P, I, P], None),
+            "llm_sched_add": ([P, L, I, I, I, I], I),
+            "llm_sched_forget": ([P, L], I),
+            "llm_sched_has_work": ([P], I),
+            "llm_sched_request": ([P, L, P], I),
+            "llm_sched_plan": ([P, I, P, P, P, P], I),
+            "llm_sched_plan_ahead": ([P, I, P, P, I, P, P], I),
+            "llm_sched_complete": ([P, I, P, P, P, P, P], I),
+            "llm_sched_abort": ([P, L], I),
+            "llm_sched_queues": ([P, I, P, P, P], I),
+            "llm_sched_counters": ([P, P], None),
+        }
+        for name, (args, res) in sigs.items():
+            fn = getattr(lib, name)
+            fn.argtypes, fn.restype = args, res
+        _declared = True
+    return lib
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, token_budget: int = 512, max_context: Optional[int]
                  = None, eos_token_ids: Sequence[int] = ()):
@@ -89,12 +129,55 @@ class Scheduler:
         self.cache = cache
         self.token_budget = int(token_budget)
         self.max_context = int(max_context or cache.max_context)
-        self.eos = frozenset(int(e) for e in eos_token_ids)
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []      # in order of admission
         self._arrivals = itertools.count()
-        self.counters = {"admitted": 0, "finished": 0, "preemptions": 0, "failed": 0,
-                         "steps_planned": 0, "prompt_tokens": 0, "decode_tokens": 0}
+        self._lib = _native()
+        self._s = self._lib.llm_sched_new(cache.core, len(cache.groups), cache.page_size,
+                                          self.token_budget, self.max_context)
+        if not self._s:
+            raise ValueError("the native scheduler refused these sizes")
+        self.eos = eos_token_ids
+        self._by_key: Dict[int, Request] = {}
+        self._cap = 0
+        self._room(64)
+
+    def __del__(self):
+        if getattr(self, "_s", None) and getattr(self, "_lib", None) is not None:
+            self._lib.llm_sched_delete(self._s)
+            self._s = None
+
+    def _room(self, n: int) -> None:
+        """Arrays for plans and events of up to ``n`` requests."""
+        if n <= self._cap:
+            return
+        cap = max(64, 2 * n)
+        self._keys = (ctypes.c_int64 * cap)()
+        self._triples = (ctypes.c_int * (3 * cap))()
+        self._events = (ctypes.c_int64 * cap)()
+        self._in_keys = (ctypes.c_int64 * cap)()
+        self._in_triples = (ctypes.c_int * (3 * cap))()
+        self._tokens = (ctypes.c_int * cap)()
+        self._reasons = (ctypes.c_int * cap)()
+        self._n_events = (ctypes.c_int * 3)()
+        self._cap = cap
+
+    @property
+    def eos(self) -> frozenset:
+        """The token ids that end a request (unless it asks to ignore them)."""
+        return self._eos
+
+    @eos.setter
+    def eos(self, token_ids) -> None:
+        self._eos = frozenset(int(e) for e in token_ids)
+        arr = (ctypes.c_int * max(1, len(self._eos)))(*sorted(self._eos))
+        self._lib.llm_sched_set_eos(self._s, len(self._eos), arr)
+
+    @property
+    def counters(self) -> Dict[str, int]:
+        out = (ctypes.c_longlong * len(_COUNTERS))()
+        self._lib.llm_sched_counters(self._s, out)
+        return dict(zip(_COUNTERS, out))
 
     # ------------------------------------------------------------------ queue
     def add(self, request: Request) -> None:
@@ -105,110 +188,71 @@ class Scheduler:
         if len(request.prompt) >= self.max_context:
             raise ValueError(f"prompt of {len(request.prompt)} tokens does not fit the context "
                              f"of {self.max_context}")
+        key = self.cache.name(request.id)
+        p = request.params
+        rc = self._lib.llm_sched_add(self._s, key, len(request.prompt), int(p.max_tokens),
+                                     int(bool(p.ignore_eos)), int(bool(p.penalties_active)))
+        if rc != 0:
+            raise ValueError(f"request {request.id!r}: the native scheduler answered {rc}")
         request.arrival = next(self._arrivals)
         request.state = WAITING
+        self._by_key[key] = request
         self.waiting.append(request)
+        self._room(len(self._by_key))
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.llm_sched_has_work(self._s))
+
+    def _mirror_queues(self) -> None:
+        nw, nr = ctypes.c_int(), ctypes.c_int()
+        n = self._lib.llm_sched_queues(self._s, self._cap, self._keys, ctypes.byref(nw),
+                                       ctypes.byref(nr))
+        if n < 0:
+            raise RuntimeError("the scheduler's arrays are too small for its queues")
+        self.waiting = deque(self._by_key[self._keys[i]] for i in range(nw.value))
+        self.running = [self._by_key[self._keys[i]] for i in range(nw.value, n)]
+
+    def _gone(self, r: Request, reason: str, error: Optional[str] = None) -> None:
+        """The native side has ended this request and closed it in the cache core."""
+        r.state = FINISHED
+        r.finish_reason = reason
+        r.error = error
+        key = self.cache.name(r.id)
+        self.cache.closed_in_core(r.id)
+        self.cache.unname(r.id)
+        self._by_key.pop(key, None)
+        self._lib.llm_sched_forget(self._s, key)
 
     # ------------------------------------------------------------------ planning
-    def _pages_for(self, req: Request, count: int, opened: bool) -> List[int]:
-        if opened and self.cache.has(req.id):
-            return self.cache.pages_needed(req.id, count)
-        ps = self.cache.page_size
-        return [-(-count // ps)] * len(self.cache.groups)
-
     def plan(self) -> StepPlan:
         """Decide the next step.  Changes the queues (admission, preemption, failure) but feeds
         nothing: the caller runs the step and reports back with :meth:`complete`."""
+        n = self._lib.llm_sched_plan(self._s, self._cap, self._keys, self._triples, self._events,
+                                     self._n_events)
+        if n < 0:
+            raise RuntimeError(f"the native scheduler answered {n}")
         plan = StepPlan()
-        cache = self.cache
-        while True:
-            free = list(cache.free_pages())
-            used = 0
-            entries: List[PlanEntry] = []
-            ok = True
-            # 1. decoding requests, one token each
-            for r in self.running:
-                if r.computed == r.sequence_len - 1 and r.output:
-                    need = self._pages_for(r, 1, True)
-                    if used >= self.token_budget:
-                        break
-                    if any(n > f for n, f in zip(need, free)):
-                        ok = False
-                        break
-                    free = [f - n for f, n in zip(free, need)]
-                    entries.append(PlanEntry(r, r.computed, 1, True))
-                    used += 1
-            if not ok:
-                victim = self.running[-1]
-                if len(self.running) == 1:
-                    self._fail(victim, "KV cache full: the request does not fit the cache "
-                                       "even alone")
-                    plan.failed.append(victim)
-                else:
-                    self._preempt(victim)
-                    plan.preempted.append(victim)
-                continue
-            # 2. prompt portions of running requests, oldest first
-            for r in self.running:
-                if used >= self.token_budget:
-                    break
-                if r.output and r.computed == r.sequence_len - 1:
-                    continue
-                left = r.sequence_len - r.computed
-                n = min(left, self.token_budget - used)
-                n = self._fit(r, n, free, True)
-                if n <= 0:
-                    continue
-                need = self._pages_for(r, n, True)
-                free = [f - k for f, k in zip(free, need)]
-                entries.append(PlanEntry(r, r.computed, n, r.computed + n == r.sequence_len))
-                used += n
-            # 3. admission
-            while self.waiting and used < self.token_budget and \
-                    cache.free_slots() - self._planned_new(entries) > 0:
-                r = self.waiting[0]
-                left = r.sequence_len - r.computed
-                if r.preemptions:
-                    # a request that lost its pages comes back only when all of it fits:
-                    # otherwise it would take the pages the older requests are about to need
-                    # and be preempted again
-                    if plan.preempted or any(
-                            k > f for k, f in zip(self._pages_for(r, left + 1, False), free)):
-                        break
-                n = self._fit(r, min(left, self.token_budget - used), free, False)
-                if n <= 0:
-                    break
-                self.waiting.popleft()
-                r.state = RUNNING
-                self.running.append(r)
-                self.counters["admitted"] += 1
-                need = self._pages_for(r, n, False)
-                free = [f - k for f, k in zip(free, need)]
-                entries.append(PlanEntry(r, r.computed, n, r.computed + n == r.sequence_len))
-                used += n
-            if not entries and self.running:
-                # nothing fits although requests are running: a prompt portion is stuck for
-                # want of pages.  Make room by preempting the newest, or fail a lone request.
-                victim = self.running[-1]
-                if len(self.running) == 1:
-                    self._fail(victim, "KV cache full: the request does not fit the cache "
-                                       "even alone")
-                    plan.failed.append(victim)
-                else:
-                    self._preempt(victim)
-                    plan.preempted.append(victim)
-                continue
-            if not entries and self.waiting and not self.running:
-                r = self.waiting.popleft()
-                self._fail(r, "KV cache full: the request does not fit the cache even alone")
-                plan.failed.append(r)
-                continue
-            plan.entries = entries
-            break
-        self.counters["steps_planned"] += 1
+        n_pre, n_fail, n_adm = self._n_events
+        at = 0
+        for _ in range(n_pre):
+            r = self._by_key[self._events[at]]
+            at += 1
+            r.computed = 0
+            r.state = WAITING
+            r.preemptions += 1
+            self.cache.closed_in_core(r.id)
+            plan.preempted.append(r)
+        failed = [self._by_key[self._events[at + i]] for i in range(n_fail)]
+        at += n_fail
+        for i in range(n_adm):
+            self._by_key[self._events[at + i]].state = RUNNING
+        t = self._triples
+        plan.entries = [PlanEntry(self._by_key[self._keys[i]], t[3 * i], t[3 * i + 1],
+                                  bool(t[3 * i + 2])) for i in range(n)]
+        for r in failed:
+            self._gone(r, "error", _TOO_LARGE)
+            plan.failed.append(r)
+        self._mirror_queues()
         return plan
 
     def plan_ahead(self, flying: StepPlan) -> Optional[StepPlan]:
@@ -219,110 +263,59 @@ class Scheduler:
         context reached) decodes one more token.  A request that ends on an end-of-sequence
         token drawn by ``flying`` has a row too many in the step ahead; :meth:`complete`
         passes over it.  Changes nothing; the cache lengths already count ``flying``."""
-        if self.waiting or flying.preempted or flying.failed or not flying.entries:
+        n = len(flying.entries)
+        if n == 0 or n > self._cap:
             return None
-        if len(flying.entries) != len(self.running) or not all(e.samples for e in flying.entries):
+        for i, e in enumerate(flying.entries):
+            self._in_keys[i] = self.cache.name(e.request.id) if e.request.state != FINISHED else 0
+            self._in_triples[3 * i] = e.start
+            self._in_triples[3 * i + 1] = e.count
+            self._in_triples[3 * i + 2] = int(e.samples)
+        m = self._lib.llm_sched_plan_ahead(self._s, n, self._in_keys, self._in_triples,
+                                           len(flying.preempted) + len(flying.failed), self._keys,
+                                           self._triples)
+        if m < 0:
             return None
-        free = list(self.cache.free_pages())
-        entries: List[PlanEntry] = []
-        for e in flying.entries:
-            r = e.request
-            if r.state != RUNNING or r.params.penalties_active:
-                return None
-            if len(r.output) + 1 >= r.params.max_tokens or \
-                    r.sequence_len + 1 >= self.max_context:
-                continue                      # its last token is the one in flight
-            need = self._pages_for(r, 1, True)
-            if any(n > f for n, f in zip(need, free)):
-                return None                   # someone has to go: decided with all facts known
-            free = [f - n for f, n in zip(free, need)]
-            entries.append(PlanEntry(r, e.start + e.count, 1, True))
-        if not entries or len(entries) > self.token_budget:
-            return None
-        self.counters["steps_planned"] += 1
-        self.counters["steps_planned_ahead"] = self.counters.get("steps_planned_ahead", 0) + 1
-        return StepPlan(entries=entries)
-
-    def _planned_new(self, entries: List[PlanEntry]) -> int:
-        return sum(1 for e in entries if not self.cache.has(e.request.id))
-
-    def _fit(self, r: Request, n: int, free: List[int], opened: bool) -> int:
-        """Largest count <= n whose pages fit in ``free``."""
-        if n <= 0:
-            return 0
-        opened = opened and self.cache.has(r.id)
-        need = self._pages_for(r, n, opened)
-        if all(k <= f for k, f in zip(need, free)):
-            return n
-        ps = self.cache.page_size
-        have = self.cache.length(r.id) if opened else 0
-        held = len(self.cache.pages_of(r.id, 0)) if opened and self.cache.groups else 0
-        room = (held + min(free)) * ps - have if self.cache.groups else n
-        return max(0, min(n, room))
-
-    def _preempt(self, r: Request) -> None:
-        self.running.remove(r)
-        if self.cache.has(r.id):
-            self.cache.close(r.id)
-        r.computed = 0
-        r.state = WAITING
-        r.preemptions += 1
-        self.counters["preemptions"] += 1
-        self.waiting.appendleft(r)
-
-    def _fail(self, r: Request, why: str) -> None:
-        if r in self.running:
-            self.running.remove(r)
-        if self.cache.has(r.id):
-            self.cache.close(r.id)
-        r.state = FINISHED
-        r.finish_reason = "error"
-        r.error = why
-        self.counters["failed"] += 1
+        t = self._triples
+        return StepPlan(entries=[PlanEntry(self._by_key[self._keys[i]], t[3 * i], 1, True)
+                                 for i in range(m)])
 
     # ------------------------------------------------------------------ after the step
     def complete(self, plan: StepPlan, sampled: Dict[Any, int]) -> List[Request]:
         """The step ran.  ``sampled`` maps a request id to the token drawn for it (for the
         entries that sample).  Returns the requests that finished; their pages are free."""
-        done: List[Request] = []
-        for e in plan.entries:
+        entries = [e for e in plan.entries if e.request.state == RUNNING]
+        # (a request that is no longer running ended while this step, planned ahead, was
+        # already running: it is passed over)
+        n = len(entries)
+        self._room(n)
+        for i, e in enumerate(entries):
             r = e.request
-            if r.state != RUNNING:
-                continue        # it ended while this step, planned ahead, was already running
+            self._in_keys[i] = self.cache.name(r.id)
+            self._in_triples[3 * i] = e.start
+            self._in_triples[3 * i + 1] = e.count
+            self._in_triples[3 * i + 2] = int(e.samples)
+            self._tokens[i] = int(sampled[r.id]) if e.samples else -1
+        k = self._lib.llm_sched_complete(self._s, n, self._in_keys, self._in_triples, self._tokens,
+                                         self._keys, self._reasons)
+        for i, e in enumerate(entries):
+            r = e.request
             r.computed += e.count
-            if r.output and e.count == 1 and e.samples:
-                self.counters["decode_tokens"] += 1
-            else:
-                self.counters["prompt_tokens"] += e.count
-            if not e.samples:
-                continue
-            tok = int(sampled[r.id])
-            r.output.append(tok)
-            if tok in self.eos and not r.params.ignore_eos:
-                self._finish(r, "stop")            # engine.rs:1185-1188
-            elif len(r.output) >= r.params.max_tokens:
-                self._finish(r, "length")          # engine.rs:1211-1213
-            elif r.sequence_len >= self.max_context:
-                self._finish(r, "length")          # engine.rs:1214-1216
-            if r.state == FINISHED:
-                done.append(r)
+            if e.samples:
+                r.output.append(self._tokens[i])
+        done = []
+        for i in range(k):
+            r = self._by_key[self._keys[i]]
+            self._gone(r, _REASONS[self._reasons[i]])
+            done.append(r)
+        if k:
+            self._mirror_queues()
         return done
-
-    def _finish(self, r: Request, reason: str) -> None:
-        self.running.remove(r)
-        if self.cache.has(r.id):
-            self.cache.close(r.id)
-        r.state = FINISHED
-        r.finish_reason = reason
-        self.counters["finished"] += 1
 
     def abort(self, r: Request) -> None:
         """Drop a request wherever it is (a client that went away, engine.rs:695-703)."""
-        if r in self.waiting:
-            self.waiting.remove(r)
-        if r in self.running:
-            self.running.remove(r)
-        if self.cache.has(r.id):
-            self.cache.close(r.id)
-        r.state = FINISHED
-        r.finish_reason = "aborted"
+        if r.state == FINISHED:
+            return
+        self._lib.llm_sched_abort(self._s, self.cache.name(r.id))
+        self._gone(r, "aborted")
+        self._mirror_queues()

@@ -488,3 +488,83 @@ def test_native_bookkeeping_agrees_with_the_plain_model(seed):
     for r in live:
         native.close(r), plain.close(r)
     assert native.free_pages() == [n_pages] * len(windows)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_native_scheduler_agrees_with_the_plain_model(seed):
+    """The scheduler decides in native code; a plain Python model of the same rules lives under
+    tests/plain.  Both get the same random load (arrivals, lengths, limits, end-of-sequence
+    tokens, aborts, steps planned ahead, so few pages that requests are preempted and one is
+    too large for the cache) and must make the same plans, step by step."""
+    from plain.scheduler_plain import PlainScheduler, Request as PlainRequest
+
+    rng = random.Random(100 + seed)
+    window = rng.choice([None, 9])
+    budget = rng.choice([5, 16, 64])
+    pages = rng.choice([8, 12, 40])
+
+    def make():
+        return manager(n_pages=pages, page=4, ctx=48, max_requests=3, window=window, layers=1)
+
+    native = Scheduler(make(), token_budget=budget, eos_token_ids=[3])
+    plain = PlainScheduler(make(), token_budget=budget, eos_token_ids=[3])
+    specs = [(i, rng.randint(1, 40), rng.randint(1, 12), rng.random() < 0.3) for i in range(14)]
+    pending = list(specs)
+    both = {}
+
+    def same_plan(a, b):
+        assert [(e.request.id, e.start, e.count, e.samples) for e in a.entries] == \
+               [(e.request.id, e.start, e.count, e.samples) for e in b.entries]
+        assert [r.id for r in a.preempted] == [r.id for r in b.preempted]
+        assert [r.id for r in a.failed] == [r.id for r in b.failed]
+
+    def same_state():
+        assert [r.id for r in native.waiting] == [r.id for r in plain.waiting]
+        assert [r.id for r in native.running] == [r.id for r in plain.running]
+        for rid, (a, b) in both.items():
+            assert (a.state, a.computed, a.output, a.finish_reason, a.preemptions) == \
+                   (b.state, b.computed, b.output, b.finish_reason, b.preemptions), rid
+        assert native.cache.free_pages() == plain.cache.free_pages()
+        na, pl = native.counters, plain.counters
+        assert all(na[k] == pl.get(k, 0) for k in na), (na, pl)
+
+    steps = 0
+    while pending or native.has_work():
+        assert native.has_work() == plain.has_work()
+        if pending and rng.random() < 0.4:
+            i, n, mt, ig = pending.pop(0)
+            params = SamplingParams(temperature=0, max_tokens=mt, ignore_eos=ig)
+            a = Request(i, list(range(1, n + 1)), params)
+            b = PlainRequest(i, list(range(1, n + 1)), params)
+            both[i] = (a, b)
+            native.add(a), plain.add(b)
+        if native.running and rng.random() < 0.05:
+            victim = rng.choice(native.running).id
+            native.abort(both[victim][0]), plain.abort(both[victim][1])
+            same_state()
+        if native.has_work():
+            pa, pb = native.plan(), plain.plan()
+            same_plan(pa, pb)
+            launch(native, pa), launch(plain, pb)
+            tokens = {e.request.id: rng.randint(0, 5) for e in pa.entries if e.samples}
+            # the step after, decided before this one's tokens are known
+            aa, ab = native.plan_ahead(pa), plain.plan_ahead(pb)
+            assert (aa is None) == (ab is None)
+            native.complete(pa, tokens), plain.complete(pb, tokens)
+            same_state()
+            if aa is not None:
+                same_plan(aa, ab)
+                live_a = [e for e in aa.entries if e.request.state == RUNNING]
+                live_b = [e for e in ab.entries if e.request.state == RUNNING]
+                for s, live in ((native, live_a), (plain, live_b)):
+                    s.cache.reserve([(e.request.id, e.count) for e in live])
+                    for e in live:
+                        s.cache.advance(e.request.id, e.count)
+                tokens = {e.request.id: rng.randint(0, 5) for e in aa.entries}
+                native.complete(aa, tokens), plain.complete(ab, tokens)
+                same_state()
+            native.cache.check_invariants()
+        steps += 1
+        assert steps < 5000
+    assert all(a.state == FINISHED for a, _ in both.values())
+    assert native.cache.free_pages() == [pages] * len(native.cache.groups)
