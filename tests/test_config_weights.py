@@ -270,3 +270,22 @@ def test_python_bindings_match_the_c_declarations():
         bound = "".join(kinds[t] for t in sigs[name])
         assert declared == bound, f"{name}: C has {declared}, the binding {bound}"
     assert seen == set(sigs), sorted(set(sigs) - seen)
+
+
+def test_decode_split_model_choices():
+    """The number of key parts of decode attention: never more CTAs than two waves when one part
+    already fills the GPU, more parts for few requests, whole tiles per part, and the same answer
+    for the same arguments (recorded CUDA graphs are keyed by it)."""
+    from llmario_b200.kernels import decode_splits
+
+    for tile in (32, 64):
+        assert decode_splits(1, 8, 64, 444, tile) == 1              # one tile: nothing to cut
+        few = decode_splits(1, 8, 4096, 444, tile)
+        many = decode_splits(64, 8, 4096, 444, tile)
+        assert few > many >= 1
+        assert 8 * few <= 2 * 444                                    # at most two waves of CTAs
+        for n, length in ((1, 1024), (8, 1024), (8, 8192), (64, 1024), (300, 2048)):
+            s = decode_splits(n, 8, length, 444, tile)
+            assert 1 <= s <= max(1, length // 64)
+            assert s == decode_splits(n, 8, length, 444, tile)
+    assert decode_splits(512, 8, 1024, 444, 64) == 1                # more requests than CTAs fit
