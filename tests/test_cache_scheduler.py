@@ -568,3 +568,42 @@ def test_native_scheduler_agrees_with_the_plain_model(seed):
         assert steps < 5000
     assert all(a.state == FINISHED for a, _ in both.values())
     assert native.cache.free_pages() == [pages] * len(native.cache.groups)
+
+
+def test_abort_and_names_used_again():
+    """A waiting request can be dropped before it ever ran; a request id can be used again once
+    its request is over (finished, failed or aborted); the cache manager forgets the key it had
+    promised."""
+    m = manager(n_pages=16, page=4, ctx=32, max_requests=2)
+    s = Scheduler(m, token_budget=8)
+    a, b = req("a", 6, max_tokens=2), req("b", 5, max_tokens=2)
+    s.add(a), s.add(b)
+    s.abort(b)                                   # never admitted
+    assert b.state == FINISHED and b.finish_reason == "aborted" and list(s.waiting) == [a]
+    while s.has_work():
+        run_plan(s, s.plan())
+    assert a.finish_reason == "length" and len(a.output) == 2
+    a2 = req("a", 3, max_tokens=1)               # the same id again
+    s.add(a2)
+    p = s.plan()
+    assert [(e.request is a2, e.start, e.count, e.samples) for e in p.entries] == [(True, 0, 3, True)]
+    s.abort(a2)                                  # while it is running and holds pages
+    assert a2.finish_reason == "aborted" and not s.has_work()
+    assert m.free_pages() == [16] * len(m.groups) and m.free_slots() == 2
+    m.check_invariants()
+    assert not m.live_requests()
+    with pytest.raises(ValueError):
+        s.add(req("c", 0))
+    big = req("big", 31, max_tokens=4)           # fits the context, not the 16 pages of 4
+    m2 = manager(n_pages=4, page=4, ctx=64, max_requests=2)
+    s2 = Scheduler(m2, token_budget=64)
+    s2.add(big)
+    p = s2.plan()
+    if p.entries:                                # the prompt is fed in portions until pages run out
+        while s2.has_work() and not p.failed:
+            run_plan(s2, p)
+            p = s2.plan()
+    assert big in p.failed and big.finish_reason == "error" and "KV cache full" in big.error
+    s2.add(req("big", 3, max_tokens=1))          # its id is free again, and so are its pages
+    run_plan(s2, s2.plan())
+    assert not s2.has_work() and m2.free_pages() == [4] * len(m2.groups)
