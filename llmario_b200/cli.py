@@ -124,8 +124,14 @@ def cmd_run(args) -> int:
 
 
 def cmd_bench(args) -> int:
+    """Prefill and decode rates at each concurrency level, by the reference's definitions
+    (docs/BENCHMARK_PLAN.md:28-42: TTFT; prefill = prompt tokens / TTFT; decode = (completion
+    - 1) / (t_last - t_first); aggregate tokens per second), every run reported, as JSON and as
+    a Markdown table (crates/cli/src/bench.rs:13-60 writes both), with the fraction of the memory
+    roofline that the decode steps reach."""
     import torch
 
+    from .benchmarks.roofline import decode_step_bytes, peaks
     from .sampling import SamplingParams
 
     levels = [int(c) for c in str(args.concurrency).split(",") if c]
@@ -133,6 +139,7 @@ def cmd_bench(args) -> int:
     args.context = args.context or (args.prompt_len + args.decode_len + 1)
     eng = _engine(args, max_requests=max(levels), cache_tokens=need)
     vocab = eng.model.vocab_size
+    pk = peaks()
     rng = random.Random(args.seed or 0)
     results = []
     for level in levels:
@@ -146,34 +153,62 @@ def cmd_bench(args) -> int:
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             t_first = None
+            decode_steps = 0
             while eng.has_work():
                 eng.step()
                 if t_first is None and all(eng.request(i).output for i in ids):
                     torch.cuda.synchronize()
                     t_first = time.perf_counter()
+                elif t_first is not None:
+                    decode_steps += 1
             torch.cuda.synchronize()
             t1 = time.perf_counter()
             gen = sum(len(eng.request(i).output) for i in ids)
             if it >= args.warmup:
-                # the reference's definitions (docs/BENCHMARK_PLAN.md:28-42): prefill =
-                # prompt tokens / time to first token; decode = (completion - 1) / (last - first)
+                decode_s = max(t1 - t_first, 1e-9)
+                step_bytes = decode_step_bytes(eng.model, eng.runner, level,
+                                               args.prompt_len + args.decode_len / 2.0)
+                gbs = step_bytes * max(decode_steps, 1) / decode_s / 1e9
                 runs.append({"ttft_s": t_first - t0,
                              "prefill_tok_s": level * args.prompt_len / (t_first - t0),
-                             "decode_tok_s": (gen - level) / max(t1 - t_first, 1e-9),
-                             "aggregate_tok_s": gen / (t1 - t0)})
+                             "decode_tok_s": (gen - level) / decode_s,
+                             "aggregate_tok_s": gen / (t1 - t0),
+                             "decode_gb_s": gbs, "decode_roofline_frac": gbs / pk["hbm_gbs"]})
         results.append({"concurrency": level, "runs": runs})
         best = max(r["decode_tok_s"] for r in runs)
         print(f"concurrency {level}: decode {best:.1f} tok/s, prefill "
               f"{max(r['prefill_tok_s'] for r in runs):.1f} tok/s", file=sys.stderr)
     report = {"model": args.model, "dtype": args.dtype, "prompt_len": args.prompt_len,
-              "decode_len": args.decode_len, "label": args.label, "results": results}
+              "decode_len": args.decode_len, "page_size": args.page_size, "label": args.label,
+              "peaks": pk, "results": results}
     text = json.dumps(report, indent=1)
     if args.out:
         os.makedirs(args.out, exist_ok=True)
-        with open(os.path.join(args.out, (args.label or "bench") + ".json"), "w") as f:
+        stem = os.path.join(args.out, args.label or "bench")
+        with open(stem + ".json", "w") as f:
             f.write(text)
+        with open(stem + ".md", "w") as f:
+            f.write(bench_markdown(report))
     print(text)
     return 0
+
+
+def bench_markdown(report: dict) -> str:
+    """The report of ``bench`` as a Markdown table, one row per run."""
+    pk = report["peaks"]
+    lines = [f"# bench: {report['model']} ({report['dtype']})", "",
+             f"Prompts of {report['prompt_len']} random token ids, {report['decode_len']} decoded "
+             f"tokens each, pages of {report['page_size']}.  Memory roofline: "
+             f"{pk['hbm_gbs']:.0f} GB/s ({pk['source']}).", "",
+             "| concurrency | run | TTFT ms | prefill tok/s | decode tok/s | aggregate tok/s | "
+             "decode GB/s | of roofline |", "|---|---|---|---|---|---|---|---|"]
+    for level in report["results"]:
+        for i, r in enumerate(level["runs"]):
+            lines.append(f"| {level['concurrency']} | {i} | {r['ttft_s'] * 1e3:.1f} | "
+                         f"{r['prefill_tok_s']:.0f} | {r['decode_tok_s']:.0f} | "
+                         f"{r['aggregate_tok_s']:.0f} | {r['decode_gb_s']:.0f} | "
+                         f"{r['decode_roofline_frac']:.3f} |")
+    return "\n".join(lines) + "\n"
 
 
 def main(argv: Optional[Sequence[str]] = None) -> int:

@@ -317,8 +317,12 @@ LLM_EXPORT int llm_attention_flash(const void* q, void* out, float* part_o, floa
                                    int page_size, float scale, int window, int splits,
                                    cudaStream_t stream) {
   if (n_items <= 0) return 0;
-  if (Hkv <= 0 || Hq % Hkv || splits < 1) return LLM_ERR_ARGUMENT;
+  if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || splits < 1 || splits > 65535 || page_size <= 0 || window < 0)
+    return LLM_ERR_ARGUMENT;
   if (splits > 1 && (!part_o || !part_ml)) return LLM_ERR_ARGUMENT;
+  // a CTA holds rows_per_cta (token, head) pairs and every head of a group belongs to one CTA:
+  // a larger group would leave heads uncomputed
+  if (Hq / Hkv > rows_per_cta) return LLM_ERR_UNSUPPORTED;
 #define GO(HD, W, KT)                                                                                 \
   return launch<HD, W, KT>((const bf16*)q, (bf16*)out, part_o, part_ml, (const bf16*)k_cache,          \
                            (const bf16*)v_cache, page_stride, block_table, table_stride, items, row_slot, \
@@ -378,6 +382,12 @@ LLM_EXPORT int llm_attention_merge(const float* part_o, const float* part_ml, vo
 //   start at zero: every (row, head, part) cell that the merge reads is written by the first
 //   kernel of the same call, parts without keys included.  Two calls that overlap on the GPU
 //   (different streams) race on it: order them.
+// * The remembered address (one per device) is written without a lock.  Two host threads that
+//   make their first call on a device at the same time both look the address up and store the
+//   same value, which is harmless.
+// * Refused before anything is launched: more than 16 query heads per KV head (LLM_ERR_UNSUPPORTED;
+//   one warp holds a group's heads), a head size other than 32, 64 or 128, a page size or
+//   number of parts that is not positive, a negative window, more than 65535 parts.
 // ------------------------------------------------------------------------------------------------
 #include "no_alloc.h"
 
@@ -412,7 +422,12 @@ LLM_EXPORT int llm_attention_decode_no_alloc(const void* q, void* out, const voi
                                              int Hq, int Hkv, int hd, int page_size, float scale,
                                              int window, int splits, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (Hkv <= 0 || Hq % Hkv || splits < 1 || hd <= 0) return LLM_ERR_ARGUMENT;
+  if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || splits < 1 || splits > 65535 || hd <= 0 || page_size <= 0 ||
+      window < 0)
+    return LLM_ERR_ARGUMENT;
+  // one warp per (row, KV head) holds 16 (token, head) pairs: a group of more than 16 query heads
+  // on a KV head would leave heads uncomputed, so it is refused before anything is launched
+  if (Hq / Hkv > 16 || (hd != 128 && hd != 64 && hd != 32)) return LLM_ERR_UNSUPPORTED;
   const long long need = (long long)rows * Hq * splits * (hd + 2);
   if (need > (long long)NO_ALLOC_SCRATCH_FLOATS) return LLM_ERR_TOO_LARGE;
   float* scratch = nullptr;

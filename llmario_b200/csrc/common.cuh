@@ -66,7 +66,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 // Bounded wait for the phase with the given parity.  mbarrier.try_wait parks the thread until the
 // phase completes or a hardware time limit passes, so waking up costs no polling delay; the loop
 // around it gives up after WAIT_CYCLES clock cycles (about two seconds).  Returns false then.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit = WAIT_CYCLES) {
   const uint32_t addr = smem_u32(bar);
   long long start = 0;
   for (uint32_t i = 0;; ++i) {
@@ -80,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     if (done) return true;
     if (i == 0) start = clock64();
-    else if (clock64() - start > WAIT_CYCLES) return false;
+    else if (clock64() - start > limit) return false;
   }
 }
 static inline int launch_status() { return (int)cudaGetLastError(); }

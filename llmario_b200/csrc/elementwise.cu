@@ -222,3 +222,47 @@ int llm_zero_f32(float* p, int rows, int cols, int ld, cudaStream_t stream) {
   const int blocks = (int)((total + 1023) / 1024 < 592 ? (total + 1023) / 1024 : 592);
   return launch_pdl(zero_f32_kernel, blocks, 256, 0, stream, p, rows, cols, ld);
 }
+
+// state[slots[i]][:] = 0 for i < *count (count read on the device, at most max_n): the fixed-size
+// state of request slots that were opened for this step, cleared inside the step so that a
+// recorded step clears whatever slots its replay names.
+__global__ void zero_slots_kernel(unsigned int* __restrict__ state, long long row_words,
+                                  const int* __restrict__ slots, const int* __restrict__ count) {
+  pdl_wait();
+  pdl_trigger();
+  if ((int)blockIdx.x >= *count) return;
+  unsigned int* row = state + (size_t)slots[blockIdx.x] * row_words;
+  for (long long i = (long long)blockIdx.y * blockDim.x + threadIdx.x; i < row_words;
+       i += (long long)gridDim.y * blockDim.x)
+    row[i] = 0u;
+}
+
+LLM_EXPORT int llm_zero_slots(void* state, long long row_bytes, const int* slots, const int* count,
+                              int max_n, cudaStream_t stream) {
+  if (max_n <= 0 || row_bytes <= 0) return 0;
+  if (row_bytes % 4 != 0 || ((uintptr_t)state & 3)) return LLM_ERR_UNSUPPORTED;
+  const long long words = row_bytes / 4;
+  const int chunks = (int)((words + 4095) / 4096 < 64 ? (words + 4095) / 4096 : 64);
+  return launch_pdl(zero_slots_kernel, dim3(max_n, chunks), 256, 0, stream, (unsigned int*)state, words,
+                    slots, count);
+}
+
+// A wait that runs out, on purpose and harmlessly: one thread waits on an mbarrier at which
+// nothing arrives, with a caller-given limit of clock cycles, gives up, records role 99 in the
+// status word and returns.  Every bounded wait of the TMA / tcgen05 kernels ends this way when
+// its limit passes; tests use this kernel to see the host side of that path (the status word
+// reaching the engine, the step's requests failing) without a kernel that misbehaves.
+__global__ void selftest_wait_kernel(int* status, long long limit) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!mbar_wait(&bar, 0, limit)) atomicExch(status, 99);
+  }
+}
+
+LLM_EXPORT int llm_selftest_wait_gives_up(int* status, long long limit_cycles, cudaStream_t stream) {
+  if (status == nullptr || limit_cycles <= 0 || limit_cycles > 2000000) return LLM_ERR_ARGUMENT;
+  selftest_wait_kernel<<<1, 32, 0, stream>>>(status, limit_cycles);
+  return launch_status();
+}

@@ -396,6 +396,16 @@ int llm_sched_abort(Sched* s, int64_t key) {
   return 0;
 }
 
+// End a request as failed wherever it is: the step that held it could not be trusted (the
+// reference turns such a failure into an error event for the job, engine.rs:1140).
+int llm_sched_fail(Sched* s, int64_t key) {
+  const int rc = llm_sched_abort(s, key);
+  if (rc != 0) return rc;
+  s->reqs.find(key)->second.reason = R_ERROR;
+  ++s->counters[C_FAILED];
+  return 0;
+}
+
 // waiting keys then running keys, in their order; returns -1 when cap is too small
 int llm_sched_queues(Sched* s, int cap, int64_t* out, int* n_waiting, int* n_running) {
   *n_waiting = (int)s->waiting.size();

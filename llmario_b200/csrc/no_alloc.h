@@ -21,6 +21,11 @@
 //   * The first call on each device resolves the array's device address; make it before any
 //     stream capture begins.
 //   * Calls share the array: do not let two of them overlap on the GPU.
+//   * At most 16 query heads per KV head; otherwise, or with another head size, the call returns
+//     LLM_ERR_UNSUPPORTED (-1).  A page size or number of parts that is not positive, a negative
+//     window or more than 65535 parts return LLM_ERR_ARGUMENT (-2).  Nothing is launched then.
+//   * The per-device address is cached without a lock; concurrent first calls store the same
+//     value.
 #pragma once
 #include <cuda_runtime.h>
 

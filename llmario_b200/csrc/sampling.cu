@@ -134,9 +134,13 @@ __device__ float block_mass(const float* row, int V, uint64_t low, float M, floa
 __global__ void __launch_bounds__(THREADS) sample_kernel(
     const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
-    const double* __restrict__ uniform, int* __restrict__ out) {
+    const double* __restrict__ uniform, int* __restrict__ out, const int* __restrict__ status,
+    int* __restrict__ status_out) {
   __shared__ Shared s;
   const int r = blockIdx.x;
+  // the library's status words travel to the host with the tokens: whoever reads the tokens
+  // learns in the same copy whether a kernel of the step gave up a wait or met a bad token id
+  if (status != nullptr && r == 0 && threadIdx.x < 4) status_out[threadIdx.x] = status[threadIdx.x];
   const float* row = logits + (size_t)r * ld;
   const uint64_t best = block_best(row, V, s);
   const int best_id = (int)(~(uint32_t)(best & 0xffffffffu));
@@ -202,12 +206,12 @@ __global__ void penalty_kernel(float* __restrict__ logits, long long ld, const i
 
 LLM_EXPORT int llm_sample(const float* logits, long long ld, int rows, int V,
                           const float* temperature, const int* top_k, const float* top_p,
-                          const float* min_p, const double* uniform, int* out,
-                          cudaStream_t stream) {
+                          const float* min_p, const double* uniform, int* out, const int* status,
+                          int* status_out, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0) return LLM_ERR_ARGUMENT;
   sample_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p,
-                                              uniform, out);
+                                              uniform, out, status, status_out);
   return launch_status();
 }
 

@@ -14,6 +14,7 @@ from typing import Any, Dict, Iterable, List, Optional, Sequence, Union
 
 import torch
 
+from .. import kernels
 from ..cache import CacheFull
 from ..sampling import DeviceSampler, RequestSampler, SamplingParams
 from .model import Model, parse_dtype
@@ -64,6 +65,7 @@ class Engine:
         self._ids = itertools.count()
         self._requests: Dict[Any, Request] = {}
         self.timers = {"step_s": 0.0, "sample_s": 0.0}
+        self.counters = {"failed_steps": 0}
         self.lookahead = bool(lookahead)
         self._flying: Optional[_Launched] = None     # a step queued ahead, not yet read
 
@@ -109,6 +111,9 @@ class Engine:
         t0 = time.perf_counter()
         tokens = cur.pending.result() if cur.pending is not None else []
         self.timers["wait_s"] = self.timers.get("wait_s", 0.0) + time.perf_counter() - t0
+        fault = kernels.status_message(cur.pending.status) if cur.pending is not None else None
+        if fault is not None:
+            return finished + self._fail_step(cur, fault)
         sampled = {}
         i = 0
         for e in cur.plan.entries:
@@ -147,6 +152,30 @@ class Engine:
         self.timers["sample_s"] += t2 - t1
         return _Launched(plan, pending)
 
+    def _fail_step(self, cur: "_Launched", fault: str) -> List[Request]:
+        """A kernel of the step reported a failure through the status words (a bounded wait
+        that gave up, a token id outside the table): what the step computed cannot be trusted.
+        Its requests end with ``finish_reason == "error"`` instead of receiving tokens drawn
+        from such logits (the reference's ``Event::Error``, engine.rs:1140); so do the requests
+        of a step already queued behind it, which ran on the same state.  The status words are
+        cleared and recorded steps are dropped, so the engine can take new requests."""
+        failed: List[Request] = []
+        plans = [cur.plan] + ([self._flying.plan] if self._flying is not None else [])
+        if self._flying is not None and self._flying.pending is not None:
+            self._flying.pending.result()          # let the step ahead leave the device
+        self._flying = None
+        torch.cuda.current_stream().synchronize()
+        kernels.clear_status(self.model.device)
+        self.runner.drop_recordings()
+        self.runner.workspace.drop()       # a buffer kept at zero may hold partial sums
+        for plan in plans:
+            for e in plan.entries:
+                if e.request.state != FINISHED:
+                    self.scheduler.fail(e.request, f"step failed on the device: {fault}")
+                    failed.append(e.request)
+        self.counters["failed_steps"] += 1
+        return failed
+
     def abort(self, request_id: Any) -> None:
         """Drop a request wherever it is; a step already queued for it runs to its end and its
         result is ignored."""
@@ -180,7 +209,7 @@ class Engine:
     def stats(self) -> Dict[str, Any]:
         """Counters in the spirit of the reference's ``Stats`` (engine.rs:59-159)."""
         c = self.runner.cache
-        return {**self.runner.counters, **self.scheduler.counters,
+        return {**self.runner.counters, **self.scheduler.counters, **self.counters,
                 "cache": dict(c.counters), "free_pages": c.free_pages(),
                 "pages": [g.n_pages for g in c.groups], "running": len(self.scheduler.running),
                 "waiting": len(self.scheduler.waiting), **self.timers}

@@ -11,7 +11,7 @@ from typing import Any, Dict, List, Optional, Tuple
 import torch
 
 from ..config import ModelSpec, load_spec
-from ..parts import BoundCall, build_part, part_class
+from ..parts import BoundCall, build_part, graph_safe, part_class, streamed_weights_of
 from ..weights import check_tensors, load_weights, random_tensors
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
@@ -45,37 +45,55 @@ class Model:
                        for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, weights, dtype, self.device)
         self.head = build_part("head", spec.head, weights, dtype, self.device)
+        # Cache entries.  Every block says what it keeps between steps as a list of needs; each
+        # need of each run-order entry gets an entry of its own in the cache manager.  A call
+        # that reads another call's cache uses that call's entries, need by need.
         self.calls: List[BoundCall] = []
+        self._needs: List[Any] = []
+        self._reads: List[Optional[int]] = []
         for i, call in enumerate(spec.run_order):
-            owner = call.reads_cache_of if call.reads_cache_of is not None else i
-            self.calls.append(BoundCall(i, call.layer, call.reads_cache_of is None, owner))
+            block = self.blocks[call.layer]
+            mine = list(block.cache_needs()) if hasattr(block, "cache_needs") \
+                else [block.mixer.cache_need()]
+            start = len(self._needs)
+            self._needs += mine
+            if call.reads_cache_of is None:
+                entries = tuple(range(start, start + len(mine)))
+                self._reads += [None] * len(mine)
+            else:
+                entries = self.calls[call.reads_cache_of].cache_entries
+                if len(entries) != len(mine):
+                    raise ValueError(f"run-order entry {i} reads the cache of entry "
+                                     f"{call.reads_cache_of}, whose block keeps {len(entries)} "
+                                     f"things where this one keeps {len(mine)}")
+                self._reads += list(entries)
+            self.calls.append(BoundCall(i, call.layer, call.reads_cache_of is None,
+                                        entries[0] if entries else None, entries))
 
     def cache_needs(self) -> Tuple[List[Any], List[Optional[int]]]:
-        """What every run-order entry keeps between steps, and whose cache it reads."""
-        needs, reads = [], []
-        for call, entry in zip(self.calls, self.spec.run_order):
-            needs.append(self.blocks[call.layer].mixer.cache_need())
-            reads.append(entry.reads_cache_of)
-        return needs, reads
+        """What every cache entry keeps between steps (PagedKV, FixedState or None), and the
+        entry whose cache it reads instead of keeping one (or None)."""
+        return list(self._needs), list(self._reads)
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether steps of single tokens may be recorded and replayed: every part declares
+        that it reads the step from device tensors only."""
+        return all(graph_safe(p) for p in [self.embedding, self.final_norm, self.head]
+                   + self.blocks)
 
     def weight_bytes(self) -> int:
-        """Bytes of the matrices a decode step streams once (every layer call and the head)."""
+        """Bytes of the matrices a decode step streams once, as the parts declare them
+        (``streamed_weights()`` of every block that runs, and of the head); a matrix that
+        several calls share is counted once."""
         seen, total = set(), 0
-
-        def add(t: torch.Tensor):
-            nonlocal total
+        tensors = streamed_weights_of(self.head)
+        for call in self.calls:
+            tensors += streamed_weights_of(self.blocks[call.layer])
+        for t in tensors:
             if t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
-
-        for call in self.calls:
-            b = self.blocks[call.layer]
-            for part in (b.mixer, b.feed_forward):
-                for v in vars(part).values():
-                    if hasattr(v, "weight") and isinstance(v.weight, torch.Tensor) \
-                            and v.weight.dim() == 2:
-                        add(v.weight)
-        add(self.head.proj.weight)
         return total
 
     # ------------------------------------------------------------------------------------

@@ -111,6 +111,7 @@ def _native():
             "llm_sched_plan_ahead": ([P, I, P, P, I, P, P], I),
             "llm_sched_complete": ([P, I, P, P, P, P, P], I),
             "llm_sched_abort": ([P, L], I),
+            "llm_sched_fail": ([P, L], I),
             "llm_sched_queues": ([P, I, P, P, P], I),
             "llm_sched_counters": ([P, P], None),
         }
@@ -318,4 +319,13 @@ class Scheduler:
             return
         self._lib.llm_sched_abort(self._s, self.cache.name(r.id))
         self._gone(r, "aborted")
+        self._mirror_queues()
+
+    def fail(self, r: Request, error: str) -> None:
+        """End a request with ``finish_reason == "error"``: a step it was part of failed on the
+        device (the reference's ``Event::Error``, engine.rs:1140).  Its pages are given back."""
+        if r.state == FINISHED:
+            return
+        self._lib.llm_sched_fail(self._s, self.cache.name(r.id))
+        self._gone(r, "error", error)
         self._mirror_queues()

@@ -84,11 +84,15 @@ class ModelRunner:
         self._meta_event: List[Optional[torch.cuda.Event]] = [None, None]
         self._flip = 0
         self._meta_generation = 0
-        self.use_graphs = bool(use_graphs) and len(self.cache.groups) <= HEADER
+        # (the header of the step's integer array has a word per cache group and one for the
+        # number of fresh request slots)
+        self.use_graphs = bool(use_graphs) and len(self.cache.groups) < HEADER and \
+            model.graph_safe
         self._graphs: Dict[Any, Any] = {}
         self._graph_seen: Dict[Any, Any] = {}
         self.counters = {"steps": 0, "rows": 0, "max_entries_in_step": 0, "refused_steps": 0,
-                         "graphs_recorded": 0, "graph_replays": 0}
+                         "graphs_recorded": 0, "graph_replays": 0, "failed_steps": 0}
+        self._carried_updates: Optional[List[np.ndarray]] = None   # of a step that failed
 
     # ------------------------------------------------------------------ requests
     def open(self, request: Any) -> None:
@@ -199,7 +203,7 @@ class ModelRunner:
                 want += [r0 + int(w) for w in e.want]
                 segments.append(Segment(e.request, s, r0, n, p0))
                 r0 += n
-        updates = cache.take_table_updates()
+        updates = self._with_carried(cache.take_table_updates())
         n_want = len(want)
         max_pos = int(pos.max())
 
@@ -207,7 +211,7 @@ class ModelRunner:
         # CUDA graph per (rows, wanted rows, context bucket) and replayed.  Its layout of the
         # integer array is fixed, with room for a bounded number of block-table changes.
         graph_key = None
-        if self.use_graphs and rows == len(entries) and not cache.state and \
+        if self.use_graphs and rows == len(entries) and \
                 all(len(u) <= GRAPH_UPDATES_PER_ROW * rows for u in updates):
             bucket = 1 << max(7, max_pos.bit_length())
             graph_key = (rows, n_want, bucket)
@@ -221,6 +225,11 @@ class ModelRunner:
         for cap in upd_cap:
             o_upd.append(off)
             off += _round4(3 * cap)
+        # request slots opened for this step, whose fixed-size state starts at zero
+        fresh = cache.take_fresh_slots() if cache.state else []
+        fresh_cap = (rows if graph_key else len(fresh)) if cache.state else 0
+        o_fresh = off
+        off += _round4(fresh_cap)
         o_src = off                      # behind everything a recorded graph reads
         if device_tokens is not None:
             off += _round4(rows)
@@ -229,6 +238,9 @@ class ModelRunner:
         h[:HEADER] = 0
         for gi, u in enumerate(updates):
             h[gi] = len(u)
+        h[HEADER - 1] = len(fresh)
+        if fresh:
+            h[o_fresh:o_fresh + len(fresh)] = np.asarray(fresh, dtype=np.int32)
         h[o_tok:o_tok + rows] = tokens
         h[o_pos:o_pos + rows] = pos
         h[o_slot:o_slot + rows] = slot
@@ -246,11 +258,6 @@ class ModelRunner:
         ev = torch.cuda.Event()
         ev.record()
         self._meta_event[which] = ev
-        fresh = cache.take_fresh_slots()
-        if fresh and cache.state:
-            idx = torch.tensor(fresh, dtype=torch.long, device=self.device)
-            for st in cache.state.values():
-                st.index_fill_(0, idx, 0)
 
         ctx = StepContext(rows=rows, tokens=dev[o_tok:o_tok + rows],
                           row_pos=dev[o_pos:o_pos + rows], row_slot=dev[o_slot:o_slot + rows],
@@ -265,12 +272,20 @@ class ModelRunner:
                     kernels.table_update_counted(g.table, dev[o:o + 3 * cap], dev[gi:gi + 1], cap)
                 elif cap:
                     kernels.table_update(g.table, dev[o:o + 3 * cap], cap)
+            if fresh_cap:
+                for st in cache.state.values():
+                    kernels.zero_slots(st, dev[o_fresh:o_fresh + fresh_cap],
+                                       dev[HEADER - 1:HEADER], fresh_cap)
             return self._forward(ctx, want_dev, n_want)
 
-        if graph_key is None:
-            logits = forward()
-        else:
-            logits = self._graph_step(graph_key, forward)
+        try:
+            if graph_key is None:
+                logits = forward()
+            else:
+                logits = self._graph_step(graph_key, forward)
+        except BaseException:
+            self._after_failed_launch(updates, opened)
+            raise
         for e in entries:
             cache.advance(e.request, len(e.tokens))
         c = self.counters
@@ -278,6 +293,39 @@ class ModelRunner:
         c["rows"] += rows
         c["max_entries_in_step"] = max(c["max_entries_in_step"], len(entries))
         return logits
+
+    def _with_carried(self, updates: List[np.ndarray]) -> List[np.ndarray]:
+        """The block-table changes of this step, behind those of an earlier step that failed
+        before it could apply them (one triple per cell, the later value wins)."""
+        carried, self._carried_updates = self._carried_updates, None
+        if carried is None:
+            return updates
+        out = []
+        for old, new in zip(carried, updates):
+            cells = {(int(s), int(i)): int(p) for s, i, p in old}
+            cells.update({(int(s), int(i)): int(p) for s, i, p in new})
+            out.append(np.array([(s, i, p) for (s, i), p in cells.items()],
+                                dtype=np.int32).reshape(-1, 3))
+        return out
+
+    def _after_failed_launch(self, updates: List[np.ndarray], opened: Sequence[Any]) -> None:
+        """A launch of the step raised (a kernel refused a size, a buffer could not grow).  The
+        requests have not advanced.  What the step had already taken is put back so that later
+        steps are right: its block-table changes are kept for the next step, requests that it
+        opened are closed, and every workspace buffer is dropped (a split-K destination that is
+        kept at zero may hold partial sums), which also drops the recorded steps."""
+        self._carried_updates = updates
+        for r in opened:
+            if self.cache.has(r):
+                self.cache.close(r)
+        self.drop_recordings()
+        self.workspace.drop()
+        self.counters["failed_steps"] += 1
+
+    def drop_recordings(self) -> None:
+        """Forget every recorded step (they are recorded again when their shapes come back)."""
+        self._graphs.clear()
+        self._graph_seen.clear()
 
     def _forward(self, ctx: StepContext, want_dev: torch.Tensor, n_want: int) -> torch.Tensor:
         """Embedding, every layer call of the run order, final norm and head at the wanted

@@ -44,12 +44,13 @@ def _signatures():
         "llm_silu_mul": [P, P, I, I, I, P],
         "llm_table_update": [P, I, P, I, P],
         "llm_table_update_counted": [P, I, P, P, I, P],
+        "llm_zero_slots": [P, L, P, P, I, P],
         "llm_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, I, I, P],
         "llm_qk_norm_rope_store": [P, I, P, P, P, I, L, P, I, P, P, P, P, P, P, F, I, I, I, I, I,
                                    I, F, I, I, I, P],
         "llm_rope_table": [P, P, P, I, I, F, P],
         "llm_attention_generic": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P],
-        "llm_sample": [P, L, I, I, P, P, P, P, P, P, P],
+        "llm_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P],
         "llm_gemv_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, P],
         "llm_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "llm_attention_flash": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
@@ -63,6 +64,8 @@ def _signatures():
         "llm_attention_tcgen05": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, I, P, P],
         "llm_attention_tcgen05_x2": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
+        "llm_random_normal": [P, I, L, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, L,
+                              P],
     }
 
 
@@ -184,6 +187,15 @@ def table_update_counted(table: torch.Tensor, updates: torch.Tensor, count: torc
                                           _ptr(count), max_n, _stream()), "table_update")
 
 
+def zero_slots(state: torch.Tensor, slots: torch.Tensor, count: torch.Tensor, max_n: int) -> None:
+    """state[slots[i]] = 0 for i < count[0] (read on the device; at most ``max_n``)."""
+    _cuda(state, slots, count)
+    assert state.is_contiguous() and slots.dtype == torch.int32 and count.dtype == torch.int32
+    row_bytes = state[0].numel() * state.element_size()
+    _check(lib().llm_zero_slots(_ptr(state), row_bytes, _ptr(slots), _ptr(count), max_n,
+                                _stream()), "zero_slots")
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False
               ) -> None:
     """out (=|+=) a @ w.T on the CUDA cores with 32-bit accumulation; a [M,K], w [N,K]."""
@@ -252,16 +264,19 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
            top_p: torch.Tensor, min_p: torch.Tensor, uniform: torch.Tensor,
-           out: torch.Tensor) -> None:
+           out: torch.Tensor, status_out: Optional[torch.Tensor] = None) -> None:
     """One token per row of ``logits`` (float32 [rows, vocab]): greedy where temperature <= 0,
-    else top-k, top-p, min-p, temperature, softmax and a draw with the row's uniform."""
-    _cuda(logits, temperature, top_k, top_p, min_p, uniform, out)
+    else top-k, top-p, min-p, temperature, softmax and a draw with the row's uniform.
+    ``status_out`` (int32 [4]): the kernel also copies the library's status words there (see
+    :func:`status_words`), so that they reach the host in the same copy as the tokens."""
+    _cuda(logits, temperature, top_k, top_p, min_p, uniform, out, status_out)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     assert uniform.dtype == torch.float64 and top_k.dtype == torch.int32
     rows, vocab = logits.shape
+    status = status_words(logits.device) if status_out is not None else None
     _check(lib().llm_sample(_ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature),
                             _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(out),
-                            _stream()), "sample")
+                            _ptr(status), _ptr(status_out), _stream()), "sample")
 
 
 def apply_penalties(logits: torch.Tensor, triples: torch.Tensor, n: int, repeat: torch.Tensor,
@@ -271,6 +286,15 @@ def apply_penalties(logits: torch.Tensor, triples: torch.Tensor, n: int, repeat:
     _check(lib().llm_apply_penalties(_ptr(logits), logits.stride(0), _ptr(triples), n,
                                      _ptr(repeat), _ptr(freq), _ptr(presence), _stream()),
            "apply_penalties")
+
+
+def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0) -> None:
+    """out.flat[i] = mean + std * z(key, first + i), z a standard normal that is a function of
+    the key and the index alone (the same bits as ``weights.random_normal`` gives on a host)."""
+    _cuda(out)
+    assert out.is_contiguous()
+    _check(lib().llm_random_normal(_ptr(out), _dt(out), out.numel(), int(key), float(mean),
+                                   float(std), int(first), _stream()), "random_normal")
 
 
 # ------------------------------------------------------------------------------------------
@@ -311,14 +335,46 @@ def tc_status(device) -> torch.Tensor:
     return st
 
 
-def check_tc_status(device) -> None:
-    """Raise if a tensor-core kernel gave up waiting (synchronises the device)."""
+status_words = tc_status       # word 0: a wait that gave up; word 1: 1 + row of a bad token id
+
+
+def status_message(words) -> Optional[str]:
+    """What non-zero status words say, or None when all is well."""
+    if words[0]:
+        return f"a tcgen05 / TMA kernel gave up waiting on a barrier (role {int(words[0])})"
+    if words[1]:
+        return f"token id outside the embedding table at row {int(words[1]) - 1} of a step"
+    return None
+
+
+def clear_status(device) -> None:
     st = _tc_status.get(torch.device(device).index or 0)
     if st is not None:
-        code = int(st[0].item())
-        if code:
+        st.zero_()
+
+
+def check_tc_status(device) -> None:
+    """Raise if a kernel recorded a failure in the status words: a tensor-core kernel that gave
+    up waiting, or a token id outside the embedding table (synchronises the device; the words
+    are cleared)."""
+    st = _tc_status.get(torch.device(device).index or 0)
+    if st is not None:
+        msg = status_message(st.tolist())
+        if msg:
             st.zero_()
-            raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (role {code})")
+            raise KernelError(msg)
+
+
+def selftest_wait_gives_up(device, limit_cycles: int = 20000) -> None:
+    """Launch a one-block kernel that waits on a barrier at which nothing ever arrives, with a
+    limit of ``limit_cycles`` clock cycles (microseconds) instead of the two seconds of the real
+    kernels.  It gives up, records role 99 in the status words and returns: the way every
+    bounded wait of the TMA / tcgen05 kernels ends, made to happen without a fault."""
+    l = lib()
+    l.llm_selftest_wait_gives_up.argtypes = [c_void_p, c_longlong, c_void_p]
+    l.llm_selftest_wait_gives_up.restype = c_int
+    _check(l.llm_selftest_wait_gives_up(_ptr(status_words(device)), int(limit_cycles), _stream()),
+           "selftest_wait_gives_up")
 
 
 def token_tile(rows: int) -> int:
@@ -434,6 +490,18 @@ def gate_up_silu(ctx, h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tenso
 
 
 FLASH_HEAD_DIMS = (32, 64, 128)
+ATTENTION_MAX_HEAD_DIM = 256      # MAX_HD of attention_generic.cu, the kernel of last resort
+
+
+def attention_refusal(num_heads: int, num_kv_heads: int, head_dim: int) -> Optional[str]:
+    """Why no attention kernel of this library takes these sizes, or None when one does (the
+    generic kernel takes every head size that is a multiple of 8 up to 256 and every group)."""
+    if head_dim <= 0 or head_dim % 8 != 0 or head_dim > ATTENTION_MAX_HEAD_DIM:
+        return (f"head_dim {head_dim}: the attention kernels take multiples of 8 up to "
+                f"{ATTENTION_MAX_HEAD_DIM}")
+    if num_kv_heads <= 0 or num_heads % num_kv_heads != 0:
+        return f"{num_heads} query heads cannot be shared among {num_kv_heads} KV heads"
+    return None
 
 
 def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,

@@ -14,12 +14,14 @@ import torch
 
 from .. import kernels
 from ..cache import PagedKV
-from ..config.spec import PartSpec
+from ..config.spec import ConfigError, PartSpec
 from .base import BoundCall, StepContext, build_part, register_part, tensor_of
 from .linear import Linear
 
 
 class Attention:
+    graph_safe = True      # a step of single tokens reads positions and slots on the device only
+
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
         self.hidden = int(spec["hidden_size"])
         self.num_heads = int(spec["num_heads"])
@@ -27,6 +29,9 @@ class Attention:
         self.head_dim = int(spec["head_dim"])
         self.scale = float(spec["scale"])
         self.window = spec.get("window")
+        refusal = kernels.attention_refusal(self.num_heads, self.num_kv_heads, self.head_dim)
+        if refusal is not None:      # now, when the model is built, not at its first step
+            raise ConfigError(f"attention: {refusal}")
         self.q_width = self.num_heads * self.head_dim
         self.kv_width = self.num_kv_heads * self.head_dim
         self.position = (build_part("position", spec["position"], weights, dtype, device)
@@ -44,6 +49,10 @@ class Attention:
 
     def cache_need(self):
         return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+
+    def streamed_weights(self):
+        """The matrices a step reads once: q, k, v (stacked) and the output projection."""
+        return [self.qkv_proj.weight, self.o_proj.weight]
 
     def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor) -> None:
         rows = ctx.rows

@@ -83,6 +83,12 @@ class Workspace:
         self._views: Dict[Any, torch.Tensor] = {}     # (name, dtype, shape) -> view of the buffer
         self.generation = 0     # grows whenever a buffer moves: recorded launches are stale then
 
+    def drop(self) -> None:
+        """Forget every buffer: the next step makes them anew (zero-kept ones as zeros)."""
+        self._bufs.clear()
+        self._views.clear()
+        self.generation += 1
+
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype, zero: bool = False
             ) -> torch.Tensor:
         """``zero``: the buffer is created holding zeros (its users keep it that way)."""
@@ -181,9 +187,35 @@ class StepContext:
 
 @dataclass
 class BoundCall:
-    """A run-order entry at run time: which cache (if any) it writes or reads."""
+    """A run-order entry at run time: which caches (if any) it writes or reads.  A block says
+    what it keeps between steps as a list of needs (``cache_needs()``); every need gets a cache
+    entry of its own, numbered over the whole run order.  A block with one mixer has one."""
 
     index: int                     # position in the run order
     layer: int
     writes_cache: bool
-    cache_entry: Optional[int]     # run-order entry that owns the cache this call uses
+    cache_entry: Optional[int]     # the (first) cache entry this call uses
+    cache_entries: Tuple[int, ...] = ()   # one per need of the block, in the block's order
+
+    def for_need(self, k: int) -> "BoundCall":
+        """This call as the part that owns the block's k-th need sees it."""
+        return BoundCall(self.index, self.layer, self.writes_cache, self.cache_entries[k],
+                         self.cache_entries)
+
+
+def streamed_weights_of(part) -> List[torch.Tensor]:
+    """The matrices a part reads once per step, as the part itself declares them
+    (``streamed_weights()``).  A part that declares nothing cannot be counted."""
+    fn = getattr(part, "streamed_weights", None)
+    if fn is None:
+        raise TypeError(f"{type(part).__name__} does not declare streamed_weights(): the bytes "
+                        "a step reads cannot be counted for a model with this part")
+    return list(fn())
+
+
+def graph_safe(part) -> bool:
+    """Whether a part's work in a step of single tokens depends on the step only through
+    tensors on the device (``ctx.tokens``, ``ctx.row_pos``, ``ctx.row_slot``, the caches), so
+    that the step's launches can be recorded once and replayed.  A part says so with an
+    attribute ``graph_safe = True``; one that does not is taken to read host data."""
+    return bool(getattr(part, "graph_safe", False))

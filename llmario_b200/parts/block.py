@@ -8,7 +8,8 @@ from typing import Dict
 import torch
 
 from ..config.spec import LayerSpec, PartSpec
-from .base import BoundCall, StepContext, build_part, register_part
+from .base import (BoundCall, StepContext, build_part, graph_safe, register_part,
+                   streamed_weights_of)
 
 
 class PreNormResidualBlock:
@@ -20,10 +21,24 @@ class PreNormResidualBlock:
         self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, dtype,
                                        device)
 
+    def cache_needs(self):
+        """What this block keeps between steps: one need per stateful part, in a fixed order
+        (here the mixer's alone).  Each need gets a cache entry; ``call.for_need(k)`` is the
+        call as the owner of the k-th need sees it."""
+        return [self.mixer.cache_need()]
+
+    def streamed_weights(self):
+        return streamed_weights_of(self.mixer) + streamed_weights_of(self.feed_forward)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(graph_safe(p) for p in (self.mixer_norm, self.ffn_norm, self.mixer,
+                                           self.feed_forward))
+
     def forward(self, ctx: StepContext, call: BoundCall, x: torch.Tensor) -> None:
         h = ctx.buffer("block.h", x.shape)
         self.mixer_norm.apply(ctx, x, h)
-        self.mixer.forward(ctx, call, h, x)
+        self.mixer.forward(ctx, call.for_need(0) if call.cache_entries else call, h, x)
         self.ffn_norm.apply(ctx, x, h)
         self.feed_forward.forward(ctx, h, x)
 

@@ -14,6 +14,8 @@ from .linear import Linear
 
 
 class SwiGLU:
+    graph_safe = True
+
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
         self.hidden = int(spec["hidden_size"])
         self.ff = int(spec["intermediate_size"])
@@ -29,6 +31,9 @@ class SwiGLU:
         else:
             self.gate_up = Linear.stacked([gate, up])
         self.down = Linear(tensor_of(spec, "down", weights))
+
+    def streamed_weights(self):
+        return [self.gate_up.weight, self.down.weight]
 
     def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor) -> None:
         rows = ctx.rows

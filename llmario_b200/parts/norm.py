@@ -12,6 +12,8 @@ from .base import StepContext, register_part, tensor_of
 
 
 class RmsNorm:
+    graph_safe = True
+
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
         self.width = int(spec["width"])
         self.eps = float(spec["eps"])

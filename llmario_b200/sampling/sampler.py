@@ -7,6 +7,7 @@ top-k -> top-p -> min-p -> temperature -> softmax -> draw.  The window holds the
 """
 from __future__ import annotations
 
+import itertools
 import os
 from collections import deque
 from typing import Deque, Dict, List, Optional, Sequence
@@ -19,10 +20,14 @@ from .params import SamplingParams
 from .rng import Xoshiro256StarStar
 
 
+_serials = itertools.count(1)
+
+
 class RequestSampler:
     """Sampling state of one request."""
 
     def __init__(self, params: SamplingParams, vocab_size: int):
+        self.serial = next(_serials)      # never repeats: names this object in cached option rows
         self.params = params
         self.vocab_size = vocab_size
         self.seed = params.seed if params.seed is not None else \
@@ -50,16 +55,24 @@ class RequestSampler:
         return 0.0 if self.params.greedy else self.rng.next_f64()
 
 
+STATUS_WORDS = 4     # the library's status words travel in front of the tokens
+
+
 class PendingTokens:
     """Tokens that the device has drawn (or will, in stream order) and the host has not read."""
 
     def __init__(self, event, host: torch.Tensor, rows: int):
         self._event, self._host, self.rows = event, host, rows
+        self.status: Optional[List[int]] = None
 
     def result(self) -> List[int]:
-        """Wait for the draw and return the token ids."""
+        """Wait for the draw and return the token ids.  Afterwards ``status`` holds the
+        library's status words as they stood when the tokens were drawn (all zero when every
+        kernel before the draw ran to its end)."""
         self._event.synchronize()
-        return self._host[:self.rows].tolist()
+        words = self._host[:STATUS_WORDS + self.rows].tolist()
+        self.status = words[:STATUS_WORDS]
+        return words[STATUS_WORDS:]
 
 
 class DeviceSampler:
@@ -85,9 +98,10 @@ class DeviceSampler:
             self._host_event = [None, None]
             self._dev = torch.empty(c * 10, dtype=torch.float32, device=self.device)
             self._dev_key = None
-            self._out = torch.empty(c, dtype=torch.int32, device=self.device)
+            # [status words | tokens]: one copy brings both to the host
+            self._out = torch.zeros(STATUS_WORDS + c, dtype=torch.int32, device=self.device)
             # two host copies in turn: a draw may be launched before the one before it is read
-            self._out_host = [torch.empty(c, dtype=torch.int32, pin_memory=True)
+            self._out_host = [torch.empty(STATUS_WORDS + c, dtype=torch.int32, pin_memory=True)
                               for _ in range(2)]
             self._flip = 0
         if triples:
@@ -101,7 +115,7 @@ class DeviceSampler:
     @property
     def device_tokens(self) -> torch.Tensor:
         """The int32 device buffer whose first rows hold the tokens of the latest draw."""
-        return self._out
+        return self._out[STATUS_WORDS:]
 
     def sample(self, logits: torch.Tensor, samplers: Sequence[RequestSampler]) -> List[int]:
         """``logits`` float32 [rows, vocab] on the device (modified in place by penalties);
@@ -124,7 +138,7 @@ class DeviceSampler:
         c = self._cap
         # the options of a row change only when the set of requests changes; the uniforms
         # change with every draw (greedy rows draw nothing)
-        key = [id(s) for s in samplers]
+        key = [s.serial for s in samplers]
         any_draw = any(not s.params.greedy for s in samplers)
         if key != self._dev_key or any_draw:
             i = self._flip
@@ -148,7 +162,6 @@ class DeviceSampler:
             self._host_event[i] = torch.cuda.Event()
             self._host_event[i].record()
             self._dev_key = key
-            self._last_objs = list(samplers)     # keeps the ids above from being reused
         d = self._dev
         if tri:
             n = len(tri) // 3
@@ -161,10 +174,12 @@ class DeviceSampler:
             kernels.apply_penalties(logits, self._tri_dev, n, d[3 * c:4 * c], d[4 * c:5 * c],
                                     d[5 * c:6 * c])
         kernels.sample(logits, d[0:c], d[6 * c:7 * c].view(torch.int32), d[c:2 * c],
-                       d[2 * c:3 * c], d[8 * c:10 * c].view(torch.float64), self._out)
+                       d[2 * c:3 * c], d[8 * c:10 * c].view(torch.float64),
+                       self._out[STATUS_WORDS:], self._out[:STATUS_WORDS])
         host = self._out_host[self._flip]
         self._flip ^= 1
-        host[:rows].copy_(self._out[:rows], non_blocking=True)
+        n = STATUS_WORDS + rows
+        host[:n].copy_(self._out[:n], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         return PendingTokens(event, host, rows)

@@ -113,45 +113,42 @@ def load_weights(model_dir: str, spec: ModelSpec, dtype: torch.dtype,
 # ------------------------------------------------------------------------------------------
 # random weights
 # ------------------------------------------------------------------------------------------
-def _tensor_seed(seed: int, name: str) -> int:
-    h = 0xCBF29CE484222325  # FNV-1a over the name, mixed with the seed
-    for b in name.encode():
-        h = ((h ^ b) * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
-    return (h ^ (seed * 0x9E3779B97F4A7C15)) & 0x7FFFFFFFFFFFFFFF
-
-
 def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype,
                    device: torch.device | str = "cpu", matrix_std: float = 0.02,
                    gain_std: float = 0.01) -> Dict[str, torch.Tensor]:
     """Seeded weights: matrices ~ N(0, matrix_std), one-dimensional gains 1 + N(0, gain_std).
-    Every tensor has a generator of its own, seeded from (seed, name), so the values do not
-    depend on the order of creation.  Values differ between devices."""
+    Every element is a function of (seed, tensor name, element index) alone
+    (:mod:`.random_normal`): the values are the same bits on a CUDA device (made by the kernel
+    of ``csrc/random_weights.cu``) and on the host (made by NumPy), and do not depend on the
+    order of creation."""
+    from .random_normal import normal_f32, tensor_key
+
     out: Dict[str, torch.Tensor] = {}
     device = torch.device(device)
     for name, shape in expected_tensors(spec).items():
-        g = torch.Generator(device=device)
-        g.manual_seed(_tensor_seed(seed, name))
-        if len(shape) == 1:
-            t = 1.0 + gain_std * torch.randn(shape, generator=g, device=device,
-                                             dtype=torch.float32)
-            out[name] = t.to(dtype)
+        key = tensor_key(seed, name)
+        mean, std = (1.0, gain_std) if len(shape) == 1 else (0.0, matrix_std)
+        t = torch.empty(shape, dtype=dtype, device=device)
+        if device.type == "cuda":
+            from .. import kernels
+
+            kernels.random_normal(t, key, mean, std)
         else:
-            # generate in slabs so that a large table never exists twice in 32-bit
-            t = torch.empty(shape, dtype=dtype, device=device)
             flat = t.view(-1)
-            step = 1 << 26
+            step = 1 << 22          # slabs bound the 64-bit temporaries
             for start in range(0, flat.numel(), step):
                 n = min(step, flat.numel() - start)
-                flat[start:start + n] = (matrix_std * torch.randn(
-                    n, generator=g, device=device, dtype=torch.float32)).to(dtype)
-            out[name] = t
+                flat[start:start + n] = torch.from_numpy(normal_f32(key, start, n, mean, std)
+                                                         ).to(dtype)
+        out[name] = t
     return out
 
 
-def write_random_model(model_dir: str, config, seed: int, dtype: Optional[torch.dtype] = None
-                       ) -> str:
+def write_random_model(model_dir: str, config, seed: int, dtype: Optional[torch.dtype] = None,
+                       device: torch.device | str = "cpu") -> str:
     """Write ``config.json`` and ``model.safetensors`` of a model with seeded random weights.
-    ``config`` is the typed configuration of a registered architecture."""
+    ``config`` is the typed configuration of a registered architecture.  ``device``: where the
+    values are made before they are written (the file is the same either way)."""
     import json
 
     names = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}
@@ -160,7 +157,8 @@ def write_random_model(model_dir: str, config, seed: int, dtype: Optional[torch.
         dtype = names.get(raw.get("torch_dtype", "bfloat16"), torch.bfloat16)
     raw["torch_dtype"] = {v: k for k, v in names.items()}[dtype]
     os.makedirs(model_dir, exist_ok=True)
-    tensors = random_tensors(config.to_spec(), seed, dtype, "cpu")
+    tensors = random_tensors(config.to_spec(), seed, dtype, device)
+    tensors = {n: t.cpu() for n, t in tensors.items()}
     write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors,
                       {"format": "pt", "seed": str(seed)})
     with open(os.path.join(model_dir, "config.json"), "w") as f:

@@ -248,7 +248,8 @@ def test_python_bindings_match_the_c_declarations():
     src = ""
     for f in sorted((pathlib.Path(kernels.__file__).parent / "csrc").glob("*.cu")):
         src += f.read_text()
-    kinds = {ctypes.c_void_p: "P", ctypes.c_int: "I", ctypes.c_longlong: "L", ctypes.c_float: "F"}
+    kinds = {ctypes.c_void_p: "P", ctypes.c_int: "I", ctypes.c_longlong: "L", ctypes.c_float: "F",
+             ctypes.c_ulonglong: "U", ctypes.c_double: "D"}
 
     def kind(param: str) -> str:
         param = param.strip()
@@ -256,8 +257,8 @@ def test_python_bindings_match_the_c_declarations():
             return "P"
         base = re.sub(r"\b(const|unsigned)\b", "", param).split()
         if base[:2] == ["long", "long"]:
-            return "L"
-        return {"int": "I", "float": "F"}[base[0]]
+            return "U" if re.search(r"\bunsigned\b", param) else "L"
+        return {"int": "I", "float": "F", "double": "D"}[base[0]]
 
     sigs = kernels._signatures()
     seen = set()

@@ -28,5 +28,5 @@ def test_whole_prompts(name, dtype):
         toks = random_tokens(name, n, seed=100 + i)
         logits = runner.step([StepEntry(f"r{i}", toks, list(range(n)))]).cpu().numpy()
         runner.close(f"r{i}")
-        assert_close(logits, plain_logits(name, dtype, toks), dtype, f"{name} {dtype} n={n}")
+        assert_close(logits, plain_logits(name, dtype, toks), dtype, f"{name} {dtype} n={n}", name)
     runner.cache.check_invariants()

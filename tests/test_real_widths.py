@@ -1,0 +1,148 @@
+"""The widths of the benchmark model against the plain implementation.
+
+Configuration W has the layer sizes that ``bench.py`` times (hidden 4096, 32 query heads on 8 KV
+heads of 128, feed-forward 12288) with two layers and a vocabulary of 2,048, so that the plain
+float64 implementation can follow it on the CPU.  At these widths the bfloat16 engine takes the
+tcgen05 products (with split K for few rows, on CTA pairs for many), the tcgen05 attention of
+prompt portions and the TMA decode attention; with many live requests decode attention splits
+the keys and merges, with few it runs fused with the rotation and the cache write; steps of
+single tokens are recorded as CUDA graphs, one per context bucket.  Every cut of the work, in
+32-bit and in bfloat16, with pages of 16 and of 64 positions, is compared with the plain logits.
+"""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import traces
+from test_replay import requests_for, run_in_process
+from util import TINY, assert_close, model_dir, plain_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+NAME = "W"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("page", [16, 64])
+def test_every_cut_at_benchmark_widths(dtype, page):
+    reqs = requests_for(NAME, (45, 170, 300), seed=7)
+    for mode in ("whole", "bulk_then_tail", "portions"):
+        steps = getattr(traces, mode)(reqs)
+        out, _ = run_in_process(NAME, dtype, steps, traces.peak_tokens(steps), page=page)
+        traces.check(steps, out, reqs, NAME, dtype, f"W {dtype} {mode}, pages of {page}")
+    reqs = requests_for(NAME, (40, 23, 75, 7, 1, 110, 64, 33, 90), seed=11)
+    steps = traces.mixed(reqs, live=4, seed=3)
+    out, runner = run_in_process(NAME, dtype, steps, traces.peak_tokens(steps), page=page)
+    traces.check(steps, out, reqs, NAME, dtype, f"W {dtype} mixed, pages of {page}")
+    assert runner.cache.counters["pages_allocated"] > runner.cache.groups[0].n_pages
+
+
+def _count(monkeypatch, kernels, names):
+    calls = {n: 0 for n in names}
+    for n in names:
+        real = getattr(kernels, n)
+
+        def counted(*a, _real=real, _n=n, **k):
+            calls[_n] += 1
+            return _real(*a, **k)
+
+        monkeypatch.setattr(kernels, n, counted)
+    return calls
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("live", [72, 8])
+def test_many_live_requests_decode_through_recorded_steps(dtype, live, monkeypatch):
+    """``live`` requests with prompts of unequal length, then 44 steps of one token each.  Many
+    requests share a length modulo the page size, so their block tables change in the same
+    step; the context bucket of the recorded step changes on the way (positions cross 128).
+    With 72 live rows bfloat16 decode attention splits the keys and merges; with 8 it is the
+    fused kernel.  Every row of every step against the plain implementation."""
+    from llmario_b200 import kernels
+    from llmario_b200.engine import Model, ModelRunner, StepEntry
+
+    page, steps = 16, 44
+    rng = random.Random(live)
+    # lengths: a third end just before a page edge, so that their first decode steps all open a
+    # new page together; the rest spread out, a few long enough to start beyond position 128
+    lengths = [(15, 31, 47)[i % 3] if i % 3 == 0 else rng.randint(3, 60) for i in range(live)]
+    for i in range(0, live, 9):
+        lengths[i] = rng.randint(100, 120)
+    prompts = {f"r{i}": random_tokens(NAME, n, 500 + i) for i, n in enumerate(lengths)}
+    tails = {r: random_tokens(NAME, steps, 900 + i) for i, r in enumerate(prompts)}
+    model = Model.from_folder(model_dir(NAME, dtype), dtype, DEV)
+    cache_tokens = sum(-(-(n + steps) // page) * page for n in lengths) + page
+    runner = ModelRunner(model, page_size=page, cache_tokens=cache_tokens, max_requests=live,
+                         max_context=256, token_budget=1024)
+    calls = _count(monkeypatch, kernels, ("attention_decode_fused", "attention_decode_tma",
+                                          "attention_merge"))
+    ids = list(prompts)
+    got = {r: [] for r in ids}
+    at = 0
+    while at < live:                     # prompts, several to a step, under the token budget
+        batch, rows = [], 0
+        while at < live and rows + lengths[at] <= 1024 and len(batch) < 16:
+            batch.append(ids[at])
+            rows += lengths[at]
+            at += 1
+        res = runner.step([StepEntry(r, prompts[r], [len(prompts[r]) - 1]) for r in batch])
+        for j, r in enumerate(batch):
+            got[r].append(res[j:j + 1].cpu().numpy())
+    before = dict(calls)
+    crossings = 0
+    for s in range(steps):
+        crossings = max(crossings, sum((lengths[i] + s) % page == 0 for i in range(live)))
+        res = runner.step([StepEntry(r, [tails[r][s]], [0]) for r in ids]).cpu().numpy()
+        for j, r in enumerate(ids):
+            got[r].append(res[j:j + 1])
+        runner.cache.check_invariants()
+    kernels.check_tc_status(DEV)
+    assert crossings >= max(2, live // 5)       # that many requests opened a page in one step
+    c = runner.counters
+    assert c["graphs_recorded"] >= 2 and c["graph_replays"] >= steps - 6, c
+    if dtype == "bfloat16":
+        fused = calls["attention_decode_fused"] - before["attention_decode_fused"]
+        split = calls["attention_decode_tma"] - before["attention_decode_tma"]
+        if live >= 64:
+            assert fused == 0 and split > 0 and calls["attention_merge"] > before["attention_merge"]
+        else:
+            assert fused > 0 and split == 0
+    for r in ids:
+        ref = plain_logits(NAME, dtype, prompts[r] + tails[r])
+        rows = np.concatenate(got[r])
+        assert_close(rows, ref[len(prompts[r]) - 1:len(prompts[r]) + steps], dtype,
+                     f"W {dtype} {live} live, {r}", NAME)
+    for r in ids:
+        runner.close(r)
+    assert all(f == runner.cache.groups[0].n_pages for f in runner.cache.free_pages())
+
+
+@pytest.mark.parametrize("lookahead", [False, True])
+def test_generation_with_many_requests_at_benchmark_widths(lookahead):
+    """Greedy generation of 72 requests through the entry point in bfloat16, with and without
+    the next step queued ahead: for a sample of the requests the plain implementation reads the
+    engine's own sequence and must choose the same token at every place where its two best
+    logits are further apart than the engine's rounding."""
+    from llmario_b200 import Engine, SamplingParams
+
+    live, new = 72, 40
+    rng = random.Random(3)
+    prompts = [random_tokens(NAME, rng.randint(3, 70), 700 + i) for i in range(live)]
+    eng = Engine(model_dir(NAME, "bfloat16"), dtype="bfloat16", page_size=16,
+                 cache_tokens=live * 128, max_requests=live, context=256, token_budget=512,
+                 lookahead=lookahead)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True))
+    st = eng.stats()
+    assert st["finished"] == live and st["graph_replays"] >= new // 2
+    assert (st["steps_planned_ahead"] > new // 2) == lookahead
+    assert st["free_pages"] == st["pages"] and st["failed_steps"] == 0
+    for i in range(0, live, 6):
+        assert len(outs[i]) == new
+        ref = plain_logits(NAME, "bfloat16", prompts[i] + outs[i])
+        for j, tok in enumerate(outs[i]):
+            l = ref[len(prompts[i]) - 1 + j]
+            top = np.sort(l)[-2:]
+            if top[1] - top[0] > 3e-2 * max(1.0, float(np.abs(l).max())):
+                assert tok == int(np.argmax(l)), (i, j, tok, int(np.argmax(l)))

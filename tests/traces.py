@@ -111,6 +111,6 @@ def check(steps: List[dict], results: Dict[int, np.ndarray], requests: Dict[str,
             at[e["id"]] += len(e["tokens"])
         if rows:
             got = results[s["step"]]
-            assert_close(got, np.stack(rows), dtype, f"{what} step {s['step']}")
+            assert_close(got, np.stack(rows), dtype, f"{what} step {s['step']}", name)
     for rid, toks in requests.items():
         assert at[rid] == len(toks), f"trace did not feed all of {rid}"
