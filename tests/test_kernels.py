@@ -730,3 +730,102 @@ def test_attention_tcgen05_persistent(Hq, Hkv, hd, page, window):
         ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
         got = outs[0][i].reshape(Hq, hd).double().cpu()
         assert (got - ref).abs().max() <= 2e-2, (i, r, p, (got - ref).abs().max())
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(32, 8, 128, 32, None), (16, 4, 64, 64, 900)])
+def test_attention_tcgen05_x2_long_prompt_against_the_formulas(Hq, Hkv, hd, page, window):
+    """Two query tiles per CTA on a prompt of 2,700 tokens (the length at which the engine
+    chooses this kernel) and a portion that continues a request at position 2,700, directly
+    against the float64 formula on a sample of rows: the first and last rows of items and of
+    the two tiles of an item, rows whose keys end inside a page, and random ones."""
+    from llmario_b200 import kernels
+    dtype = torch.bfloat16
+    G = Hq // Hkv
+    cap = 2 * (128 // G)
+    lengths = [2700, 2700 + 300]
+    storage, table, ks, vs = paged_setup(lengths, page, Hkv, hd, dtype, seed=12)
+    scale = 1 / math.sqrt(hd)
+    spans = [(0, 0, 2700), (1, 2700, 3000)]
+    rows, items = [], []
+    for r, a, b in spans:
+        for at in range(a, b, cap):
+            n = min(cap, b - at)
+            items.append((len(rows), n, r, at))
+            rows += [(r, p) for p in range(at, at + n)]
+    q = torch.randn(len(rows), Hq, hd, generator=torch.Generator().manual_seed(21)).to(dtype)
+    out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
+    kernels.attention_tcgen05_x2(q.reshape(len(rows), -1).to(DEV).contiguous(), out,
+                                 storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table,
+                                 torch.tensor(items, dtype=torch.int32, device=DEV).reshape(-1),
+                                 len(items), Hq, Hkv, hd, page, scale, window, storage.shape[0])
+    kernels.check_tc_status(DEV)
+    assert torch.isfinite(out.float()).all()
+    rng = random.Random(5)
+    sample = {0, 1, cap // 2 - 1, cap // 2, cap - 1, cap, 2699, 2700, 2700 + cap // 2, len(rows) - 1}
+    sample |= {rng.randrange(len(rows)) for _ in range(30)}
+    for i in sorted(sample):
+        r, p = rows[i]
+        ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
+        got = out[i].reshape(Hq, hd).double().cpu()
+        assert (got - ref).abs().max() <= 2e-2, (i, r, p, float((got - ref).abs().max()))
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(8, 2, 128, 16, None), (6, 3, 64, 8, 50),
+                                                   (32, 8, 128, 64, None)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_attention_decode_fused_against_the_formulas(Hq, Hkv, hd, page, window, splits):
+    """The fused decode kernel directly against float64: per-head norm of the new query and
+    key, half-split rotation by the position's angles, the new key and value stored (as
+    bfloat16) at the request's last position, attention over the cache."""
+    from types import SimpleNamespace
+    from llmario_b200 import kernels
+    dtype = torch.bfloat16
+    lengths = [1, 33, 150, 64, 700, 385, 32, 65]
+    rows = len(lengths)
+    storage, table, ks, vs = paged_setup(lengths, page, Hkv, hd, dtype, seed=2)
+    scale, eps = 1 / math.sqrt(hd), 1e-5
+    slot = torch.arange(rows, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    width = (Hq + 2 * Hkv) * hd
+    proj = rnd(rows, width, scale=2.0, seed=3)
+    qw, kw = 1 + 0.1 * rnd(hd, seed=1), 1 + 0.1 * rnd(hd, seed=2)
+    inv = np.power(np.float32(1e4), -(np.arange(hd // 2, dtype=np.float32) * 2) / hd).astype(np.float32)
+    cs = torch.empty(rows, hd // 2, 2, dtype=torch.float32, device=DEV)
+    kernels.rope_table(pos, torch.tensor(inv, device=DEV), cs, 1.0)
+    bufs = {}
+    ctx = SimpleNamespace(rows=rows, max_pos=max(lengths) - 1, row_slot=slot, row_pos=pos, dtype=dtype,
+                          buffer=lambda name, shape, dt=torch.bfloat16, zero=False: bufs.setdefault(
+                              (name, tuple(shape)), torch.empty(*shape, dtype=dt, device=DEV)),
+                          segments=[SimpleNamespace(rows=1) for _ in range(rows)])
+    view = SimpleNamespace(storage=storage, slot=1, k=storage[0, 1, 0], v=storage[0, 1, 1],
+                           page_stride=storage.stride(0), block_table=table, page_size=page)
+    used = proj.clone()
+    got = torch.zeros(rows, Hq * hd, dtype=dtype, device=DEV)
+    kernels.attention_decode_fused(ctx, used, got, view, True, qw, kw, cs, eps, True, Hq, Hkv, hd,
+                                   scale, window, splits=splits)
+    kernels.check_tc_status(DEV)
+    assert int((used != 0).sum()) == 0          # what was consumed of the projection is cleared
+
+    def head_norm_rope(x, w, p):       # x [heads, hd] float64
+        x = x * (1.0 / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)) * w
+        ang = p * torch.tensor(inv, dtype=torch.float64)
+        a, b = x[:, :hd // 2], x[:, hd // 2:]
+        return torch.cat([a * torch.cos(ang) - b * torch.sin(ang),
+                          a * torch.sin(ang) + b * torch.cos(ang)], -1)
+
+    pr = proj.double().cpu()
+    qwd, kwd = qw.double().cpu(), kw.double().cpu()
+    for r, n in enumerate(lengths):
+        p = n - 1
+        q = head_norm_rope(pr[r, :Hq * hd].reshape(Hq, hd), qwd, p)
+        k_new = head_norm_rope(pr[r, Hq * hd:(Hq + Hkv) * hd].reshape(Hkv, hd), kwd, p)
+        v_new = pr[r, (Hq + Hkv) * hd:].reshape(Hkv, hd)
+        k, v = ks[r].double().clone(), vs[r].double().clone()
+        k[p], v[p] = k_new.bfloat16().double(), v_new.bfloat16().double()
+        ref = attention_ref(q.bfloat16().double(), k, v, p, window, scale)
+        err = (got[r].reshape(Hq, hd).double().cpu() - ref).abs().max()
+        assert err <= 2e-2, (r, n, float(err))
+        # the cache holds the new key and value at the request's last position
+        pg, s = table[r, p // page].item(), p % page
+        assert (storage[pg, 1, 0, :, s].double().cpu() - k_new).abs().max() <= 2e-2 * k_new.abs().max()
+        assert (storage[pg, 1, 1, :, s].double().cpu() - v_new).abs().max() <= 2e-2 * v_new.abs().max()

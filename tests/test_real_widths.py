@@ -58,8 +58,8 @@ def test_many_live_requests_decode_through_recorded_steps(dtype, live, monkeypat
     """``live`` requests with prompts of unequal length, then 44 steps of one token each.  Many
     requests share a length modulo the page size, so their block tables change in the same
     step; the context bucket of the recorded step changes on the way (positions cross 128).
-    With 72 live rows bfloat16 decode attention splits the keys and merges; with 8 it is the
-    fused kernel.  Every row of every step against the plain implementation."""
+    With 72 live rows bfloat16 decode attention splits the keys and merges once the contexts
+    have grown; with 8 it is the fused kernel.  Every row of every step against the plain implementation."""
     from llmario_b200 import kernels
     from llmario_b200.engine import Model, ModelRunner, StepEntry
 
@@ -105,8 +105,8 @@ def test_many_live_requests_decode_through_recorded_steps(dtype, live, monkeypat
     if dtype == "bfloat16":
         fused = calls["attention_decode_fused"] - before["attention_decode_fused"]
         split = calls["attention_decode_tma"] - before["attention_decode_tma"]
-        if live >= 64:
-            assert fused == 0 and split > 0 and calls["attention_merge"] > before["attention_merge"]
+        if live >= 64:      # (while every context is short the 72 rows still fit the fused kernel)
+            assert split > 0 and calls["attention_merge"] > before["attention_merge"]
         else:
             assert fused > 0 and split == 0
     for r in ids:

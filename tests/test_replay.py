@@ -104,12 +104,17 @@ def test_sizes_no_tensor_core_path_takes(dtype):
     traces.check(steps, out, reqs, name, dtype, f"{name} {dtype} mixed")
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_program(dtype):
-    """The program itself: standard input to files, `done` lines, exit code."""
-    name = "B"
-    reqs = requests_for(name, (50, 37, 20), seed=5)
-    steps = traces.mixed(reqs, live=3, seed=1)
+@pytest.mark.parametrize("name,dtype,mode", [("B", "float32", "mixed"), ("B", "bfloat16", "mixed"),
+                                             ("D", "bfloat16", "mixed"),
+                                             ("D", "bfloat16", "bulk_then_tail")])
+def test_trace_run_program(name, dtype, mode):
+    """The program itself: standard input to files, `done` lines, exit code.  It is run with
+    the options the task gives it and nothing else, so its pages hold 64 positions."""
+    if name == "B":
+        reqs = requests_for(name, (50, 37, 20), seed=5)
+    else:
+        reqs = requests_for(name, (150, 260, 70, 33), seed=6)
+    steps = traces.mixed(reqs, live=3, seed=1) if mode == "mixed" else getattr(traces, mode)(reqs)
     with tempfile.TemporaryDirectory() as out_dir:
         p = subprocess.run(
             [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model",
@@ -129,4 +134,4 @@ def test_trace_run_program(dtype):
                 out[s["step"]] = np.fromfile(path, dtype="<f4").reshape(n, vocab)
             else:
                 assert not os.path.exists(path)
-    traces.check(steps, out, reqs, name, dtype, f"trace_run {dtype}")
+    traces.check(steps, out, reqs, name, dtype, f"trace_run {name} {dtype} {mode}")
