@@ -35,7 +35,7 @@ class Engine:
                  num_pages: Optional[int] = None, cache_tokens: Optional[int] = None,
                  token_budget: int = 512, max_requests: int = 64,
                  context: Optional[int] = None, num_layers: Optional[int] = None,
-                 lookahead: bool = True):
+                 lookahead: bool = True, native: bool = True):
         """``model``: a folder with config.json and model.safetensors, or a built
         :class:`Model`; or give ``config`` (a typed configuration) and ``seed`` for random
         weights.  ``context``: most tokens of one request; ``max_requests``: requests running at
@@ -44,7 +44,9 @@ class Engine:
         of the free device memory hold, whichever is less).  ``lookahead``:
         while a step of decoding requests runs, the next one is already queued on the device
         with its input tokens taken from the sampler's output there, so that the device does
-        not wait for the host between steps; the tokens a caller sees are the same."""
+        not wait for the host between steps; the tokens a caller sees are the same.
+        ``native``: standard blocks are driven by the C++ step driver (one call per run of
+        layers) instead of launch by launch from Python; the launches are the same."""
         if not torch.cuda.is_available():
             raise RuntimeError("llmario_b200 needs a CUDA device; there is no CPU path")
         if isinstance(model, Model):
@@ -59,7 +61,8 @@ class Engine:
         ctx = int(context or spec.max_positions)
         self.runner = ModelRunner(self.model, page_size=page_size, n_pages=num_pages,
                                   max_requests=max_requests, max_context=ctx,
-                                  token_budget=token_budget, cache_tokens=cache_tokens)
+                                  token_budget=token_budget, cache_tokens=cache_tokens,
+                                  use_native=native)
         self.scheduler = Scheduler(self.runner.cache, token_budget, ctx, spec.eos_token_ids)
         self.sampler = DeviceSampler(self.model.device)
         self._ids = itertools.count()
@@ -166,8 +169,7 @@ class Engine:
         self._flying = None
         torch.cuda.current_stream().synchronize()
         kernels.clear_status(self.model.device)
-        self.runner.drop_recordings()
-        self.runner.workspace.drop()       # a buffer kept at zero may hold partial sums
+        self.runner.drop_buffers()         # a buffer kept at zero may hold partial sums
         for plan in plans:
             for e in plan.entries:
                 if e.request.state != FINISHED:

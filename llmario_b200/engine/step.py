@@ -21,6 +21,7 @@ import torch
 from .. import kernels
 from ..cache import CacheError, CacheFull, CacheManager, PagedKV
 from ..parts import Segment, StepContext, Workspace
+from . import native
 from .model import Model
 
 
@@ -49,7 +50,7 @@ class ModelRunner:
     def __init__(self, model: Model, page_size: int = 64, n_pages: Optional[int] = None,
                  max_requests: int = 64, max_context: Optional[int] = None,
                  token_budget: int = 2048, cache_tokens: Optional[int] = None,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, use_native: bool = True):
         self.model = model
         self.device = model.device
         if self.device.type != "cuda":
@@ -79,6 +80,11 @@ class ModelRunner:
                                   self.max_context)
         self.cache.allocate_storage(model.dtype, self.device)
         self.workspace = Workspace(self.device)
+        # blocks that are the standard arrangement of the standard parts are driven from C++,
+        # one call per run of them; every other block runs through its own forward()
+        self.native = native.NativeLayers(model, self.cache) if use_native else None
+        if self.native is not None and not self.native.any():
+            self.native = None
         self._meta_dev: Optional[torch.Tensor] = None
         self._meta_host: List[Optional[torch.Tensor]] = [None, None]
         self._meta_event: List[Optional[torch.cuda.Event]] = [None, None]
@@ -318,8 +324,7 @@ class ModelRunner:
         for r in opened:
             if self.cache.has(r):
                 self.cache.close(r)
-        self.drop_recordings()
-        self.workspace.drop()
+        self.drop_buffers()
         self.counters["failed_steps"] += 1
 
     def drop_recordings(self) -> None:
@@ -327,14 +332,36 @@ class ModelRunner:
         self._graphs.clear()
         self._graph_seen.clear()
 
+    def drop_buffers(self) -> None:
+        """Forget every temporary buffer, those of the native driver included, and with them
+        the recorded steps: after a failure a buffer that is kept at zero may hold sums."""
+        self.drop_recordings()
+        self.workspace.drop()
+        if self.native is not None:
+            native.arena_drop()
+
+    def _generation(self):
+        return (self.workspace.generation, self._meta_generation,
+                native.arena_generation() if self.native is not None else 0)
+
     def _forward(self, ctx: StepContext, want_dev: torch.Tensor, n_want: int) -> torch.Tensor:
         """Embedding, every layer call of the run order, final norm and head at the wanted
         rows.  Returns a view of a workspace buffer: read it before the next step."""
         m = self.model
         x = ctx.buffer("x", (ctx.rows, m.hidden_size), torch.float32)
         m.embedding.forward(ctx, ctx.tokens, x)
-        for call in m.calls:
-            m.blocks[call.layer].forward(ctx, call, x)
+        nat = self.native
+        if nat is not None:
+            nat.begin_step(ctx, x)
+        calls, i = m.calls, 0
+        while i < len(calls):
+            n = nat.runs.get(i) if nat is not None else None
+            if n:
+                nat.run(i, n)
+                i += n
+            else:
+                m.blocks[calls[i].layer].forward(ctx, calls[i], x)
+                i += 1
         logits = ctx.buffer("logits", (n_want, m.vocab_size), torch.float32)
         if n_want:
             hsel = ctx.buffer("head.h", (n_want, m.hidden_size))
@@ -346,7 +373,7 @@ class ModelRunner:
         """Run ``forward`` eagerly the first time a key is seen, record it the second time,
         replay the recording from then on.  A recording is dropped when a workspace buffer or
         the integer array has moved since."""
-        gen = (self.workspace.generation, self._meta_generation)
+        gen = self._generation()
         rec = self._graphs.get(key)
         if rec is not None and rec[0] == gen:
             rec[1].replay()
@@ -356,8 +383,8 @@ class ModelRunner:
         if self._graph_seen.get(key) != gen:
             self._graph_seen[key] = gen          # warm: sizes every buffer, loads every kernel
             out = forward()
-            if (self.workspace.generation, self._meta_generation) != gen:
-                self._graph_seen[key] = (self.workspace.generation, self._meta_generation)
+            if self._generation() != gen:
+                self._graph_seen[key] = self._generation()
             return out
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()

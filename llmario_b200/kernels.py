@@ -631,7 +631,20 @@ def attention_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tens
         _ptr(clear), clear.stride(0) if clear is not None else 0, _stream()), "attention_merge")
 
 
-FUSE_DECODE = "few waves"     # or "always" / "never": for measurements
+FUSE_DECODE = "few waves"     # or "always" / "never": for measurements (see fuse_decode)
+
+
+def fuse_decode(mode: str) -> None:
+    """When decode attention runs fused with the rotation and the cache write: "few waves" (the
+    default), "always" or "never".  For measurements; sets it for parts driven from Python and
+    for the native step driver alike."""
+    global FUSE_DECODE
+    code = {"few waves": 0, "always": 1, "never": 2}[mode]
+    FUSE_DECODE = mode
+    l = lib()
+    l.llm_set_fuse_decode.argtypes = [c_int]
+    l.llm_set_fuse_decode.restype = None
+    l.llm_set_fuse_decode(code)
 
 
 def decode_fusion_ok(ctx, view, num_heads: int, num_kv_heads: int, head_dim: int, rot_dim: int,

@@ -109,8 +109,9 @@ def test_long_portion_with_two_query_tiles_per_cta(models, monkeypatch):
         if not two_tiles:
             monkeypatch.setattr(kernels, "prefill_x2_ok", lambda *a: False)
         monkeypatch.setattr(kernels, "attention_tcgen05_x2", counted)
+        # (driven from Python, so that the choice of kernel can be overridden from here)
         runner = ModelRunner(m16, page_size=32, cache_tokens=8192, max_requests=2,
-                             max_context=8192, token_budget=4096)
+                             max_context=8192, token_budget=4096, use_native=False)
         a = runner.step([StepEntry("r", toks[:2600], want)]).float().cpu().numpy()
         b = runner.step([StepEntry("r", toks[2600:], [0, 1234, 2499])]).float().cpu().numpy()
         kernels.check_tc_status(DEV)
