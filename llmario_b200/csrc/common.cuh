@@ -93,11 +93,20 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 extern int g_llm_pdl;   // 1: launch with the programmatic-serialization attribute (llm_set_pdl)
+// 1: the last kernel this library launched was the rotation kernel (rope_kv.cu).  The product on
+// CTA pairs honours it: it is then launched without the programmatic attribute, i.e. only after
+// the rotation kernel has finished.  A measurement once ran the sequence "rotation kernel of 2,048
+// rows, then directly the CTA-pair product as its programmatic dependent" (no model has it: the
+// attention kernel always comes between them) and it stopped making progress in two of three
+// tries, with no bounded wait having given up; reading the kernels did not show why.  The
+// sequence is therefore not launched that way by anyone, a part registered by a user included.
+extern int g_llm_after_rotation;
 
 // Launch a kernel that calls pdl_wait() itself.
 template <typename... KArgs, typename... Args>
 static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                              cudaStream_t stream, Args... args) {
+  g_llm_after_rotation = 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

@@ -2,6 +2,7 @@
 #include "common.cuh"
 
 int g_llm_pdl = 1;
+int g_llm_after_rotation = 0;
 LLM_EXPORT void llm_set_pdl(int on) { g_llm_pdl = on ? 1 : 0; }
 
 // x[t][:] = table[token[t]][:]   (residual stream is 32-bit in every mode)

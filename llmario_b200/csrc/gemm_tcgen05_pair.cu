@@ -337,7 +337,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, 
   }
   const int pairs = m_tiles * n_tiles < resident_pairs ? m_tiles * n_tiles : resident_pairs;
   cfg.gridDim = dim3(2 * pairs);
-  cfg.numAttrs = g_llm_pdl ? 2 : 1;
+  // directly behind the rotation kernel the pair kernel starts only when that kernel is done
+  cfg.numAttrs = (g_llm_pdl && !g_llm_after_rotation) ? 2 : 1;
+  g_llm_after_rotation = 0;
   return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, mc, T, N, K, half, m_tiles, n_tiles, status);
 }
 }  // namespace

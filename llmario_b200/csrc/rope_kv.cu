@@ -217,21 +217,28 @@ LLM_EXPORT int llm_qk_norm_rope_store(
   const int heads = Hq + (has_kv ? 2 * Hkv : 0);
   const int threads = 128;
   if (rows >= 256 && dtype == LLM_BF16 && hd == 128 && rot_dim == 128 && cos_sin && !clear_proj &&
-      !(proj_stride & 1) && !(((uintptr_t)proj | (uintptr_t)cos_sin) & 15))
-    return launch_pdl(qk_norm_rope_store_rows_kernel, dim3(rows, (heads + 15) / 16), threads, 0, stream, proj,
-                      proj_stride, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, page_stride, block_table,
-                      table_stride, row_slot, row_pos, q_norm_w, k_norm_w, (const float2*)cos_sin, Hq, Hkv,
-                      page_size, eps, has_kv, use_norm);
+      !(proj_stride & 1) && !(((uintptr_t)proj | (uintptr_t)cos_sin) & 15)) {
+    const int rc = launch_pdl(qk_norm_rope_store_rows_kernel, dim3(rows, (heads + 15) / 16), threads, 0, stream,
+                              proj, proj_stride, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, page_stride,
+                              block_table, table_stride, row_slot, row_pos, q_norm_w, k_norm_w,
+                              (const float2*)cos_sin, Hq, Hkv, page_size, eps, has_kv, use_norm);
+    g_llm_after_rotation = 1;      // (see common.cuh: a CTA-pair product behind this kernel waits for its end)
+    return rc;
+  }
   const dim3 blocks(rows, (heads + 3) / 4);
 #define ARGS proj, proj_stride, (TQ*)q_out, (TQ*)k_cache, (TQ*)v_cache, page_stride, block_table, \
   table_stride, row_slot, row_pos, q_norm_w, k_norm_w, inv_freq, (const float2*)cos_sin, attn_factor, \
   rows, Hq, Hkv, hd, rot_dim, page_size, eps, has_kv, use_norm, clear_proj
   if (dtype == LLM_F32) {
     typedef float TQ;
-    return launch_pdl(qk_norm_rope_store_kernel<float, float>, blocks, threads, 0, stream, ARGS);
+    const int rc = launch_pdl(qk_norm_rope_store_kernel<float, float>, blocks, threads, 0, stream, ARGS);
+    g_llm_after_rotation = 1;
+    return rc;
   } else if (dtype == LLM_BF16) {
     typedef bf16 TQ;
-    return launch_pdl(qk_norm_rope_store_kernel<bf16, bf16>, blocks, threads, 0, stream, ARGS);
+    const int rc = launch_pdl(qk_norm_rope_store_kernel<bf16, bf16>, blocks, threads, 0, stream, ARGS);
+    g_llm_after_rotation = 1;
+    return rc;
   }
 #undef ARGS
   return LLM_ERR_UNSUPPORTED;

@@ -18,9 +18,11 @@
 // tokens).  Temporary buffers come from a grow-only arena of this library; it grows only in steps
 // that run eagerly (a recorded step has run eagerly with the same sizes before).
 #include <math.h>
+#include <algorithm>
 #include <stdint.h>
 #include <string.h>
 
+#include <deque>
 #include <map>
 #include <vector>
 
@@ -78,6 +80,10 @@ int llm_attention_tcgen05(const void* q, void* out, int rows, const void* k_cach
                           long long page_stride, long long n_pages, const int* block_table, int table_stride,
                           const int* items, int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
                           int window, int persistent, int* status, cudaStream_t stream);
+int llm_kv_gather(const void* k_src, const void* v_src, long long src_page_stride, const int* block_table,
+                  int table_stride, int page_size, void* k_dst, void* v_dst, long long dst_page_stride,
+                  int dst_page_size, int Hkv, int hd, int dtype, const int* items, int n_items,
+                  int total_chunks, cudaStream_t stream);
 int llm_attention_tcgen05_x2(const void* q, void* out, int rows, const void* k_cache, const void* v_cache,
                              long long page_stride, long long n_pages, const int* block_table,
                              int table_stride, const int* items, int n_items, int Hq, int Hkv, int hd,
@@ -92,12 +98,19 @@ namespace {
 constexpr int SPLIT_K_MAX_ROWS = 256;       // up to here the q/k/v destination is kept at zero
 constexpr int DECODE_TMA_TILE = 64;         // keys of a tile of attention_decode_tma.cu
 constexpr int PERSISTENT_ATTENTION_MAX_KEYS = 6144;
+// Prompt portions over a cache with small pages: the request's keys and values are first
+// gathered into scratch pages of GATHER_PAGE positions when the portion has at least
+// GATHER_MIN_PAIRS (token, head of the group) pairs.  (The tcgen05 kernel reaches about twice the
+// rate with TMA boxes; the copy costs about as much as the attention of 90 / group tokens.)
+constexpr int GATHER_PAGE = 128;
+constexpr int GATHER_MIN_PAIRS = 512;
+int g_gather = 1;                           // 0: never gather (for measurements)
 int g_fuse_mode = 0;                        // 0: when few waves, 1: always, 2: never
 
 // how often the driver chose which kernel (llm_driver_counts; tests and statistics read them)
 enum Kind : int {
   K_NORM, K_GEMM_TCGEN05, K_GEMM_SIMT, K_ROPE_TABLE, K_ROPE_STORE, K_DECODE_FUSED, K_DECODE_TMA, K_DECODE,
-  K_FLASH, K_MERGE, K_TCGEN05, K_TCGEN05_X2, K_GENERIC, K_SILU_MUL, N_KINDS
+  K_FLASH, K_MERGE, K_TCGEN05, K_TCGEN05_X2, K_GENERIC, K_SILU_MUL, K_KV_GATHER, N_KINDS
 };
 long long g_counts[N_KINDS] = {};
 
@@ -126,7 +139,7 @@ bool tc_ok(const void* a, int a_dt, int lda, const void* w, int w_dt, int ldw, i
 // ------------------------------------------------------------------------------------------------
 enum BufId : int {
   B_H = 1, B_PROJ, B_ZPROJ /* + width */, B_Q, B_OUT, B_ACT, B_GATE_UP, B_PART_O, B_PART_ML, B_ROPE /* + k */,
-  B_ITEMS
+  B_ITEMS, B_GATHER
 };
 
 struct Buf { void* p = nullptr; size_t bytes = 0; };
@@ -167,8 +180,11 @@ struct Arena {
     bufs.clear();
     ++generation;
   }
-  // ints on the device holding `host[0..n)`, copied in stream order
-  int upload(const std::vector<int>& host, int** dev, cudaStream_t stream) {
+  // ints on the device holding `host[0..n)`, copied in stream order.  `index`: which upload of
+  // the step this is; each has a device buffer of its own, so that what an earlier upload of
+  // the step left stays valid (across steps the buffers are used again: the copy runs in stream
+  // order, after every kernel of the step before).
+  int upload(const std::vector<int>& host, int index, int** dev, cudaStream_t stream) {
     const int s = turn;
     turn = (turn + 1) % SLOTS;
     if (ev[s]) {
@@ -186,7 +202,7 @@ struct Arena {
     }
     memcpy(pinned[s], host.data(), host.size() * sizeof(int));
     void* d = nullptr;
-    int rc = get(B_ITEMS * 1000000LL + s, host.size() * sizeof(int), false, &d);
+    int rc = get(B_ITEMS * 1000000LL + index, host.size() * sizeof(int), false, &d);
     if (rc) return rc;
     cudaError_t e = cudaMemcpyAsync(d, pinned[s], host.size() * sizeof(int), cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return (int)e;
@@ -214,17 +230,58 @@ struct Plan {          // the rows of the step as work items for one (group, lar
   const int* small = nullptr;       // device quadruples (first row, tokens, slot, first position)
   const int* large = nullptr;
   const int* small_rows = nullptr;  // the rows of the small items, for the merge
+  std::vector<int> large_host;      // the large items as the host made them
 };
+
+// The large items of a plan split for a cache with small pages: requests whose portion is long
+// enough are read from gathered scratch pages, the others from the cache as it is.
+struct GatherPlan {
+  int group = 0, large_cap = 0, page_size = 0, window = 0;
+  int n_requests = 0, total_chunks = 0, scratch_pages = 0, table_stride = 0;
+  int n_gathered = 0, n_direct = 0;
+  const int* list = nullptr;        // device: n_requests x GatherItem
+  const int* table = nullptr;       // device: block table of the scratch pages, a row per request
+  const int* gathered = nullptr;    // device: items whose "slot" is the row of `table`
+  const int* direct = nullptr;      // device: items read from the cache itself
+};
+
+// What is made once per step and shared by its layers (and by calls that come one by one from
+// Python parts): work items and the tables of cosines and sines.  Keyed by the step's id.
+struct StepCache {
+  long long step_id = -1;
+  int uploads = 0;
+  std::deque<Plan> plans;
+  std::deque<GatherPlan> gathers;
+  std::map<const float*, float*> rope;     // inv_freq table -> cos/sin of this step's rows
+};
+
+StepCache& step_cache(long long step_id) {
+  static std::map<int, StepCache> per_device;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  StepCache& c = per_device[dev];
+  if (c.step_id != step_id || step_id < 0) {
+    c.plans.clear();
+    c.gathers.clear();
+    c.rope.clear();
+    c.uploads = 0;
+    c.step_id = step_id;
+  }
+  return c;
+}
 
 struct Run {
   const LlmStepDesc& st;
   cudaStream_t stream;
   Arena& ar;
   int launches = 0;
-  std::vector<Plan> plans;
-  std::map<const float*, float*> rope;     // inv_freq table -> cos/sin of this step's rows
+  std::deque<Plan>& plans;
+  std::deque<GatherPlan>& gathers;
+  std::map<const float*, float*>& rope;
+  int& uploads;
 
-  Run(const LlmStepDesc& s, cudaStream_t str) : st(s), stream(str), ar(arena()) {}
+  Run(const LlmStepDesc& s, cudaStream_t str, StepCache& c)
+      : st(s), stream(str), ar(arena()), plans(c.plans), gathers(c.gathers), rope(c.rope), uploads(c.uploads) {}
 
   int check(int rc, Kind kind) {
     if (rc == 0) {
@@ -292,12 +349,13 @@ struct Run {
       }
       p.n_small = (int)small.size() / 4;
       p.n_large = (int)large.size() / 4;
+      p.large_host = large;
       p.small_single = single;
       std::vector<int> flat(small);
       flat.insert(flat.end(), large.begin(), large.end());
       flat.insert(flat.end(), small_rows.begin(), small_rows.end());
       int* dev = nullptr;
-      int rc = ar.upload(flat, &dev, stream);
+      int rc = ar.upload(flat, uploads++, &dev, stream);
       if (rc) return rc;
       if (p.n_small) {
         p.small = dev;
@@ -307,6 +365,74 @@ struct Run {
     }
     plans.push_back(p);
     *out = &plans.back();
+    return 0;
+  }
+
+  // Split the large items of `plan` for a cache with pages of `ps` < 32 positions.
+  int gather_for(const Plan& plan, int ps, int window, const GatherPlan** out) {
+    for (const GatherPlan& g : gathers)
+      if (g.group == plan.group && g.large_cap == plan.large_cap && g.page_size == ps && g.window == window) {
+        *out = &g;
+        return 0;
+      }
+    GatherPlan g;
+    g.group = plan.group, g.large_cap = plan.large_cap, g.page_size = ps, g.window = window;
+    const int D = GATHER_PAGE;
+    // a request's items follow one another; its portion is theirs together
+    struct Req { int slot, pos0, pos1, first_item, n_items; };
+    std::vector<Req> reqs;
+    const std::vector<int>& L = plan.large_host;
+    for (int i = 0; i < plan.n_large; ++i) {
+      const int* it = &L[4 * i];
+      if (!reqs.empty() && reqs.back().slot == it[2] && reqs.back().pos1 == it[3])
+        reqs.back().pos1 += it[1], reqs.back().n_items += 1;
+      else
+        reqs.push_back(Req{it[2], it[3], it[3] + it[1], i, 1});
+    }
+    std::vector<int> list, table, gathered, direct;
+    int max_pages = 0;
+    for (const Req& r : reqs)
+      if ((r.pos1 - r.pos0) * plan.group >= GATHER_MIN_PAIRS) max_pages = std::max(max_pages, (r.pos1 + D - 1) / D);
+    g.table_stride = max_pages;
+    for (const Req& r : reqs) {
+      const bool take = (r.pos1 - r.pos0) * plan.group >= GATHER_MIN_PAIRS;
+      for (int i = r.first_item; i < r.first_item + r.n_items; ++i) {
+        const int* it = &L[4 * i];
+        if (take) gathered.insert(gathered.end(), {it[0], it[1], g.n_requests, it[3]});
+        else direct.insert(direct.end(), {it[0], it[1], it[2], it[3]});
+      }
+      if (!take) continue;
+      const int lo = window > 0 && r.pos0 + 1 > window ? r.pos0 + 1 - window : 0;
+      const int first_page = lo / D;                        // scratch page of the lowest key read
+      const int first_pos = first_page * D;
+      const int n_chunks = (r.pos1 - 1) / ps - first_pos / ps + 1;
+      list.insert(list.end(), {r.slot, first_pos, n_chunks, g.scratch_pages, lo, g.total_chunks});
+      for (int pi = 0; pi < max_pages; ++pi)
+        table.push_back(pi >= first_page && pi * D < r.pos1 ? g.scratch_pages + pi - first_page : -1);
+      g.scratch_pages += (r.pos1 - 1) / D - first_page + 1;
+      g.total_chunks += n_chunks;
+      ++g.n_requests;
+    }
+    g.n_gathered = (int)gathered.size() / 4;
+    g.n_direct = (int)direct.size() / 4;
+    if (g.n_requests) {
+      std::vector<int> flat(list);
+      const size_t o_table = flat.size();
+      flat.insert(flat.end(), table.begin(), table.end());
+      const size_t o_gathered = flat.size();
+      flat.insert(flat.end(), gathered.begin(), gathered.end());
+      const size_t o_direct = flat.size();
+      flat.insert(flat.end(), direct.begin(), direct.end());
+      int* dev = nullptr;
+      int rc = ar.upload(flat, uploads++, &dev, stream);
+      if (rc) return rc;
+      g.list = dev;
+      g.table = dev + o_table;
+      g.gathered = dev + o_gathered;
+      g.direct = g.n_direct ? dev + o_direct : nullptr;
+    }
+    gathers.push_back(g);
+    *out = &gathers.back();
     return 0;
   }
 
@@ -390,11 +516,41 @@ struct Run {
       return check(llm_attention_tcgen05_x2(q, out, st.rows, c.k, c.v, c.page_stride, c.n_pages,
                                             c.block_table, c.table_stride, plan->large, plan->n_large, Hq, Hkv,
                                             hd, ps, L.scale, window, st.status, stream), K_TCGEN05_X2);
-    if (plan->n_large && tc)
+    if (plan->n_large && tc) {
+      const int persistent = reach <= PERSISTENT_ATTENTION_MAX_KEYS ? 1 : 0;
+      const int* direct = plan->large;
+      int n_direct = plan->n_large;
+      if (g_gather && ps < 32 && GATHER_PAGE % ps == 0 && !plan->large_host.empty()) {
+        // pages too small for TMA boxes: long portions read gathered copies of their requests' keys
+        const GatherPlan* gp = nullptr;
+        rc = gather_for(*plan, ps, window, &gp);
+        if (rc) return rc;
+        if (gp->n_requests) {
+          const int D = GATHER_PAGE;
+          const long long stride = 2LL * Hkv * D * hd;
+          void* scratch = nullptr;
+          rc = buffer(B_GATHER, (size_t)gp->scratch_pages * stride * 2, &scratch);
+          if (rc) return rc;
+          bf16* ks = (bf16*)scratch;
+          bf16* vs = ks + (size_t)Hkv * D * hd;
+          rc = check(llm_kv_gather(c.k, c.v, c.page_stride, c.block_table, c.table_stride, ps, ks, vs, stride, D,
+                                   Hkv, hd, LLM_BF16, gp->list, gp->n_requests, gp->total_chunks, stream),
+                     K_KV_GATHER);
+          if (rc) return rc;
+          rc = check(llm_attention_tcgen05(q, out, st.rows, ks, vs, stride, gp->scratch_pages, gp->table,
+                                           gp->table_stride, gp->gathered, gp->n_gathered, Hq, Hkv, hd, D, L.scale,
+                                           window, persistent, st.status, stream), K_TCGEN05);
+          if (rc) return rc;
+          direct = gp->direct;
+          n_direct = gp->n_direct;
+        }
+      }
+      if (n_direct == 0) return 0;
       return check(llm_attention_tcgen05(q, out, st.rows, c.k, c.v, c.page_stride,
                                          c.storage != nullptr ? c.n_pages : 0, c.block_table, c.table_stride,
-                                         plan->large, plan->n_large, Hq, Hkv, hd, ps, L.scale, window,
-                                         reach <= PERSISTENT_ATTENTION_MAX_KEYS ? 1 : 0, st.status, stream), K_TCGEN05);
+                                         direct, n_direct, Hq, Hkv, hd, ps, L.scale, window, persistent,
+                                         st.status, stream), K_TCGEN05);
+    }
     if (plan->n_large)
       return check(llm_attention_flash(q, out, nullptr, nullptr, c.k, c.v, c.page_stride, c.block_table,
                                        c.table_stride, plan->large, nullptr, nullptr, plan->n_large, 64, Hq,
@@ -560,9 +716,25 @@ LLM_EXPORT int llm_run_layers(const LlmLayerDesc* layers, const LlmCallDesc* cal
   if (n_launches) *n_launches = 0;
   if (n_calls <= 0 || step->rows <= 0) return 0;
   if (!step->all_single && (step->segments == nullptr || step->n_segments <= 0)) return LLM_ERR_ARGUMENT;
-  Run run(*step, stream);
+  Run run(*step, stream, step_cache(step->step_id));
   int rc = 0;
   for (int i = 0; i < n_calls && rc == 0; ++i) rc = run.layer(layers[calls[i].layer], calls[i]);
   if (n_launches) *n_launches = run.launches;
   return rc;
 }
+
+// The attention of one layer call by itself, for mixers that are driven from Python: q and out
+// [rows][heads * head_dim] in the step's dtype; of `layer` only the sizes, the scale and the window
+// are read.  The same choices as inside llm_run_layers.
+LLM_EXPORT int llm_attention_step(const LlmLayerDesc* layer, const LlmCallDesc* call, const LlmStepDesc* step,
+                                  const void* q, void* out, int* n_launches, cudaStream_t stream) {
+  if (n_launches) *n_launches = 0;
+  if (step->rows <= 0) return 0;
+  if (!step->all_single && (step->segments == nullptr || step->n_segments <= 0)) return LLM_ERR_ARGUMENT;
+  Run run(*step, stream, step_cache(step->step_id));
+  const int rc = run.attention(*layer, *call, q, out);
+  if (n_launches) *n_launches = run.launches;
+  return rc;
+}
+
+LLM_EXPORT void llm_set_gather(int on) { g_gather = on ? 1 : 0; }

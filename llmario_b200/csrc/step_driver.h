@@ -52,6 +52,7 @@ struct LlmStepDesc {
   int all_single;          // every request of the step has one row
   int dtype;               // dtype of activations between parts
   int pad_;
+  long long step_id;       // names the step: what is made once per step is kept under it (-1: keep nothing)
   const int* segments;     // host: n_segments x (first row, rows, request slot, first position)
   const int* tokens;       // device int32 [rows]
   const int* row_pos;
@@ -67,6 +68,9 @@ void llm_set_fuse_decode(int mode);
 int llm_driver_counts(long long* out, int cap);
 long long llm_arena_generation();
 int llm_arena_drop();
+int llm_attention_step(const LlmLayerDesc* layer, const LlmCallDesc* call, const LlmStepDesc* step,
+                       const void* q, void* out, int* n_launches, cudaStream_t stream);
+void llm_set_gather(int on);
 int llm_run_layers(const LlmLayerDesc* layers, const LlmCallDesc* calls, int n_calls,
                    const LlmStepDesc* step, int* n_launches, cudaStream_t stream);
 }

@@ -1,111 +1,29 @@
-"""Python face of the native step driver (``csrc/step_driver.cu``).
+"""Whole standard blocks described to the native step driver.
 
 The model is still put together from parts in Python: the registry, the run order and parts
 that a user registers stay as they are.  But the blocks that are the standard arrangement of the
 standard parts (pre-norm residual block, RMS norms, grouped-query attention with optional
-per-head norms and half-split rotation, gated feed-forward) are described once to the native
-driver, and a step runs every maximal run of such blocks with one call instead of some eight
-launches per layer issued from Python.  The driver applies the same dispatch rules as
-``llmario_b200.kernels`` (a test holds them to the same answers), so both ways give the same
-launches; blocks it does not know run through their own ``forward``.
+per-head norms and half-split rotation, gated feed-forward) are described once to the driver
+(``csrc/step_driver.cu``), and a step runs every maximal run of such blocks with one call instead
+of some eight launches per layer issued from Python.  Blocks the driver does not know run through
+their own ``forward``.
 """
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_float, c_int, c_longlong, c_void_p
-from typing import Dict, List, Optional, Sequence, Tuple
+from ctypes import POINTER, c_int
+from typing import Dict, Optional, Tuple
 
-import numpy as np
 import torch
 
-from .. import kernels
+from .. import driver, kernels
+from ..driver import (CallDesc, LayerDesc, StepDesc, arena_drop, arena_generation,  # noqa: F401
+                      kernel_counts, policies)
 from ..parts.attention import Attention
 from ..parts.block import PreNormResidualBlock
 from ..parts.feed_forward import SwiGLU
 from ..parts.norm import RmsNorm
 from ..parts.position import RotaryHalfSplit
-
-
-class LayerDesc(Structure):
-    _fields_ = [("hidden", c_int), ("num_heads", c_int), ("num_kv_heads", c_int),
-                ("head_dim", c_int), ("window", c_int), ("rot_dim", c_int),
-                ("intermediate", c_int), ("interleaved", c_int),
-                ("w_qkv_dtype", c_int), ("w_o_dtype", c_int), ("w_gate_up_dtype", c_int),
-                ("w_down_dtype", c_int),
-                ("scale", c_float), ("attn_factor", c_float), ("mixer_norm_eps", c_float),
-                ("ffn_norm_eps", c_float), ("qk_norm_eps", c_float), ("pad_", c_float),
-                ("mixer_norm_w", c_void_p), ("ffn_norm_w", c_void_p), ("q_norm_w", c_void_p),
-                ("k_norm_w", c_void_p), ("inv_freq", c_void_p), ("w_qkv", c_void_p),
-                ("w_o", c_void_p), ("w_gate_up", c_void_p), ("w_down", c_void_p)]
-
-
-class CallDesc(Structure):
-    _fields_ = [("layer", c_int), ("writes_cache", c_int), ("table_stride", c_int),
-                ("page_size", c_int), ("n_slots", c_int), ("slot", c_int),
-                ("page_stride", c_longlong), ("n_pages", c_longlong), ("k", c_void_p),
-                ("v", c_void_p), ("block_table", c_void_p), ("storage", c_void_p)]
-
-
-class StepDesc(Structure):
-    _fields_ = [("rows", c_int), ("max_pos", c_int), ("n_segments", c_int),
-                ("all_single", c_int), ("dtype", c_int), ("pad_", c_int),
-                ("segments", c_void_p), ("tokens", c_void_p), ("row_pos", c_void_p),
-                ("row_slot", c_void_p), ("x", c_void_p), ("status", c_void_p)]
-
-
-_declared = False
-
-
-def _lib():
-    global _declared
-    l = kernels.lib()
-    if not _declared:
-        l.llm_run_layers.argtypes = [POINTER(LayerDesc), POINTER(CallDesc), c_int,
-                                     POINTER(StepDesc), POINTER(c_int), c_void_p]
-        l.llm_run_layers.restype = c_int
-        l.llm_arena_generation.argtypes = []
-        l.llm_arena_generation.restype = c_longlong
-        l.llm_arena_drop.argtypes = []
-        l.llm_arena_drop.restype = c_int
-        for name, n in (("llm_token_tile", 1), ("llm_k_splits", 3), ("llm_decode_splits", 5)):
-            fn = getattr(l, name)
-            fn.argtypes, fn.restype = [c_int] * n, c_int
-        l.llm_set_fuse_decode.argtypes = [c_int]
-        l.llm_set_fuse_decode.restype = None
-        _declared = True
-    return l
-
-
-def arena_generation() -> int:
-    """Grows whenever a buffer of the driver's arena moves: recorded steps are stale then."""
-    return int(_lib().llm_arena_generation())
-
-
-def arena_drop() -> None:
-    """Forget the driver's buffers (after a failed step: one kept at zero may hold sums)."""
-    kernels._check(_lib().llm_arena_drop(), "arena_drop")
-    kernels.launches -= 1
-
-
-KINDS = ("norm", "gemm_tcgen05", "gemm_simt", "rope_table", "rope_store", "decode_fused",
-         "decode_tma", "decode", "flash", "merge", "tcgen05", "tcgen05_x2", "generic", "silu_mul")
-
-
-def kernel_counts() -> Dict[str, int]:
-    """How often the driver has launched which kind of kernel since the library was loaded."""
-    l = _lib()
-    l.llm_driver_counts.argtypes = [POINTER(c_longlong), c_int]
-    l.llm_driver_counts.restype = c_int
-    out = (c_longlong * len(KINDS))()
-    n = l.llm_driver_counts(out, len(KINDS))
-    assert n == len(KINDS), "the kinds of the driver and of this module differ"
-    return dict(zip(KINDS, out))
-
-
-def policies():
-    """The native statements of the dispatch policies: (token_tile, k_splits, decode_splits)."""
-    l = _lib()
-    return l.llm_token_tile, l.llm_k_splits, l.llm_decode_splits
 
 
 def describe_block(block, shared_tables: Dict[Tuple, torch.Tensor]) -> Optional[LayerDesc]:
@@ -174,16 +92,7 @@ class NativeLayers:
             if view is None:
                 self.native_call.append(False)
                 continue
-            c = self.calls[i]
-            c.layer, c.writes_cache = call.layer, int(call.writes_cache)
-            c.table_stride, c.page_size = view.block_table.stride(0), view.page_size
-            c.page_stride = view.page_stride
-            c.k, c.v, c.block_table = view.k.data_ptr(), view.v.data_ptr(), view.block_table.data_ptr()
-            st = view.storage
-            if st is not None and st.is_contiguous() and st.dim() == 6:
-                c.storage, c.n_pages, c.n_slots, c.slot = st.data_ptr(), st.shape[0], st.shape[1], view.slot
-            else:
-                c.storage, c.n_pages, c.n_slots, c.slot = None, 0, 0, 0
+            driver.fill_call(self.calls[i], call.layer, call.writes_cache, view)
             self.native_call.append(True)
         # maximal runs of native calls: [(first, count)], and which run starts at a given call
         self.runs: Dict[int, int] = {}
@@ -197,35 +106,16 @@ class NativeLayers:
                 i = j
             else:
                 i += 1
-        self._step = StepDesc()
+        self._step: Optional[StepDesc] = None
         self._launches = c_int(0)
-        self._lib = _lib()
-        self._status = kernels.status_words(model.device).data_ptr()
-        self._segments: Optional[np.ndarray] = None
+        self._lib = driver._lib()
 
     def any(self) -> bool:
         return bool(self.runs)
 
     def begin_step(self, ctx, x: torch.Tensor) -> None:
         """Describe the step once; every run of layers of the step uses the description."""
-        s = self._step
-        s.rows, s.max_pos = ctx.rows, ctx.max_pos
-        single = len(ctx.segments) == ctx.rows
-        s.all_single = int(single)
-        s.n_segments = len(ctx.segments)
-        if single:
-            s.segments = None
-        else:
-            seg = np.empty((len(ctx.segments), 4), dtype=np.int32)
-            for i, g in enumerate(ctx.segments):
-                seg[i] = (g.row_start, g.rows, g.slot, g.pos_start)
-            self._segments = seg                  # kept alive for the calls of this step
-            s.segments = seg.ctypes.data
-        s.dtype = kernels._DT[ctx.dtype]
-        s.tokens, s.row_pos, s.row_slot = ctx.tokens.data_ptr(), ctx.row_pos.data_ptr(), \
-            ctx.row_slot.data_ptr()
-        s.x = x.data_ptr()
-        s.status = self._status
+        self._step = driver.describe_step(ctx, x)
 
     def run(self, first: int, count: int) -> None:
         """Run-order entries ``first .. first + count`` on the step described last."""

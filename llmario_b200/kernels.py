@@ -602,17 +602,6 @@ def attention_tcgen05_x2(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tens
         _stream()), f"attention_tcgen05_x2 (head_dim {head_dim})")
 
 
-def prefill_x2_ok(view, head_dim: int, group: int) -> bool:
-    """Whether prompt portions can run two query tiles per CTA (keys and values by TMA)."""
-    ps = view.page_size
-    return (prefill_tcgen05_ok(view, head_dim, group) and ps >= 32 and ps & (ps - 1) == 0
-            and getattr(view, "storage", None) is not None)
-
-
-def prefill_tcgen05_ok(view, head_dim: int, group: int) -> bool:
-    return head_dim in (64, 128) and 128 % group == 0 and (view.page_stride * 2) % 16 == 0
-
-
 def decode_tma_ok(view, head_dim: int) -> bool:
     st = getattr(view, "storage", None)
     ps = view.page_size
@@ -723,66 +712,3 @@ def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int =
 
 DECODE_TMA_TILE = 64      # keys of a tile of attention_decode_tma.cu
 PERSISTENT_ATTENTION_MAX_KEYS = 6144
-
-
-def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
-              head_dim: int, scale: float, window: Optional[int]) -> None:
-    """Causal attention of every row of the step over its own request's cached keys.
-    bfloat16 with a head size the tensor-core kernels have: decode rows and very short portions
-    go to the decode kernel (keys split across CTAs), longer portions to the four-warp kernel.
-    Everything else (32-bit, other head sizes, very large groups) runs the generic kernel."""
-    group = num_heads // num_kv_heads
-    if q.dtype != torch.bfloat16 or head_dim not in FLASH_HEAD_DIMS or group > 16:
-        attention_generic(q, out, view.k, view.v, view.page_stride, view.block_table,
-                          ctx.row_slot, ctx.row_pos, num_heads, num_kv_heads, head_dim,
-                          view.page_size, scale, window)
-        return
-    tc = prefill_tcgen05_ok(view, head_dim, group)
-    # Two query tiles per CTA halve the TMA copies of keys and values: that pays where the copies
-    # bind (pages of 32) and there are CTAs enough to fill the GPU several times over.  With
-    # pages of 64 and more the one-tile kernel, two softmax threads to a row, is as fast or faster.
-    x2 = (tc and prefill_x2_ok(view, head_dim, group) and view.page_size < 64
-          and ctx.rows * num_kv_heads >= 4 * sm_count() * (128 // group))
-    plan = ctx.attention_plan(group, (256 if x2 else 128 if tc else 64) // group)
-    common = (view.k, view.v, view.page_stride, view.block_table)
-    if plan.n_small:
-        reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
-        tma = group <= 8 and decode_tma_ok(view, head_dim)
-        splits = decode_splits(plan.n_small, num_kv_heads, reach, (3 if tma else 6) * sm_count(),
-                               DECODE_TMA_TILE if tma else 32) if plan.small_single else 1
-        part_o = part_ml = None
-        if splits > 1:
-            part_o = ctx.buffer("attn.part_o", (ctx.rows * num_heads * splits * head_dim,),
-                                torch.float32)
-            part_ml = ctx.buffer("attn.part_ml", (ctx.rows * num_heads * splits * 2,),
-                                 torch.float32)
-        if tma:
-            attention_decode_tma(q, out, view.storage, view.slot, view.block_table, plan.small,
-                                 plan.n_small, num_heads, num_kv_heads, head_dim, view.page_size,
-                                 scale, window, splits, part_o, part_ml, ctx.row_slot, ctx.row_pos)
-        elif group <= 8:    # at most eight (token, head) pairs per item: keys on the M side
-            attention_decode(q, out, *common, plan.small, plan.n_small, num_heads, num_kv_heads,
-                             head_dim, view.page_size, scale, window, splits, part_o, part_ml,
-                             ctx.row_slot, ctx.row_pos)
-        else:
-            attention_flash(q, out, *common, plan.small, plan.n_small, 16, num_heads,
-                            num_kv_heads, head_dim, view.page_size, scale, window, splits,
-                            part_o, part_ml, ctx.row_slot, ctx.row_pos)
-        if splits > 1:
-            attention_merge(part_o, part_ml, out, plan.small_rows, plan.n_small, num_heads,
-                            head_dim, splits)
-    if plan.n_large and x2:
-        attention_tcgen05_x2(q, out, *common, plan.large, plan.n_large, num_heads, num_kv_heads,
-                             head_dim, view.page_size, scale, window, view.storage.shape[0])
-    elif plan.n_large and tc:
-        storage = getattr(view, "storage", None)
-        # one persistent CTA per SM saves about 3 us per (item, KV head) pair; with long items
-        # (positions beyond some 6,000) that is little and the fixed deal of pairs costs more
-        reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
-        attention_tcgen05(q, out, *common, plan.large, plan.n_large, num_heads, num_kv_heads,
-                          head_dim, view.page_size, scale, window,
-                          storage.shape[0] if storage is not None else 0,
-                          persistent=reach <= PERSISTENT_ATTENTION_MAX_KEYS)
-    elif plan.n_large:
-        attention_flash(q, out, *common, plan.large, plan.n_large, 64, num_heads, num_kv_heads,
-                        head_dim, view.page_size, scale, window)

@@ -12,7 +12,7 @@ from typing import Dict, Optional
 
 import torch
 
-from .. import kernels
+from .. import driver, kernels
 from ..cache import PagedKV
 from ..config.spec import ConfigError, PartSpec
 from .base import BoundCall, StepContext, build_part, register_part, tensor_of
@@ -96,8 +96,8 @@ class Attention:
             inv_freq, attn_factor, self.num_heads, self.num_kv_heads, self.head_dim, rot_dim,
             view.page_size, self.q_norm.eps if self.q_norm is not None else 0.0, angles,
             clear_proj=kept_zero)
-        kernels.attention(ctx, q, out, view, self.num_heads, self.num_kv_heads, self.head_dim,
-                          self.scale, self.window)
+        driver.attention(ctx, q, out, view, self.num_heads, self.num_kv_heads, self.head_dim,
+                         self.scale, self.window)
         self.o_proj(out, x, accumulate=True)
 
 

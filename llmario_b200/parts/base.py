@@ -115,21 +115,6 @@ class Workspace:
 
 
 @dataclass
-class AttentionPlan:
-    """The rows of a step cut into work items for the attention kernels of one group size:
-    ``small`` items fit one warp (tokens * group <= 16), ``large`` ones four warps.  Tensors
-    hold int32 quadruples (first row, tokens, request slot, first position); ``small`` is None
-    when every row of the step is a small item of its own (a pure decode step)."""
-
-    n_small: int = 0
-    n_large: int = 0
-    small: Optional[torch.Tensor] = None
-    large: Optional[torch.Tensor] = None
-    small_rows: Optional[torch.Tensor] = None   # the rows of the small items, for the merge
-    small_single: bool = False                  # every small item is one token
-
-
-@dataclass
 class StepContext:
     """Everything a part may read about the running step."""
 
@@ -145,44 +130,11 @@ class StepContext:
     fresh_slots: Sequence[int] = ()   # request slots opened since the last step
     max_pos: int = 0               # largest position in this step
 
-    plans: Dict[Any, AttentionPlan] = field(default_factory=dict)
     shared: Dict[Any, Any] = field(default_factory=dict)   # what parts compute once per step
 
     def buffer(self, name: str, shape: Sequence[int], dtype: Optional[torch.dtype] = None,
                zero: bool = False) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype or self.dtype, zero)
-
-    def attention_plan(self, group: int, large_cap: Optional[int] = None) -> AttentionPlan:
-        """Work items for attention kernels whose CTAs hold ``group`` query heads per token:
-        small items have at most 8 (token, head) pairs (16 for a group above 8), large ones at
-        most ``large_cap`` tokens (default: 64 pairs)."""
-        large_cap = max(1, large_cap or 64 // group)
-        plan = self.plans.get((group, large_cap))
-        if plan is not None:
-            return plan
-        small_cap = max(1, (8 if group <= 8 else 16) // group)
-        if all(s.rows == 1 for s in self.segments):
-            plan = AttentionPlan(n_small=self.rows, small_single=True)   # rows describe themselves
-        else:
-            small, large = [], []
-            for s in self.segments:
-                if s.rows <= small_cap:
-                    small.append((s.row_start, s.rows, s.slot, s.pos_start))
-                else:
-                    for at in range(0, s.rows, large_cap):
-                        n = min(large_cap, s.rows - at)
-                        large.append((s.row_start + at, n, s.slot, s.pos_start + at))
-            plan = AttentionPlan(n_small=len(small), n_large=len(large),
-                                 small_single=all(i[1] == 1 for i in small))
-            flat = [v for item in small + large for v in item] + [i[0] for i in small]
-            dev = torch.tensor(flat, dtype=torch.int32).to(self.device, non_blocking=True)
-            if small:
-                plan.small = dev[:4 * len(small)]
-                plan.small_rows = dev[4 * (len(small) + len(large)):]
-            if large:
-                plan.large = dev[4 * len(small):4 * (len(small) + len(large))]
-        self.plans[(group, large_cap)] = plan
-        return plan
 
 
 @dataclass

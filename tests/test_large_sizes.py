@@ -84,43 +84,3 @@ def test_benchmark_sizes_bfloat16_against_float32(models):
         for g in (got[r], got_cut[r]):
             assert np.isfinite(g).all()
             assert np.abs(g - ref[r]).max() <= 5e-2 * scale, (r, np.abs(g - ref[r]).max(), scale)
-
-
-def test_long_portion_with_two_query_tiles_per_cta(models, monkeypatch):
-    """A prompt portion long enough for the attention kernel with two query tiles per CTA
-    (pages of 32 positions, where it is chosen), against the same step with the one-tile kernel: logits at several
-    places of the portion and a portion that continues a request."""
-    from llmario_b200 import kernels
-    from llmario_b200.engine import ModelRunner, StepEntry
-
-    m16, _ = models
-    rng = random.Random(2)
-    vocab = m16.vocab_size
-    toks = [rng.randrange(vocab) for _ in range(2600 + 2500)]
-    want = [0, 63, 64, 1000, 2599]
-    calls = {"x2": 0}
-    real = kernels.attention_tcgen05_x2
-
-    def counted(*a, **k):
-        calls["x2"] += 1
-        return real(*a, **k)
-
-    def run(two_tiles):
-        if not two_tiles:
-            monkeypatch.setattr(kernels, "prefill_x2_ok", lambda *a: False)
-        monkeypatch.setattr(kernels, "attention_tcgen05_x2", counted)
-        # (driven from Python, so that the choice of kernel can be overridden from here)
-        runner = ModelRunner(m16, page_size=32, cache_tokens=8192, max_requests=2,
-                             max_context=8192, token_budget=4096, use_native=False)
-        a = runner.step([StepEntry("r", toks[:2600], want)]).float().cpu().numpy()
-        b = runner.step([StepEntry("r", toks[2600:], [0, 1234, 2499])]).float().cpu().numpy()
-        kernels.check_tc_status(DEV)
-        monkeypatch.undo()
-        return np.concatenate([a, b])
-
-    got = run(True)
-    assert calls["x2"] >= 4            # both steps, both layers
-    ref = run(False)
-    assert calls["x2"] >= 4 and np.isfinite(got).all()
-    scale = np.abs(ref).max()
-    assert np.abs(got - ref).max() <= 0.03 * scale, np.abs(got - ref).max() / scale

@@ -136,3 +136,70 @@ def test_generation_with_many_requests_at_benchmark_widths(lookahead):
             top = np.sort(l)[-2:]
             if top[1] - top[0] > 3e-2 * max(1.0, float(np.abs(l).max())):
                 assert tok == int(np.argmax(l)), (i, j, tok, int(np.argmax(l)))
+
+
+def test_long_portion_with_two_query_tiles_per_cta():
+    """A prompt portion long enough for the attention kernel with two query tiles per CTA (pages
+    of 32 positions, where the driver chooses it), then a portion that continues the request
+    with the one-tile kernel: logits at several places against the plain implementation."""
+    from llmario_b200 import kernels
+    from llmario_b200.engine import Model, ModelRunner, StepEntry, native
+
+    toks = random_tokens(NAME, 2400 + 150, 77)
+    want = [0, 63, 64, 1000, 2047, 2399]
+    model = Model.from_folder(model_dir(NAME, "bfloat16"), "bfloat16", DEV)
+    runner = ModelRunner(model, page_size=32, cache_tokens=4096, max_requests=2, max_context=4096,
+                         token_budget=4096)
+    before = native.kernel_counts()
+    a = runner.step([StepEntry("r", toks[:2400], want)]).float().cpu().numpy()
+    mid = native.kernel_counts()
+    b = runner.step([StepEntry("r", toks[2400:], [0, 77, 149])]).float().cpu().numpy()
+    after = native.kernel_counts()
+    kernels.check_tc_status(DEV)
+    assert mid["tcgen05_x2"] - before["tcgen05_x2"] == 2           # both layers
+    assert after["tcgen05_x2"] == mid["tcgen05_x2"] and after["tcgen05"] - mid["tcgen05"] == 2
+    ref = plain_logits(NAME, "bfloat16", toks)
+    assert_close(a, ref[want], "bfloat16", "two query tiles per CTA", NAME)
+    assert_close(b, ref[[2400, 2477, 2549]], "bfloat16", "continued with one tile", NAME)
+
+
+@pytest.mark.parametrize("page", [8, 16])
+def test_long_portions_over_small_pages_read_gathered_keys(page):
+    """With pages too small for TMA boxes, portions of many tokens read a gathered copy of
+    their requests' keys and values; short portions in the same step read the cache as it is.
+    A request is cut into portions so that later portions gather what earlier steps wrote;
+    against the plain implementation, and against the same steps without gathering."""
+    from llmario_b200 import driver, kernels
+    from llmario_b200.engine import Model, ModelRunner, StepEntry, native
+
+    reqs = {"a": random_tokens(NAME, 700, 31), "b": random_tokens(NAME, 333, 32),
+            "c": random_tokens(NAME, 60, 33)}
+    plan = [[("a", 0, 300), ("c", 0, 40)], [("a", 300, 200), ("b", 0, 333), ("c", 40, 1)],
+            [("a", 500, 200), ("c", 41, 19)]]
+    model = Model.from_folder(model_dir(NAME, "bfloat16"), "bfloat16", DEV)
+    outs = {}
+    for gather in (True, False):
+        driver.use_gather(gather)
+        try:
+            runner = ModelRunner(model, page_size=page, cache_tokens=2048, max_requests=4,
+                                 max_context=1024, token_budget=1024)
+            before = native.kernel_counts()
+            got = {r: [] for r in reqs}
+            for step in plan:
+                res = runner.step([StepEntry(r, reqs[r][s:s + n], list(range(n)))
+                                   for r, s, n in step]).float().cpu().numpy()
+                at = 0
+                for r, s, n in step:
+                    got[r].append(res[at:at + n])
+                    at += n
+            kernels.check_tc_status(DEV)
+            after = native.kernel_counts()
+            # two layers, three steps; portions of 128 tokens or more are gathered
+            assert (after["kv_gather"] - before["kv_gather"] == 6) == gather
+            outs[gather] = {r: np.concatenate(v) for r, v in got.items()}
+        finally:
+            driver.use_gather(True)
+    for r, toks in reqs.items():
+        ref = plain_logits(NAME, "bfloat16", toks)
+        assert_close(outs[True][r], ref, "bfloat16", f"gathered keys, pages of {page}, {r}", NAME)
+        assert_close(outs[False][r], ref, "bfloat16", f"cache as it is, pages of {page}, {r}", NAME)
