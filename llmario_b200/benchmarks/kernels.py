@@ -3,6 +3,8 @@
     python -m llmario_b200.benchmarks.kernels gemm --rows 8 --out 24576 --in 4096 --mode gated
     python -m llmario_b200.benchmarks.kernels attention --batch 8 --context 1024
     python -m llmario_b200.benchmarks.kernels prefill-attention --tokens 2048
+    python -m llmario_b200.benchmarks.kernels step --batch 8 --context 1024
+    python -m llmario_b200.benchmarks.kernels prompt-step --tokens 2048 --layers 4
 
 Between timed launches a buffer larger than the L2 cache is overwritten unless ``--no-flush`` is
 given.  Prints the median time, the bytes or flops it stands for, and the rate.
@@ -184,6 +186,39 @@ def cmd_step(a) -> None:
           f"batch={a.batch} context={a.context}: {start.elapsed_time(end) / a.steps * 1e3:.1f} us/step")
 
 
+def cmd_prompt_step(a) -> None:
+    """One prompt of ``--tokens`` tokens in one step, ``--steps`` times, between
+    cudaProfilerStart and cudaProfilerStop (for a list of the kernels a prompt step launches)."""
+    import random
+
+    from ..cli import preset_config
+    from ..engine import Model, ModelRunner, StepEntry
+
+    model = Model.random(preset_config(a.model, a.layers), 0, "bfloat16", DEV)
+    runner = ModelRunner(model, page_size=a.page_size, cache_tokens=a.tokens + 256, max_requests=2,
+                         max_context=max(8192, a.tokens + 256), token_budget=a.tokens)
+    rng, vocab = random.Random(0), model.vocab_size
+
+    def prompt(i):
+        runner.step([StepEntry(i, [rng.randrange(vocab) for _ in range(a.tokens)], [a.tokens - 1])])
+        runner.close(i)
+
+    for i in range(2):
+        prompt(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
+    start.record()
+    for i in range(a.steps):
+        prompt(10 + i)
+    end.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    kernels.check_tc_status(DEV)
+    print(f"prompt step {a.model} layers={len(model.blocks)} tokens={a.tokens} "
+          f"pages of {a.page_size}: {start.elapsed_time(end) / a.steps * 1e3:.1f} us/step")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -234,6 +269,13 @@ def main(argv=None) -> int:
     st.add_argument("--page-size", type=int, default=16)
     st.add_argument("--eager", action="store_true", help="no CUDA graphs")
     st.set_defaults(fn=cmd_step)
+    ps = sub.add_parser("prompt-step")
+    ps.add_argument("--model", default="qwen3-8b")
+    ps.add_argument("--layers", type=int, default=None)
+    ps.add_argument("--tokens", type=int, default=2048)
+    ps.add_argument("--steps", type=int, default=2)
+    ps.add_argument("--page-size", type=int, default=16)
+    ps.set_defaults(fn=cmd_prompt_step)
     for s in (g, d, p):
         s.add_argument("--reps", type=int, default=20)
         s.add_argument("--no-flush", action="store_true")

@@ -22,6 +22,8 @@
 // turn) meets it before tensor memory is freed.  No load is multicast.
 #include "tcgen05.cuh"
 
+extern int g_llm_pair_ksplits;
+
 namespace {
 
 constexpr int BN = 256;          // tokens per pair tile
@@ -113,7 +115,7 @@ template <int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(192, 1) gemm_pair_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     const __grid_constant__ CUtensorMap map_c, int T, int N, int K, int half, int m_tiles, int n_tiles,
-    int* __restrict__ status) {
+    int ksplits, int* __restrict__ status) {
   constexpr int FEAT = EPI == EPI_GATED ? 64 : TILE_M;     // output features of this CTA per tile
   extern __shared__ uint8_t raw[];
   auto& sm = *reinterpret_cast<PairStorage<STAGES, FEAT, TC>*>(
@@ -125,6 +127,9 @@ __global__ void __launch_bounds__(192, 1) gemm_pair_kernel(
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int nkb = (K + TILE_K - 1) / TILE_K;
   const int tiles = m_tiles * n_tiles;
+  // A work item is a tile and one of `ksplits` ranges of K (more than one only with the adding
+  // epilogue, whose partial sums meet in memory): item w is tile w % tiles, range w / tiles.
+  const int works = tiles * ksplits;
   constexpr uint32_t STAGE_BYTES = TILE_M * TILE_K * 2 + HALF_N * TILE_K * 2;
   // float32 accumulator, bf16 A and B, both K-major, N = 256, M = 256 over the pair
   constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
@@ -168,22 +173,24 @@ __global__ void __launch_bounds__(192, 1) gemm_pair_kernel(
     long long it = 0;
     bool ok = true;
     bool first = true;
-    for (int tile = pair; tile < tiles && ok; tile += n_pairs) {
+    for (int work = pair; work < works && ok; work += n_pairs) {
+      const int tile = work % tiles, ks = work / tiles;
+      const int kb0 = (int)((long long)ks * nkb / ksplits), kb1 = (int)((long long)(ks + 1) * nkb / ksplits);
       const int f0 = (tile / n_tiles) * (2 * FEAT) + (int)rank * FEAT;      // first output feature
       const int row0 = EPI == EPI_GATED ? 2 * f0 : f0;                      // first weight row
       const int t0 = (tile % n_tiles) * BN + (int)rank * HALF_N;
-      int kb = 0;
+      int kb = kb0;
       if (first) {
         // weights do not depend on earlier kernels: fetch a ring of them before waiting
-        const int head = min(nkb, STAGES);
-        for (int i = 0; i < head; ++i) load_w(i, row0, i * TILE_K);
+        const int head = min(kb1 - kb0, STAGES);
+        for (int i = 0; i < head; ++i) load_w(i, row0, (kb0 + i) * TILE_K);
         pdl_wait();
-        for (int i = 0; i < head; ++i) tma_load_2d_pair(sm.b[i], &map_x, i * TILE_K, t0, full_addr[i]);
+        for (int i = 0; i < head; ++i) tma_load_2d_pair(sm.b[i], &map_x, (kb0 + i) * TILE_K, t0, full_addr[i]);
         it = head;
-        kb = head;
+        kb = kb0 + head;
         first = false;
       }
-      for (; kb < nkb; ++kb, ++it) {
+      for (; kb < kb1; ++kb, ++it) {
         const int s = (int)(it % STAGES);
         ok = mbar_wait_pair(&sm.empty[s], (uint32_t)((it / STAGES) & 1) ^ 1);
         if (!ok) { atomicExch(status, 1); sm.dead = 1; break; }
@@ -198,13 +205,15 @@ __global__ void __launch_bounds__(192, 1) gemm_pair_kernel(
     long long it = 0;
     int local = 0;
     bool ok = true;
-    for (int tile = pair; tile < tiles && ok; tile += n_pairs, ++local) {
+    for (int work = pair; work < works && ok; work += n_pairs, ++local) {
+      const int ks = work / tiles;
+      const int kb0 = (int)((long long)ks * nkb / ksplits), kb1 = (int)((long long)(ks + 1) * nkb / ksplits);
       const int buf = local & 1;
       ok = mbar_wait_pair(&sm.acc_empty[buf], (uint32_t)((local >> 1) & 1) ^ 1);
       if (!ok) { atomicExch(status, 2); sm.dead = 1; break; }
       tc_fence_after();
       const uint32_t acc = tmem + (uint32_t)buf * BN;
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = (int)(it % STAGES);
         ok = mbar_wait_pair(&sm.full[s], (uint32_t)((it / STAGES) & 1));
         if (!ok) { atomicExch(status, 2); sm.dead = 1; break; }
@@ -214,7 +223,7 @@ __global__ void __launch_bounds__(192, 1) gemm_pair_kernel(
 #pragma unroll
         for (int k = 0; k < TILE_K / UMMA_K; ++k)
           pair_mma(acc, da + (uint64_t)(k * UMMA_K * 2 >> 4), db + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
-                   (kb > 0 || k > 0) ? 1u : 0u);
+                   (kb > kb0 || k > 0) ? 1u : 0u);
         pair_commit(&sm.empty[s]);
       }
       if (ok) pair_commit(&sm.acc_full[buf]);
@@ -227,7 +236,8 @@ __global__ void __launch_bounds__(192, 1) gemm_pair_kernel(
     pdl_wait();
     int local = 0;
     int chunk_no = 0;
-    for (int tile = pair; tile < tiles; tile += n_pairs, ++local) {
+    for (int work = pair; work < works; work += n_pairs, ++local) {
+      const int tile = work % tiles;
       const int n0 = (tile / n_tiles) * (2 * FEAT) + (int)rank * FEAT, t0 = (tile % n_tiles) * BN;
       const int buf = local & 1;
       bool ok = mbar_wait_pair(&sm.acc_full[buf], (uint32_t)((local >> 1) & 1));
@@ -335,12 +345,29 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, 
     }
     resident_pairs = n < sm_count / 2 ? n : sm_count / 2;
   }
-  const int pairs = m_tiles * n_tiles < resident_pairs ? m_tiles * n_tiles : resident_pairs;
+  // The adding epilogue lets K be cut.  With few tiles to a pair the last round of tiles leaves
+  // most pairs idle (160 tiles on 74 pairs: three rounds for the work of 2.2), and with fewer
+  // tiles than pairs some never work.  A work item costs its 64-wide blocks of K plus about six
+  // blocks' worth of start and epilogue (fitted to measured times of seven shapes); K is cut into
+  // the number of ranges, each of at least eight blocks, for which the rounds cost least.
+  int ksplits = 1;
+  if (EPI == EPI_ACCUM) {
+    const int tiles = m_tiles * n_tiles, nkb = (K + TILE_K - 1) / TILE_K;
+    double best = 0;
+    for (int s = 1; s <= 8 && nkb / s >= 8; ++s) {
+      const int rounds = (tiles * s + resident_pairs - 1) / resident_pairs;
+      const double cost = rounds * ((double)nkb / s + 6.0);
+      if (s == 1 || cost < best * 0.99) best = cost, ksplits = s;
+    }
+    if (g_llm_pair_ksplits > 0 && nkb / g_llm_pair_ksplits >= 1) ksplits = g_llm_pair_ksplits;
+  }
+  const int works = m_tiles * n_tiles * ksplits;
+  const int pairs = works < resident_pairs ? works : resident_pairs;
   cfg.gridDim = dim3(2 * pairs);
   // directly behind the rotation kernel the pair kernel starts only when that kernel is done
   cfg.numAttrs = (g_llm_pdl && !g_llm_after_rotation) ? 2 : 1;
   g_llm_after_rotation = 0;
-  return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, mc, T, N, K, half, m_tiles, n_tiles, status);
+  return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, mc, T, N, K, half, m_tiles, n_tiles, ksplits, status);
 }
 }  // namespace
 
@@ -348,6 +375,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, 
 // split; the gated form only with interleaved rows).  Returns LLM_ERR_UNSUPPORTED when the output
 // cannot be written by TMA or the mode is not one of these: the caller then uses the one-CTA kernel.
 int g_llm_pair = 1;   // 0: the dispatcher keeps to the one-CTA kernels (for comparisons)
+int g_llm_pair_ksplits = 0;   // > 0: this many ranges of K in the adding epilogue (for measurements)
+LLM_EXPORT void llm_set_pair_ksplits(int n) { g_llm_pair_ksplits = n; }
 LLM_EXPORT void llm_set_pair(int on) { g_llm_pair = on ? 1 : 0; }
 
 int llm_gemm_tcgen05_pair(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K, int lda,
