@@ -420,10 +420,14 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* X, const void* W, void* C, int c_dty
     // many rows: the persistent kernels (tiles of 256 tokens, epilogue overlapped with the next
     // tile), on CTA pairs where that form exists; if the output cannot be written by TMA, the
     // one-tile kernel with 128 tokens
-    if (splits == 1) {
+    // (the pair kernel cuts K itself where its adding epilogue allows, so it also takes the
+    // products for which the caller asked for a split)
+    if (splits == 1 || mode == 1) {
       int r = llm_gemm_tcgen05_pair(X, W, C, c_dtype, T, N, K, lda, ldw, ldc, mode, half, status, stream);
       if (r != LLM_ERR_UNSUPPORTED) return r;
-      r = llm_gemm_tcgen05_persistent(X, W, C, c_dtype, T, N, K, lda, ldw, ldc, mode, half, status, stream);
+    }
+    if (splits == 1) {
+      int r = llm_gemm_tcgen05_persistent(X, W, C, c_dtype, T, N, K, lda, ldw, ldc, mode, half, status, stream);
       if (r != LLM_ERR_UNSUPPORTED) return r;
     }
     bn = 128;

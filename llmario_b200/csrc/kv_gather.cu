@@ -15,14 +15,17 @@
 
 namespace {
 // One request to gather: its chunks are the source pages from position `first_pos` (a multiple of
-// D) to its last position.
+// D) to the end of the scratch page that holds its last position `hi`.  Chunks wholly below `lo`
+// or above `hi` are written as zeros: the attention kernel fetches whole scratch pages, masks
+// the keys it may not see and multiplies their values by zero, so they must be finite.
 struct GatherItem {
   int slot;          // row of the source block table
   int first_pos;     // position of chunk 0
   int n_chunks;
   int dst_base;      // scratch page that holds position first_pos
-  int lo;            // lowest position the attention call will read
+  int lo, hi;        // lowest and highest position the attention call will read
   int chunk_start;   // chunks of the items before this one
+  int pad_;
 };
 
 template <typename T>
@@ -45,7 +48,8 @@ __global__ void __launch_bounds__(256) kv_gather_kernel(
   const int pos = it.first_pos + c * P;
   const int kvh = blockIdx.y;
   const bool value = blockIdx.z != 0;
-  const int src_page = (pos + P - 1 >= it.lo) ? table[(size_t)it.slot * table_stride + pos / P] : -1;
+  const int src_page =
+      (pos + P - 1 >= it.lo && pos <= it.hi) ? table[(size_t)it.slot * table_stride + pos / P] : -1;
   T* dst = (value ? v_dst : k_dst) + (size_t)(it.dst_base + (pos - it.first_pos) / D) * dst_page_stride +
            ((size_t)kvh * D + pos % D) * hd;
   const int n16 = P * hd * (int)sizeof(T) / 16;
@@ -61,7 +65,7 @@ __global__ void __launch_bounds__(256) kv_gather_kernel(
 }
 }  // namespace
 
-// items: n_items x (slot, first_pos, n_chunks, dst_base, lo, chunk_start) int32 on the device;
+// items: n_items x (slot, first_pos, n_chunks, dst_base, lo, hi, chunk_start, 0) int32 on the device;
 // total_chunks: the sum of n_chunks.  P must divide D; P * hd elements must be a multiple of 16
 // bytes and the planes 16-byte aligned.
 LLM_EXPORT int llm_kv_gather(const void* k_src, const void* v_src, long long src_page_stride,

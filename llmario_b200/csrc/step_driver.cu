@@ -142,7 +142,7 @@ enum BufId : int {
   B_ITEMS, B_GATHER
 };
 
-struct Buf { void* p = nullptr; size_t bytes = 0; };
+struct Buf { void* p = nullptr; size_t bytes = 0; bool kept_zero = false; };
 
 struct Arena {
   std::map<long long, Buf> bufs;
@@ -169,6 +169,7 @@ struct Arena {
         if (e != cudaSuccess) return (int)e;
       }
       b.bytes = want;
+      b.kept_zero = zero;
       ++generation;
     }
     *out = b.p;
@@ -405,11 +406,12 @@ struct Run {
       const int lo = window > 0 && r.pos0 + 1 > window ? r.pos0 + 1 - window : 0;
       const int first_page = lo / D;                        // scratch page of the lowest key read
       const int first_pos = first_page * D;
-      const int n_chunks = (r.pos1 - 1) / ps - first_pos / ps + 1;
-      list.insert(list.end(), {r.slot, first_pos, n_chunks, g.scratch_pages, lo, g.total_chunks});
+      const int n_pages = (r.pos1 - 1) / D - first_page + 1;
+      const int n_chunks = n_pages * (D / ps);          // whole scratch pages: the tail is zeroed
+      list.insert(list.end(), {r.slot, first_pos, n_chunks, g.scratch_pages, lo, r.pos1 - 1, g.total_chunks, 0});
       for (int pi = 0; pi < max_pages; ++pi)
         table.push_back(pi >= first_page && pi * D < r.pos1 ? g.scratch_pages + pi - first_page : -1);
-      g.scratch_pages += (r.pos1 - 1) / D - first_page + 1;
+      g.scratch_pages += n_pages;
       g.total_chunks += n_chunks;
       ++g.n_requests;
     }
@@ -738,3 +740,17 @@ LLM_EXPORT int llm_attention_step(const LlmLayerDesc* layer, const LlmCallDesc* 
 }
 
 LLM_EXPORT void llm_set_gather(int on) { g_gather = on ? 1 : 0; }
+
+// Fill every temporary buffer of the arena (not those that are kept at zero) with `byte`.  For
+// tests: with 0xff every 16- and 32-bit value is a NaN, so a kernel that reads what nothing wrote
+// in this step shows up in the result.  Synchronises the device.
+LLM_EXPORT int llm_arena_fill(int byte) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  for (auto& kv : arena().bufs)
+    if (kv.second.p && !kv.second.kept_zero) {
+      e = cudaMemset(kv.second.p, byte, kv.second.bytes);
+      if (e != cudaSuccess) return (int)e;
+    }
+  return (int)cudaDeviceSynchronize();
+}

@@ -109,6 +109,18 @@ def policies():
     return l.llm_token_tile, l.llm_k_splits, l.llm_decode_splits
 
 
+def arena_fill(byte: int = 0xFF) -> None:
+    """Fill the driver's temporary buffers (not those it keeps at zero) with ``byte``; with 0xff
+    every value in them is a NaN.  For tests: a kernel that reads what no kernel of the same
+    step wrote then shows in the result."""
+    l = _lib()
+    l.llm_arena_fill.argtypes = [c_int]
+    l.llm_arena_fill.restype = c_int
+    rc = l.llm_arena_fill(int(byte))
+    if rc != 0:
+        raise kernels.KernelError(f"arena_fill: CUDA error {rc}")
+
+
 def use_gather(on: bool) -> None:
     """Whether long prompt portions over a cache with small pages read gathered copies of their
     requests' keys and values (the default) or the cache as it is.  For measurements."""

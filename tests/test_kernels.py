@@ -16,7 +16,8 @@ def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
     return (scale * torch.randn(*shape, generator=g)).to(dtype).to(DEV)
 
 
-@pytest.mark.parametrize("rows,width", [(1, 40), (7, 1000), (33, 4096)])
+@pytest.mark.parametrize("rows,width", [(1, 40), (7, 1000), (33, 4096), (515, 1024), (2050, 1000),
+                                        (600, 2048), (513, 96)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_rms_norm(rows, width, out_dtype):
     from llmario_b200 import kernels

@@ -36,6 +36,7 @@ def test_native_policies_equal_the_python_ones():
 
 
 def _replay(name, dtype, steps, max_tokens, page, use_native):
+    from llmario_b200 import driver
     from llmario_b200.engine import Model, ModelRunner, StepEntry
 
     model = Model.from_folder(model_dir(name, dtype), dtype, "cuda:0")
@@ -46,6 +47,8 @@ def _replay(name, dtype, steps, max_tokens, page, use_native):
     assert (runner.native is not None) == use_native
     out = {}
     for s in steps:
+        if use_native and s["step"] % 3 == 0:
+            driver.arena_fill(0xFF)      # stale scratch contents must not reach any result
         logits = runner.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]])
         if logits.shape[0]:
             out[s["step"]] = logits.cpu().numpy()
