@@ -101,7 +101,17 @@ def cmd_attention(a) -> None:
     pml = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=DEV)
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
 
+    if a.persistent:
+        parts = 4
+        po = torch.empty(B * Hq * parts * hd, dtype=torch.float32, device=DEV)
+        pml = torch.empty(B * Hq * parts * 2, dtype=torch.float32, device=DEV)
+
     def fn():
+        if a.persistent:
+            kernels.attention_decode_persistent(q, po, pml, storage, 0, table, slot, pos, Hq, Hkv, hd,
+                                                page, hd ** -0.5, None, parts)
+            kernels.attention_merge(po, pml, out, None, B, Hq, hd, parts)
+            return
         if a.row_major:
             kernels.attention_flash(q, out, storage[0, 0, 0], storage[0, 0, 1], storage.stride(0),
                                     table, None, B, 16, Hq, Hkv, hd, page, hd ** -0.5, None, splits,
@@ -161,6 +171,8 @@ def cmd_step(a) -> None:
     from ..cli import preset_config
     from ..engine import Model, ModelRunner, StepEntry
 
+    from .. import driver
+    driver.use_persistent_decode(a.persistent)
     model = Model.random(preset_config(a.model, a.layers), 0, "bfloat16", DEV)
     runner = ModelRunner(model, page_size=a.page_size, cache_tokens=a.batch * (a.context + 256),
                          max_requests=max(a.batch, 8), max_context=8192, use_graphs=not a.eager)
@@ -243,6 +255,8 @@ def main(argv=None) -> int:
                    help="the decode kernel that loads with cp.async instead of TMA tiles")
     d.add_argument("--chain", type=int, default=1,
                    help="launches per timed interval (hides the host's launch time)")
+    d.add_argument("--persistent", action="store_true",
+                   help="the persistent decode kernel: all tiles shared evenly by resident CTAs")
     d.add_argument("--row-major", action="store_true",
                    help="the 16-row kernel of attention_flash.cu instead of the decode kernel")
     d.set_defaults(fn=cmd_attention)
@@ -268,6 +282,8 @@ def main(argv=None) -> int:
     st.add_argument("--steps", type=int, default=4)
     st.add_argument("--page-size", type=int, default=16)
     st.add_argument("--eager", action="store_true", help="no CUDA graphs")
+    st.add_argument("--persistent", action="store_true",
+                    help="decode attention by the persistent kernel where its CTAs make one to five waves")
     st.set_defaults(fn=cmd_step)
     ps = sub.add_parser("prompt-step")
     ps.add_argument("--model", default="qwen3-8b")

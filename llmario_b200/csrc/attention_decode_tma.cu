@@ -425,6 +425,347 @@ __global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The persistent form, for steps of single new tokens whose (request, KV head) units would make
+// several waves of CTAs.  As many one-warp CTAs as the GPU holds at once share the tiles of ALL
+// units evenly: the tiles are numbered unit by unit (request-major, then KV head), CTA w takes
+// tiles [w Q, (w + 1) Q), and so walks the end of one unit, whole units, and the start of another.
+// No wave is left half empty, and the ring of tiles runs on from one unit to the next.  Each
+// piece of a unit that a CTA computes goes to part_o / part_ml as part z = w - (first tile of the
+// unit) / Q; the CTA that computes a unit's last tile marks the parts after its own as empty
+// (maximum -inf), and llm_attention_merge reads `parts` of them per (row, head).  Q is chosen on
+// the device (every CTA computes the same numbers from the rows' positions): the tiles per CTA,
+// but never so few that a unit would need more than `parts` pieces.
+// ---------------------------------------------------------------------------------------------
+constexpr int PERSIST_MAX_ROWS = 256;
+
+struct Cursor {       // a tile of the CTA's run and the unit it belongs to
+  int r, kvh;         // request row and KV head
+  int rel, t;         // tile of the unit counted from its first, tiles of the unit
+  int first;          // the unit's first tile (lo / KT)
+  int lo, hi, slot;   // lowest and highest position the row reads, its request slot
+};
+
+template <int HD, int KT, int STAGES>
+__global__ void __launch_bounds__(32, 3) flash_decode_persistent_kernel(
+    const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, float* __restrict__ part_o,
+    float* __restrict__ part_ml, const int* __restrict__ block_table, int table_stride,
+    const int* __restrict__ row_slot, const int* __restrict__ row_pos, int rows, int Hq, int Hkv, int page_size,
+    int n_slots, int slot, float scale_log2, int window, int parts, int* __restrict__ status) {
+  constexpr int KS = HD / 16, MT = KT / 16, DM = HD / 16;
+  constexpr int TILE_BYTES = KT * HD * 2;
+  extern __shared__ uint8_t raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* kv_tiles = smem;                          // [STAGES][2 * TILE_BYTES]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * 2 * TILE_BYTES);
+  int* s_pref = reinterpret_cast<int*>(full + STAGES);          // [rows + 1] tiles of the rows before
+  int* s_pos = s_pref + PERSIST_MAX_ROWS + 1;
+  int* s_slot = s_pos + PERSIST_MAX_ROWS;
+  pdl_trigger();
+
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  if (lane == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+
+  // ---- every CTA: the tiles of every row (positions and slots are complete before the step's
+  // first layer starts, so they are read before the wait), their running sum, the longest unit
+  const int G = Hq / Hkv;
+  constexpr int PER_LANE = PERSIST_MAX_ROWS / 32;
+  int mine[PER_LANE], sum = 0, longest = 0;
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int r = lane * PER_LANE + i;
+    int tiles = 0;
+    if (r < rows) {
+      const int pos = row_pos[r];
+      const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+      tiles = pos / KT - lo / KT + 1;
+      s_pos[r] = pos;
+      s_slot[r] = row_slot[r];
+    }
+    mine[i] = tiles;
+    sum += tiles;
+    longest = max(longest, tiles);
+  }
+  int before = sum;                                   // inclusive scan over the lanes
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, before, o);
+    if (lane >= o) before += v;
+  }
+  const int total_rows = __shfl_sync(0xffffffffu, before, 31);
+  before -= sum;
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int r = lane * PER_LANE + i;
+    if (r <= rows) s_pref[r] = before;
+    before += mine[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
+  __syncwarp();
+  const long long T = (long long)total_rows * Hkv;    // tiles of all units
+  long long Q = (T + gridDim.x - 1) / gridDim.x;
+  const int least = (longest + parts - 2) / (parts - 1);        // a unit makes at most `parts` pieces
+  if (Q < least) Q = least;
+  const long long g0 = (long long)blockIdx.x * Q;
+  const long long g1 = min(T, g0 + Q);
+  if (g0 >= g1) return;
+
+  const int R = page_size < KT ? page_size : KT;
+  const int lgR = 31 - __clz(R);
+  const int lgP = 31 - __clz(page_size);
+
+  auto row_info = [&](int r, Cursor& c) {
+    c.r = r;
+    c.hi = s_pos[r];
+    c.lo = (window > 0 && c.hi + 1 > window) ? c.hi + 1 - window : 0;
+    c.first = c.lo / KT;
+    c.t = c.hi / KT - c.first + 1;
+    c.slot = s_slot[r];
+  };
+  auto locate = [&](long long gi, Cursor& c) {        // the tile numbered gi
+    int a = 0, b = rows - 1;
+    while (a < b) {
+      const int mid = (a + b + 1) >> 1;
+      if ((long long)s_pref[mid] * Hkv <= gi) a = mid; else b = mid - 1;
+    }
+    row_info(a, c);
+    const int rem = (int)(gi - (long long)s_pref[a] * Hkv);
+    c.kvh = rem / c.t;
+    c.rel = rem % c.t;
+  };
+  auto advance = [&](Cursor& c) {
+    if (++c.rel < c.t) return;
+    c.rel = 0;
+    if (++c.kvh < Hkv) return;
+    c.kvh = 0;
+    if (c.r + 1 < rows) row_info(c.r + 1, c);
+  };
+
+  // The producer keeps 32 entries of the current row's block table in the warp's lanes.
+  int held_row = -1, held_from = 0, held = 0;
+  auto load_tile = [&](const Cursor& c, int stage) {  // the whole warp calls it; lane 0 issues
+    const int base = (c.first + c.rel) * KT;
+    const int* table = block_table + (size_t)c.slot * table_stride;
+    const int last_page = c.hi >> lgP;
+    uint32_t bytes = 0;
+    for (int p = base; p < base + KT; p += R)
+      if (p <= c.hi && p + R - 1 >= c.lo) bytes += (uint32_t)R * HD * 2 * 2;
+    if (lane == 0) mbar_expect_tx(&full[stage], bytes);
+    for (int p = base; p < base + KT; p += R) {
+      if (p > c.hi || p + R - 1 < c.lo) continue;
+      const int pi = p >> lgP;
+      if (held_row != c.r || pi < held_from || pi >= held_from + 32) {
+        held_row = c.r;
+        held_from = pi;
+        held = pi + lane <= last_page ? table[pi + lane] : 0;
+      }
+      const int plane = (__shfl_sync(0xffffffffu, held, pi - held_from) * n_slots + slot) * 2;
+      if (lane == 0)
+        tma_load_5d(kv_tiles + stage * 2 * TILE_BYTES + ((p - base) >> lgR) * (2 * R * HD * 2), &map_kv, 0, 0,
+                    p & (page_size - 1), c.kvh, plane, &full[stage]);
+    }
+  };
+
+  Cursor prod, cons;
+  locate(g0, prod);
+  cons = prod;
+  long long issued = g0;
+  // tiles wholly below the row's new position hold nothing the kernel ahead writes
+  while (issued < g1 && issued - g0 < STAGES && (prod.first + prod.rel + 1) * KT <= prod.hi) {
+    load_tile(prod, (int)(issued - g0) % STAGES);
+    advance(prod);
+    ++issued;
+  }
+  pdl_wait();
+  while (issued < g1 && issued - g0 < STAGES) {
+    load_tile(prod, (int)(issued - g0) % STAGES);
+    advance(prod);
+    ++issued;
+  }
+
+  uint32_t qf[KS][2];
+  float o[DM][4];
+  float m[2], l[2];
+  bool cvalid[2];
+  size_t crow[2];
+  bool fresh = true;
+  bool alive = true;
+  int n_it = 0;
+  for (long long gi = g0; gi < g1; ++gi, ++n_it) {
+    if (fresh) {                                   // a piece begins: this unit's queries, empty sums
+      fresh = false;
+      const bool valid = g < G;
+      const bf16* src = q + ((size_t)cons.r * Hq + cons.kvh * G + (valid ? g : 0)) * HD + 2 * t;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        qf[k][0] = valid ? *reinterpret_cast<const uint32_t*>(src + k * 16) : 0u;
+        qf[k][1] = valid ? *reinterpret_cast<const uint32_t*>(src + k * 16 + 8) : 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = 2 * t + j;
+        cvalid[j] = n < G;
+        crow[j] = (size_t)cons.r * Hq + cons.kvh * G + (cvalid[j] ? n : 0);
+        m[j] = -INFINITY;
+        l[j] = 0.f;
+      }
+#pragma unroll
+      for (int d = 0; d < DM; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    }
+    const int stage = n_it % STAGES;
+    alive = mbar_wait(&full[stage], (uint32_t)(n_it / STAGES) & 1);
+    alive = __all_sync(0xffffffffu, alive);
+    if (!alive) {
+      if (lane == 0) atomicExch(status, 5);
+      break;
+    }
+    uint8_t* tile = kv_tiles + stage * 2 * TILE_BYTES;
+    const int base = (cons.first + cons.rel) * KT;
+    {
+      // a page without a key of the row was not fetched: its values meet zero weights and must
+      // be finite (its keys may be anything: their scores are replaced by -inf)
+      for (int p = base; p < base + KT; p += R)
+        if (p > cons.hi || p + R - 1 < cons.lo) {
+          uint4* vz = reinterpret_cast<uint4*>(tile + ((p - base) >> lgR) * (2 * R * HD * 2) + R * HD * 2);
+          for (int i = lane; i < R * HD * 2 / 16; i += 32) vz[i] = make_uint4(0, 0, 0, 0);
+        }
+      __syncwarp();
+    }
+    // ---- S^T = K Q^T
+    float s[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t a[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4(a, tile + tile_off<HD>(0, mt * 16 + (mi & 1) * 8 + (lane & 7), 2 * k + (mi >> 1), lgR));
+        mma_bf16(s[mt], a, qf[k][0], qf[k][1]);
+      }
+    }
+    // ---- mask, running maximum per pair, exponentials
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = e & 1;
+        const int p = base + mt * 16 + g + 8 * (e >> 1);
+        const bool vis = cvalid[j] && p <= cons.hi && p >= cons.lo;
+        s[mt][e] = vis ? s[mt][e] * scale_log2 : -INFINITY;
+        tmax[j] = fmaxf(tmax[j], s[mt][e]);
+      }
+    float corr[2], muse[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 4));
+      tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 8));
+      tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 16));
+      const float mnew = fmaxf(m[j], tmax[j]);
+      muse[j] = mnew == -INFINITY ? 0.f : mnew;
+      corr[j] = fast_exp2(m[j] - muse[j]);
+      m[j] = mnew;
+      l[j] *= corr[j];
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pexp = fast_exp2(s[mt][e] - muse[e & 1]);
+        s[mt][e] = pexp;
+        l[e & 1] += pexp;
+      }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+      for (int d = 0; d < DM; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[1];
+        o[d][2] *= corr[0]; o[d][3] *= corr[1];
+      }
+    }
+    // ---- O^T += V^T P^T
+#pragma unroll
+    for (int kk = 0; kk < MT; ++kk) {
+      const uint32_t b0 = movmatrix_trans(pack_bf16(s[kk][0], s[kk][1]));
+      const uint32_t b1 = movmatrix_trans(pack_bf16(s[kk][2], s[kk][3]));
+#pragma unroll
+      for (int d = 0; d < DM; ++d) {
+        uint32_t a[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4_trans(a, tile + tile_off<HD>(1, kk * 16 + (mi >> 1) * 8 + (lane & 7), 2 * d + (mi & 1), lgR));
+        mma_bf16(o[d], a, b0, b1);
+      }
+    }
+    __syncwarp();                  // every lane has read this stage
+    if (issued < g1) {
+      if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      load_tile(prod, stage);
+      advance(prod);
+      ++issued;
+    }
+    // ---- the piece ends with the unit or with this CTA's run: its sums go out as one part
+    const bool unit_end = cons.rel == cons.t - 1;
+    if (unit_end || gi == g1 - 1) {
+      const long long unit_first = (long long)s_pref[cons.r] * Hkv + (long long)cons.kvh * cons.t;
+      const int z = (int)((long long)blockIdx.x - unit_first / Q);
+      float lsum[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        lsum[j] = l[j];
+        lsum[j] += __shfl_xor_sync(0xffffffffu, lsum[j], 4);
+        lsum[j] += __shfl_xor_sync(0xffffffffu, lsum[j], 8);
+        lsum[j] += __shfl_xor_sync(0xffffffffu, lsum[j], 16);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        if (!cvalid[j]) continue;
+        float* dst = part_o + (crow[j] * parts + z) * HD;
+#pragma unroll
+        for (int d = 0; d < DM; ++d) {
+          dst[d * 16 + g] = o[d][j];
+          dst[d * 16 + g + 8] = o[d][2 + j];
+        }
+        if (g == 0) {
+          part_ml[(crow[j] * parts + z) * 2] = m[j];
+          part_ml[(crow[j] * parts + z) * 2 + 1] = lsum[j];
+          if (unit_end)                            // no CTA computes a part after this one
+            for (int zz = z + 1; zz < parts; ++zz) part_ml[(crow[j] * parts + zz) * 2] = -INFINITY;
+        }
+      }
+      fresh = true;
+    }
+    advance(cons);
+  }
+  if (!alive)     // let the loads that are still in flight land before the shared memory goes
+    for (int i = 0; i < STAGES; ++i) mbar_wait(&full[i], 0), mbar_wait(&full[i], 1);
+}
+
+template <int HD>
+int launch_persistent(const CUtensorMap& map, const bf16* q, float* part_o, float* part_ml, const int* table,
+                      int table_stride, const int* row_slot, const int* row_pos, int rows, int Hq, int Hkv,
+                      int page_size, int n_slots, int slot, float scale, int window, int parts, int ctas,
+                      int* status, cudaStream_t s) {
+  constexpr int KT = DECODE_KT, STAGES = DECODE_STAGES;
+  auto kernel = flash_decode_persistent_kernel<HD, KT, STAGES>;
+  constexpr int smem = 2 * STAGES * KT * HD * 2 + STAGES * 8 + (3 * PERSIST_MAX_ROWS + 1) * 4 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return launch_pdl(kernel, dim3(ctas), 32, smem, s, map, q, part_o, part_ml, table, table_stride, row_slot,
+                    row_pos, rows, Hq, Hkv, page_size, n_slots, slot, scale * 1.4426950408889634f, window, parts,
+                    status);
+}
+
 template <int HD, bool FUSED>
 int launch(const CUtensorMap& map, const bf16* q, bf16* out, float* part_o, float* part_ml, const int* table,
            int table_stride, const int* items, const int* row_slot, const int* row_pos, int n_items, int Hq,
@@ -483,6 +824,33 @@ LLM_EXPORT int llm_attention_decode_tma(const void* q, void* out, float* part_o,
   return launch<HD, false>(map, (const bf16*)q, (bf16*)out, part_o, part_ml, block_table, table_stride,  \
                            items, row_slot, row_pos, n_items, Hq, Hkv, page_size, (int)n_slots, slot, scale, \
                            window, splits, status, none, stream)
+  if (hd == 128) GO(128);
+  GO(64);
+#undef GO
+}
+
+// The persistent form for steps of single new tokens (see flash_decode_persistent_kernel): rows
+// one-token items described by row_slot / row_pos, at most 256 of them and at most eight query
+// heads per KV head.  It always writes `parts` parts per (row, head) into part_o / part_ml
+// ([rows * Hq * parts][hd] and [...][2] floats; 2 <= parts <= 32), of which some are marked empty,
+// and is followed by llm_attention_merge with splits = parts.  ctas: how many one-warp CTAs to
+// launch (what the GPU holds at once: three per SM).
+LLM_EXPORT int llm_attention_decode_persistent(const void* q, float* part_o, float* part_ml,
+                                               const void* storage, long long n_pages, int n_slots,
+                                               int slot, const int* block_table, int table_stride,
+                                               const int* row_slot, const int* row_pos, int rows, int Hq,
+                                               int Hkv, int hd, int page_size, float scale, int window,
+                                               int parts, int ctas, int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!row_slot || !row_pos || parts < 2 || parts > 32 || ctas <= 0 || window < 0) return LLM_ERR_ARGUMENT;
+  if (rows > PERSIST_MAX_ROWS || (Hkv > 0 && Hq / Hkv > 8)) return LLM_ERR_UNSUPPORTED;
+  CUtensorMap map;
+  if (int e = check_and_map(storage, n_pages, n_slots, slot, Hq, Hkv, hd, page_size, parts, part_o, part_ml, &map))
+    return e;
+#define GO(HD)                                                                                              \
+  return launch_persistent<HD>(map, (const bf16*)q, part_o, part_ml, block_table, table_stride, row_slot,    \
+                               row_pos, rows, Hq, Hkv, page_size, (int)n_slots, slot, scale, window, parts,   \
+                               ctas, status, stream)
   if (hd == 128) GO(128);
   GO(64);
 #undef GO

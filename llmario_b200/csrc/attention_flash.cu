@@ -275,7 +275,8 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
     float acc = 0.f, lsum = 0.f;
     for (int z = 0; z < splits; ++z) {
       const float mz = part_ml[(rowhead * splits + z) * 2];
-      const float w = mz == -INFINITY ? 0.f : exp2f(mz - mstar);
+      if (mz == -INFINITY) continue;      // a part without keys: what lies in its place is not read
+      const float w = exp2f(mz - mstar);
       acc += w * part_o[(rowhead * splits + z) * HD + d];
       lsum += w * part_ml[(rowhead * splits + z) * 2 + 1];
     }

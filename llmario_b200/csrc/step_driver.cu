@@ -66,6 +66,11 @@ int llm_attention_decode_tma(const void* q, void* out, float* part_o, float* par
                              int table_stride, const int* items, const int* row_slot, const int* row_pos,
                              int n_items, int Hq, int Hkv, int hd, int page_size, float scale, int window,
                              int splits, int* status, cudaStream_t stream);
+int llm_attention_decode_persistent(const void* q, float* part_o, float* part_ml, const void* storage,
+                                    long long n_pages, int n_slots, int slot, const int* block_table,
+                                    int table_stride, const int* row_slot, const int* row_pos, int rows, int Hq,
+                                    int Hkv, int hd, int page_size, float scale, int window, int parts, int ctas,
+                                    int* status, cudaStream_t stream);
 int llm_attention_decode_fused(float* proj, int proj_stride, void* out, float* part_o, float* part_ml,
                                const void* storage, long long n_pages, int n_slots, int slot, void* k_cache,
                                void* v_cache, long long page_stride, const int* block_table,
@@ -105,12 +110,27 @@ constexpr int PERSISTENT_ATTENTION_MAX_KEYS = 6144;
 constexpr int GATHER_PAGE = 128;
 constexpr int GATHER_MIN_PAIRS = 512;
 int g_gather = 1;                           // 0: never gather (for measurements)
+// The persistent decode kernel (attention_decode_tma.cu: as many one-warp CTAs as fit at once
+// share all tiles of a step of single tokens evenly; every (row, head) gets PERSISTENT_PARTS parts,
+// some empty, for the merge) is OFF unless llm_set_persistent_decode(1).  Measured, 32 query / 8 KV
+// heads of 128: by itself it beats one CTA per part where those make one to five waves (32 rows x
+// 1,024 keys 31.0 -> 28.2 us, 64 x 1,024 53.0 -> 49.9, 64 x 4,096 169.5 -> 167.4; not beyond 128
+// rows, since every CTA first reads all rows' positions).  Inside the decode step of the 36-layer
+// model at batch 64 it gains 1.4 % at best (5.38 -> 5.30 ms with 410 CTAs) and LOSES 16 % with the
+// 444 CTAs that fit an idle GPU (6.24 ms): between other kernels not all of them find room at
+// once, and a CTA that starts late still has its full share to walk.  Short-lived CTAs do not
+// have that cliff, so they stay the default.
+constexpr int PERSISTENT_PARTS = 4;
+constexpr int PERSISTENT_MAX_ROWS = 128;
+constexpr int PERSISTENT_MAX_WAVES = 5;
+int g_persistent_decode = 0;
 int g_fuse_mode = 0;                        // 0: when few waves, 1: always, 2: never
 
 // how often the driver chose which kernel (llm_driver_counts; tests and statistics read them)
 enum Kind : int {
   K_NORM, K_GEMM_TCGEN05, K_GEMM_SIMT, K_ROPE_TABLE, K_ROPE_STORE, K_DECODE_FUSED, K_DECODE_TMA, K_DECODE,
-  K_FLASH, K_MERGE, K_TCGEN05, K_TCGEN05_X2, K_GENERIC, K_SILU_MUL, K_KV_GATHER, N_KINDS
+  K_FLASH, K_MERGE, K_TCGEN05, K_TCGEN05_X2, K_GENERIC, K_SILU_MUL, K_KV_GATHER, K_DECODE_PERSISTENT,
+  N_KINDS
 };
 long long g_counts[N_KINDS] = {};
 
@@ -492,6 +512,21 @@ struct Run {
                                                  tma ? DECODE_TMA_TILE : 32)
                              : 1;
       float *part_o, *part_ml;
+      const int resident = 3 * sm_count();
+      if (g_persistent_decode && tma && plan->small == nullptr && st.rows <= PERSISTENT_MAX_ROWS &&
+          (long long)plan->n_small * Hkv * splits > resident &&
+          (long long)plan->n_small * Hkv * splits <= (long long)PERSISTENT_MAX_WAVES * resident) {
+        rc = parts(PERSISTENT_PARTS, L, &part_o, &part_ml);
+        if (rc) return rc;
+        rc = check(llm_attention_decode_persistent(q, part_o, part_ml, c.storage, c.n_pages, c.n_slots, c.slot,
+                                                   c.block_table, c.table_stride, st.row_slot, st.row_pos,
+                                                   plan->n_small, Hq, Hkv, hd, ps, L.scale, window,
+                                                   PERSISTENT_PARTS, resident - resident / 12, st.status, stream),
+                   K_DECODE_PERSISTENT);
+        if (rc) return rc;
+        return check(llm_attention_merge_clear(part_o, part_ml, out, nullptr, plan->n_small, Hq, hd,
+                                               PERSISTENT_PARTS, nullptr, 0, stream), K_MERGE);
+      }
       rc = parts(splits, L, &part_o, &part_ml);
       if (rc) return rc;
       if (tma)
@@ -740,6 +775,7 @@ LLM_EXPORT int llm_attention_step(const LlmLayerDesc* layer, const LlmCallDesc* 
 }
 
 LLM_EXPORT void llm_set_gather(int on) { g_gather = on ? 1 : 0; }
+LLM_EXPORT void llm_set_persistent_decode(int on) { g_persistent_decode = on ? 1 : 0; }
 
 // Fill every temporary buffer of the arena (not those that are kept at zero) with `byte`.  For
 // tests: with 0xff every 16- and 32-bit value is a NaN, so a kernel that reads what nothing wrote

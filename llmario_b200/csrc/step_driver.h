@@ -71,6 +71,7 @@ int llm_arena_drop();
 int llm_attention_step(const LlmLayerDesc* layer, const LlmCallDesc* call, const LlmStepDesc* step,
                        const void* q, void* out, int* n_launches, cudaStream_t stream);
 void llm_set_gather(int on);
+void llm_set_persistent_decode(int on);
 int llm_arena_fill(int byte);
 int llm_run_layers(const LlmLayerDesc* layers, const LlmCallDesc* calls, int n_calls,
                    const LlmStepDesc* step, int* n_launches, cudaStream_t stream);

@@ -89,7 +89,7 @@ def arena_drop() -> None:
 
 KINDS = ("norm", "gemm_tcgen05", "gemm_simt", "rope_table", "rope_store", "decode_fused",
          "decode_tma", "decode", "flash", "merge", "tcgen05", "tcgen05_x2", "generic", "silu_mul",
-         "kv_gather")
+         "kv_gather", "decode_persistent")
 
 
 def kernel_counts() -> Dict[str, int]:
@@ -119,6 +119,17 @@ def arena_fill(byte: int = 0xFF) -> None:
     rc = l.llm_arena_fill(int(byte))
     if rc != 0:
         raise kernels.KernelError(f"arena_fill: CUDA error {rc}")
+
+
+def use_persistent_decode(on: bool) -> None:
+    """Whether steps of single tokens whose decode-attention CTAs would make one to five waves
+    run the persistent kernel, or one CTA per (request, KV head, part) (the default: inside a
+    whole step the persistent form gains a percent at best and loses much when its CTAs do not
+    all find room at once).  For measurements."""
+    l = _lib()
+    l.llm_set_persistent_decode.argtypes = [c_int]
+    l.llm_set_persistent_decode.restype = None
+    l.llm_set_persistent_decode(int(on))
 
 
 def use_gather(on: bool) -> None:

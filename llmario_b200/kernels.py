@@ -61,6 +61,8 @@ def _signatures():
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
         "llm_attention_decode_tma": [P, P, P, P, P, L, I, I, P, I, P, P, P, I, I, I, I, I, F, I,
                                      I, P, P],
+        "llm_attention_decode_persistent": [P, P, P, P, L, I, I, P, I, P, P, I, I, I, I, I, F, I, I, I,
+                                            P, P],
         "llm_attention_tcgen05": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, I, P, P],
         "llm_attention_tcgen05_x2": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, P, P],
         "llm_apply_penalties": [P, L, P, I, P, P, P, P],
@@ -563,6 +565,28 @@ def attention_decode_tma(q: torch.Tensor, out: torch.Tensor, storage: torch.Tens
         _ptr(row_slot), _ptr(row_pos), n_items, num_heads, num_kv_heads, head_dim, page_size,
         float(scale), int(window or 0), splits, _ptr(tc_status(q.device)), _stream()),
         f"attention_decode_tma (head_dim {head_dim})")
+
+
+def attention_decode_persistent(q: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
+                                storage: torch.Tensor, slot: int, block_table: torch.Tensor,
+                                row_slot: torch.Tensor, row_pos: torch.Tensor, num_heads: int,
+                                num_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                                window: Optional[int], parts: int, ctas: Optional[int] = None) -> None:
+    """Decode attention of one new token per row with the tiles of all (row, KV head) units
+    shared evenly by ``ctas`` one-warp CTAs (default: what the GPU holds at once).  Leaves
+    ``parts`` parts per (row, head) in ``part_o`` / ``part_ml`` (some marked empty) for
+    :func:`attention_merge` with ``splits = parts``."""
+    _cuda(q, part_o, part_ml, storage, block_table, row_slot, row_pos)
+    assert q.dtype == torch.bfloat16 and storage.dtype == torch.bfloat16
+    assert storage.is_contiguous() and storage.dim() == 6
+    rows = q.shape[0]
+    assert part_o.numel() >= rows * num_heads * parts * head_dim
+    _check(lib().llm_attention_decode_persistent(
+        _ptr(q), _ptr(part_o), _ptr(part_ml), _ptr(storage), storage.shape[0], storage.shape[1],
+        slot, _ptr(block_table), block_table.stride(0), _ptr(row_slot), _ptr(row_pos), rows,
+        num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), parts,
+        int(ctas or 3 * sm_count()), _ptr(tc_status(q.device)), _stream()),
+        f"attention_decode_persistent (head_dim {head_dim})")
 
 
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,

@@ -830,3 +830,44 @@ def test_attention_decode_fused_against_the_formulas(Hq, Hkv, hd, page, window, 
         pg, s = table[r, p // page].item(), p % page
         assert (storage[pg, 1, 0, :, s].double().cpu() - k_new).abs().max() <= 2e-2 * k_new.abs().max()
         assert (storage[pg, 1, 1, :, s].double().cpu() - v_new).abs().max() <= 2e-2 * v_new.abs().max()
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,window", [(32, 8, 128, 16, None), (8, 2, 128, 64, None),
+                                                   (6, 3, 64, 8, 50), (8, 1, 128, 16, 200),
+                                                   (4, 4, 64, 128, 100), (16, 2, 128, 32, None)])
+@pytest.mark.parametrize("ctas", [1, 7, 60, 444])
+def test_attention_decode_persistent(Hq, Hkv, hd, page, window, ctas):
+    """The persistent decode kernel: all (row, KV head) units' tiles shared evenly by a given
+    number of one-warp CTAs, so that CTAs begin and end in the middle of units; with one CTA a
+    single warp walks everything, with 444 most CTAs have one tile or none and units are cut as
+    finely as the number of parts allows.  The parts buffers start as NaNs: a part nobody
+    computes must be marked empty, and an empty part must not be read.  Against float64."""
+    from llmario_b200 import kernels
+    dtype = torch.bfloat16
+    lengths = [1, 33, 150, 64, 700, 385, 65, 128, 129, 1000, 2, 447]
+    storage, table, ks, vs = paged_setup(lengths, page, Hkv, hd, dtype, seed=9)
+    scale = 1 / math.sqrt(hd)
+    rows = [(r, n - 1) for r, n in enumerate(lengths)]
+    q = torch.randn(len(rows), Hq, hd, generator=torch.Generator().manual_seed(6)).to(dtype)
+    # one key stands out for head 0 of the longest request: far back, at a tile's edge
+    far = 63 if not window else lengths[9] - window
+    ks[9][far, 0] = (6 * math.sqrt(hd) * q[9, 0].float() / q[9, 0].float().norm()).to(dtype)
+    storage[table[9, far // page].item(), 1, 0, 0, far % page] = ks[9][far, 0].to(DEV)
+    qd = q.reshape(len(rows), -1).to(DEV).contiguous()
+    slot = torch.arange(len(rows), dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    for parts in (2, 4):
+        po = torch.full((len(rows) * Hq * parts * hd,), float("nan"), dtype=torch.float32, device=DEV)
+        pml = torch.full((len(rows) * Hq * parts * 2,), float("nan"), dtype=torch.float32, device=DEV)
+        out = torch.zeros(len(rows), Hq * hd, dtype=dtype, device=DEV)
+        kernels.attention_decode_persistent(qd, po, pml, storage, 1, table, slot, pos, Hq, Hkv, hd,
+                                            page, scale, window, parts, ctas)
+        kernels.attention_merge(po, pml, out, None, len(rows), Hq, hd, parts)
+        kernels.check_tc_status(DEV)
+        assert torch.isfinite(out.float()).all(), (parts, ctas)
+        for i, (r, p) in enumerate(rows):
+            ref = attention_ref(q[i].float(), ks[r].float(), vs[r].float(), p, window, scale)
+            got = out[i].reshape(Hq, hd).double().cpu()
+            assert (got - ref).abs().max() <= 2e-2, (parts, ctas, i, r, p, float((got - ref).abs().max()))
+        got = out[9].reshape(Hq, hd).float().cpu()[0]
+        assert (got - vs[9][far, 0].float()).abs().max() < 0.1     # the key that stands out

@@ -39,14 +39,26 @@ def test_every_cut_at_benchmark_widths(dtype, page):
     assert runner.cache.counters["pages_allocated"] > runner.cache.groups[0].n_pages
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("live", [72, 8])
-def test_many_live_requests_decode_through_recorded_steps(dtype, live, monkeypatch):
+@pytest.mark.parametrize("dtype,live,persistent", [("float32", 72, False), ("bfloat16", 72, False),
+                                                   ("bfloat16", 72, True), ("float32", 8, False),
+                                                   ("bfloat16", 8, False)])
+def test_many_live_requests_decode_through_recorded_steps(dtype, live, persistent):
     """``live`` requests with prompts of unequal length, then 44 steps of one token each.  Many
     requests share a length modulo the page size, so their block tables change in the same
     step; the context bucket of the recorded step changes on the way (positions cross 128).
     With 72 live rows bfloat16 decode attention splits the keys and merges once the contexts
     have grown; with 8 it is the fused kernel.  Every row of every step against the plain implementation."""
+    from llmario_b200 import driver, kernels
+    from llmario_b200.engine import Model, ModelRunner, StepEntry
+
+    driver.use_persistent_decode(persistent)
+    try:
+        _many_live(dtype, live, persistent)
+    finally:
+        driver.use_persistent_decode(False)
+
+
+def _many_live(dtype, live, persistent):
     from llmario_b200 import kernels
     from llmario_b200.engine import Model, ModelRunner, StepEntry
 
@@ -93,9 +105,11 @@ def test_many_live_requests_decode_through_recorded_steps(dtype, live, monkeypat
     if dtype == "bfloat16":
         after = native.kernel_counts()
         fused = after["decode_fused"] - before["decode_fused"]
-        split = after["decode_tma"] - before["decode_tma"]
+        split = after["decode_tma"] + after["decode_persistent"] - before["decode_tma"] - \
+            before["decode_persistent"]
         if live >= 64:      # (while every context is short the 72 rows still fit the fused kernel)
             assert split > 0 and after["merge"] > before["merge"]
+            assert (after["decode_persistent"] > before["decode_persistent"]) == persistent
         else:
             assert fused > 0 and split == 0
         assert after["gemm_tcgen05"] > before["gemm_tcgen05"] and after["gemm_simt"] == before["gemm_simt"]
