@@ -317,7 +317,7 @@ def serve_workload(args, cfg, model, pk, clocks):
                 if last_mixed >= 0 else None,
                 "decode_roofline": roof, "launches": kernels.launches - l0})
         for i in ids:
-            engine._requests.pop(i, None)
+            engine.release(i)
     clk = clocks.summary(first_mark)
     best = sorted(runs, key=lambda r: r["aggregate_tok_s"])[len(runs) // 2]
     name = NAMES.get(args.model, args.model)

@@ -83,8 +83,9 @@ def arena_generation() -> int:
 
 def arena_drop() -> None:
     """Forget the driver's buffers (after a failed step: one kept at zero may hold sums)."""
-    kernels._check(_lib().llm_arena_drop(), "arena_drop")
-    kernels.launches -= 1
+    rc = _lib().llm_arena_drop()
+    if rc != 0:
+        raise kernels.KernelError(f"arena_drop: CUDA error {rc}")
 
 
 KINDS = ("norm", "gemm_tcgen05", "gemm_simt", "rope_table", "rope_store", "decode_fused",

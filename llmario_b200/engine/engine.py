@@ -199,7 +199,7 @@ class Engine:
         self.run_until_done()
         out = []
         for rid in ids:
-            r = self._requests.pop(rid)
+            r = self.release(rid)
             if r.error:
                 raise RuntimeError(f"request {rid!r}: {r.error}")
             out.append(list(r.output))
@@ -207,6 +207,14 @@ class Engine:
 
     def request(self, request_id: Any) -> Request:
         return self._requests[request_id]
+
+    def release(self, request_id: Any) -> Optional[Request]:
+        """Forget a finished request (its record is kept until then so that its output can be
+        read).  Returns the record, or None when the id is unknown."""
+        r = self._requests.get(request_id)
+        if r is not None and r.state != FINISHED:
+            raise ValueError(f"request {request_id!r} is still {r.state}")
+        return self._requests.pop(request_id, None)
 
     def stats(self) -> Dict[str, Any]:
         """Counters in the spirit of the reference's ``Stats`` (engine.rs:59-159)."""

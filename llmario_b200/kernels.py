@@ -45,6 +45,7 @@ def _signatures():
         "llm_table_update": [P, I, P, I, P],
         "llm_table_update_counted": [P, I, P, P, I, P],
         "llm_zero_slots": [P, L, P, P, I, P],
+        "llm_kv_gather": [P, P, L, P, I, I, P, P, L, I, I, I, I, P, I, I, P],
         "llm_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, I, I, P],
         "llm_qk_norm_rope_store": [P, I, P, P, P, I, L, P, I, P, P, P, P, P, P, F, I, I, I, I, I,
                                    I, F, I, I, I, P],
@@ -196,6 +197,24 @@ def zero_slots(state: torch.Tensor, slots: torch.Tensor, count: torch.Tensor, ma
     row_bytes = state[0].numel() * state.element_size()
     _check(lib().llm_zero_slots(_ptr(state), row_bytes, _ptr(slots), _ptr(count), max_n,
                                 _stream()), "zero_slots")
+
+
+def kv_gather(k_src: torch.Tensor, v_src: torch.Tensor, src_page_stride: int,
+              block_table: torch.Tensor, page_size: int, k_dst: torch.Tensor, v_dst: torch.Tensor,
+              dst_page_stride: int, dst_page_size: int, num_kv_heads: int, head_dim: int,
+              items: torch.Tensor, n_items: int, total_chunks: int) -> None:
+    """Copy requests' keys and values from cache pages of ``page_size`` positions into scratch
+    pages of ``dst_page_size`` (a multiple).  ``k_src`` / ``v_src`` / ``k_dst`` / ``v_dst``: the
+    K and V planes of page 0 on either side, pages ``*_page_stride`` elements apart.  ``items``:
+    int32 octuples (block-table row, first position, chunks, first scratch page, lowest and
+    highest position read, chunks of the items before, 0); a chunk is one source page; chunks
+    wholly outside [lowest, highest] or whose page the request no longer holds become zeros."""
+    _cuda(k_src, v_src, block_table, k_dst, v_dst, items)
+    assert k_src.dtype == k_dst.dtype and items.dtype == torch.int32
+    _check(lib().llm_kv_gather(_ptr(k_src), _ptr(v_src), src_page_stride, _ptr(block_table),
+                               block_table.stride(0), page_size, _ptr(k_dst), _ptr(v_dst),
+                               dst_page_stride, dst_page_size, num_kv_heads, head_dim, _dt(k_src),
+                               _ptr(items), n_items, total_chunks, _stream()), "kv_gather")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False

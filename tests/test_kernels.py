@@ -871,3 +871,48 @@ def test_attention_decode_persistent(Hq, Hkv, hd, page, window, ctas):
             assert (got - ref).abs().max() <= 2e-2, (parts, ctas, i, r, p, float((got - ref).abs().max()))
         got = out[9].reshape(Hq, hd).float().cpu()[0]
         assert (got - vs[9][far, 0].float()).abs().max() < 0.1     # the key that stands out
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("page,D,hd,Hkv", [(16, 128, 128, 2), (4, 64, 32, 3), (8, 128, 64, 1)])
+def test_kv_gather(dtype, page, D, hd, Hkv):
+    """Requests' keys and values copied from small pages into large scratch pages: every
+    position in [lowest, highest] lands at its place, everything else of the scratch pages that
+    the items name is zero (the tail behind the last position, positions below the lowest one,
+    a page the request gave back), and nothing outside them is touched."""
+    from llmario_b200 import kernels
+    lengths = [300, 41, 130]
+    storage, table, ks, vs = paged_setup(lengths, page, Hkv, hd, dtype, seed=5)
+    table = table.clone()
+    table[0, 0] = -1                      # request 0 has given its first page back to a window
+    lows = [page + 3, 0, 70]              # lowest positions read (request 0: past the page it lost)
+    items, tab = [], []
+    pages = chunks = 0
+    for r, n in enumerate(lengths):
+        first_page = lows[r] // D
+        n_pages = (n - 1) // D - first_page + 1
+        items += [r, first_page * D, n_pages * (D // page), pages, lows[r], n - 1, chunks, 0]
+        pages += n_pages
+        chunks += n_pages * (D // page)
+    scratch = torch.full((pages + 1, 1, 2, Hkv, D, hd), 7.0, dtype=dtype, device=DEV)
+    kernels.kv_gather(storage[0, 1, 0], storage[0, 1, 1], storage.stride(0), table, page,
+                      scratch[0, 0, 0], scratch[0, 0, 1], scratch.stride(0), D, Hkv, hd,
+                      torch.tensor(items, dtype=torch.int32, device=DEV), len(lengths), chunks)
+    got = scratch.float().cpu()
+    assert bool((got[pages] == 7.0).all())            # the page behind the last one: untouched
+    at = 0
+    for r, n in enumerate(lengths):
+        first_page = lows[r] // D
+        n_pages = (n - 1) // D - first_page + 1
+        for kv, src in ((0, ks[r]), (1, vs[r])):
+            want = torch.zeros(n_pages * D, Hkv, hd)
+            lo_chunk = (lows[r] // page) * page        # chunks are copied whole
+            if r == 0:
+                lo_chunk = max(lo_chunk, page)        # its first page is gone
+            a, b = max(lo_chunk, first_page * D), n
+            want[a - first_page * D:b - first_page * D] = src[a:b].float()
+            # a chunk is copied whole: positions of the last source page behind the request's
+            # end hold whatever the cache holds there (zeros in this cache)
+            have = got[at:at + n_pages, 0, kv].permute(0, 2, 1, 3).reshape(n_pages * D, Hkv, hd)
+            assert torch.equal(have, want), (r, kv)
+        at += n_pages
