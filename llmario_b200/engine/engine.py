@@ -105,12 +105,20 @@ class Engine:
             finished += plan.failed
             if not plan.entries:
                 return finished
-            cur = self._launch(plan, None)
+            try:
+                cur = self._launch(plan, None)
+            except RuntimeError as e:
+                # a launch of the step raised (a kernel refused a size, memory ran out): the
+                # step function has put its own state right; the step's requests fail
+                return finished + self._fail_plans([plan], f"step could not be launched: {e}")
         if self.lookahead:
             # queue the step after this one before waiting for this one's tokens
             ahead = self.scheduler.plan_ahead(cur.plan)
             if ahead is not None:
-                self._flying = self._launch(ahead, cur)
+                try:
+                    self._flying = self._launch(ahead, cur)
+                except RuntimeError:
+                    self._flying = None      # planned ahead only: the next iteration plans anew
         t0 = time.perf_counter()
         tokens = cur.pending.result() if cur.pending is not None else []
         self.timers["wait_s"] = self.timers.get("wait_s", 0.0) + time.perf_counter() - t0
@@ -162,7 +170,6 @@ class Engine:
         from such logits (the reference's ``Event::Error``, engine.rs:1140); so do the requests
         of a step already queued behind it, which ran on the same state.  The status words are
         cleared and recorded steps are dropped, so the engine can take new requests."""
-        failed: List[Request] = []
         plans = [cur.plan] + ([self._flying.plan] if self._flying is not None else [])
         if self._flying is not None and self._flying.pending is not None:
             self._flying.pending.result()          # let the step ahead leave the device
@@ -170,10 +177,16 @@ class Engine:
         torch.cuda.current_stream().synchronize()
         kernels.clear_status(self.model.device)
         self.runner.drop_buffers()         # a buffer kept at zero may hold partial sums
+        return self._fail_plans(plans, f"step failed on the device: {fault}")
+
+    def _fail_plans(self, plans: Sequence[StepPlan], message: str) -> List[Request]:
+        """End every request of ``plans`` that is still running with ``finish_reason ==
+        "error"``; their pages are given back."""
+        failed: List[Request] = []
         for plan in plans:
             for e in plan.entries:
                 if e.request.state != FINISHED:
-                    self.scheduler.fail(e.request, f"step failed on the device: {fault}")
+                    self.scheduler.fail(e.request, message)
                     failed.append(e.request)
         self.counters["failed_steps"] += 1
         return failed

@@ -97,7 +97,7 @@ class ModelRunner:
         self._graphs: Dict[Any, Any] = {}
         self._graph_seen: Dict[Any, Any] = {}
         self.counters = {"steps": 0, "rows": 0, "max_entries_in_step": 0, "refused_steps": 0,
-                         "graphs_recorded": 0, "graph_replays": 0, "failed_steps": 0}
+                         "graphs_recorded": 0, "graph_replays": 0, "failed_launches": 0}
         self._carried_updates: Optional[List[np.ndarray]] = None   # of a step that failed
 
     # ------------------------------------------------------------------ requests
@@ -325,7 +325,7 @@ class ModelRunner:
             if self.cache.has(r):
                 self.cache.close(r)
         self.drop_buffers()
-        self.counters["failed_steps"] += 1
+        self.counters["failed_launches"] += 1
 
     def drop_recordings(self) -> None:
         """Forget every recorded step (they are recorded again when their shapes come back)."""

@@ -113,9 +113,57 @@ def test_a_launch_that_raises_leaves_the_runner_usable(monkeypatch):
     with pytest.raises(kernels.KernelError, match="made to fail"):
         runner.step(entries)                 # crosses a page edge: new table cells were taken
     assert runner.length("a") == 14 and not runner.cache.has("b")
-    assert runner.counters["failed_steps"] == 1
+    assert runner.counters["failed_launches"] == 1
     got = runner.step(entries).cpu().numpy()
     ref = plain_logits(name, dtype, toks)
     assert_close(got[:19], ref[14:33], dtype, "after a failed launch", name)
     assert_close(got[19:], ref[4:5], dtype, "after a failed launch, new request", name)
     runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("lookahead", [False, True])
+def test_the_engine_fails_the_requests_of_a_step_that_could_not_be_launched(monkeypatch, lookahead):
+    """A launch raises inside the step function (made to, once).  When it is the step the engine
+    needs next, the engine ends that step's requests with an error and goes on; later requests
+    get the tokens a fresh engine gives them.  When it is a step that was only being queued
+    ahead, nothing is lost: the engine plans that step again in its turn."""
+    from llmario_b200 import Engine, SamplingParams, kernels
+
+    name, dtype = "D", "bfloat16"
+    params = SamplingParams(temperature=0.0, max_tokens=10)
+    prompts = [random_tokens(name, n, 80 + n) for n in (12, 30)]
+
+    def engine():
+        return Engine(model_dir(name, dtype), dtype=dtype, page_size=16, cache_tokens=512,
+                      max_requests=4, context=128, token_budget=64, lookahead=lookahead)
+
+    want = engine().generate(prompts, params)
+    eng = engine()
+    ids = [eng.add_request(p, params) for p in prompts]
+    for _ in range(3):
+        assert eng.step() == []
+    real = eng.runner._graph_step          # (decode steps are replayed: no part's forward runs)
+    state = {"fail": True}
+
+    def flaky(key, forward):
+        if state["fail"]:
+            state["fail"] = False
+            raise kernels.KernelError("made to fail")
+        return real(key, forward)
+
+    monkeypatch.setattr(eng.runner, "_graph_step", flaky)
+    finished = eng.run_until_done()
+    assert sorted(r.id for r in finished) == sorted(ids) and not state["fail"]
+    st = eng.stats()
+    if lookahead:
+        assert [eng.request(i).output for i in ids] == want
+        assert all(r.finish_reason == "length" for r in finished)
+    else:
+        assert all(r.finish_reason == "error" and "made to fail" in r.error for r in finished)
+        assert all(0 < len(r.output) < 10 for r in finished)
+    assert st["failed_launches"] == 1 and st["failed_steps"] == (0 if lookahead else 1)
+    assert st["free_pages"] == st["pages"] and not eng.has_work()
+    eng.runner.cache.check_invariants()
+    for i in ids:
+        eng.release(i)
+    assert eng.generate(prompts, params) == want
