@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Any, Dict, Optional, Type
+from typing import List, Any, Dict, Optional, Type
 
 from .spec import ConfigError, ModelSpec
 
@@ -70,9 +70,32 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
     return raw
 
 
+def _eos_ids(value) -> List[int]:
+    if isinstance(value, bool):
+        return []
+    if isinstance(value, int):
+        return [value]
+    if isinstance(value, list):
+        return [int(v) for v in value if isinstance(v, int) and not isinstance(v, bool)]
+    return []
+
+
 def load_config(model_dir: str):
-    """Read ``config.json`` of a model folder into the typed configuration of its architecture."""
+    """Read ``config.json`` of a model folder into the typed configuration of its architecture.
+    The end-of-sequence ids of ``generation_config.json``, when the folder has one, are merged
+    with those of ``config.json`` (crates/engine/formats/src/safetensors.rs:635-651)."""
     raw = read_config_json(model_dir)
+    gen_path = os.path.join(model_dir, "generation_config.json")
+    if os.path.isfile(gen_path):
+        try:
+            with open(gen_path) as f:
+                gen = json.load(f)
+        except json.JSONDecodeError as e:
+            raise ConfigError(f"{gen_path}: not valid JSON ({e})") from None
+        if isinstance(gen, dict):
+            ids = sorted(set(_eos_ids(raw.get("eos_token_id")) + _eos_ids(gen.get("eos_token_id"))))
+            if ids:
+                raw = dict(raw, eos_token_id=ids)
     return config_class(resolve_architecture(raw)).from_dict(raw)
 
 

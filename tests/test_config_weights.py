@@ -290,3 +290,21 @@ def test_decode_split_model_choices():
             assert 1 <= s <= max(1, length // 64)
             assert s == decode_splits(n, 8, length, 444, tile)
     assert decode_splits(512, 8, 1024, 444, 64) == 1                # more requests than CTAs fit
+
+
+def test_generation_config_adds_end_of_sequence_ids(tmp_path):
+    """``eos_token_id`` of config.json (an id or a list) is merged with that of
+    generation_config.json, sorted and without doubles (safetensors.rs:635-651)."""
+    import json
+    from llmario_b200.config import load_config
+    from util import config_json
+
+    raw = dict(config_json("A"), eos_token_id=7)
+    (tmp_path / "config.json").write_text(json.dumps(raw))
+    assert load_config(str(tmp_path)).eos_token_ids == (7,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [9, 7, 3], "top_k": 20}))
+    cfg = load_config(str(tmp_path))
+    assert cfg.eos_token_ids == (3, 7, 9) and cfg.to_spec().eos_token_ids == (3, 7, 9)
+    (tmp_path / "generation_config.json").write_text("{not json")
+    with pytest.raises(Exception, match="not valid JSON"):
+        load_config(str(tmp_path))
