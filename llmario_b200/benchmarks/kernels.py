@@ -206,6 +206,8 @@ def cmd_prompt_step(a) -> None:
     from ..cli import preset_config
     from ..engine import Model, ModelRunner, StepEntry
 
+    from .. import driver
+    driver.use_gather(not a.no_gather)
     model = Model.random(preset_config(a.model, a.layers), 0, "bfloat16", DEV)
     runner = ModelRunner(model, page_size=a.page_size, cache_tokens=a.tokens + 256, max_requests=2,
                          max_context=max(8192, a.tokens + 256), token_budget=a.tokens)
@@ -291,6 +293,8 @@ def main(argv=None) -> int:
     ps.add_argument("--tokens", type=int, default=2048)
     ps.add_argument("--steps", type=int, default=2)
     ps.add_argument("--page-size", type=int, default=16)
+    ps.add_argument("--no-gather", action="store_true",
+                    help="attention reads small cache pages as they are (instead of a gathered copy)")
     ps.set_defaults(fn=cmd_prompt_step)
     for s in (g, d, p):
         s.add_argument("--reps", type=int, default=20)
