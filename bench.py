@@ -171,16 +171,20 @@ def e2e_bench(engine, batch, prompt_len, steps, warmup, rng):
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
+    st0 = engine.stats()
     t0 = time.perf_counter()
     n0 = sum(len(engine.request(i).output) for i in ids)
     for _ in range(steps):
         engine.step()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
+    st1 = engine.stats()
     n1 = sum(len(engine.request(i).output) for i in ids)
     for i in ids:
         engine.abort(i)
-    return (n1 - n0) / (t1 - t0)
+    # bytes the engine copied to and from the device per step, counted where it copies them
+    copied = ((st1["h2d_bytes"] - st0["h2d_bytes"]) / steps, (st1["d2h_bytes"] - st0["d2h_bytes"]) / steps)
+    return (n1 - n0) / (t1 - t0), copied
 
 
 def prefill_bench(runner, model, tokens, rng, reps=5):
@@ -269,6 +273,7 @@ def serve_workload(args, cfg, model, pk, clocks):
         if it == args.warmup:
             first_mark = clocks.mark()
         l0 = kernels.launches
+        st0 = engine.stats()
         t0 = time.perf_counter()
         ids = [engine.add_request(p, params) for p in prompts]
         t_first, t_last = {}, {}
@@ -315,7 +320,9 @@ def serve_workload(args, cfg, model, pk, clocks):
                 "mixed_wall_s": (stamps[last_mixed] - t0) if last_mixed >= 0 else 0.0,
                 "host_share_of_mixed": host["mixed_s"] / max(1e-9, (stamps[last_mixed] - t0))
                 if last_mixed >= 0 else None,
-                "decode_roofline": roof, "launches": kernels.launches - l0})
+                "decode_roofline": roof, "launches": kernels.launches - l0,
+                "h2d_bytes_per_step": (engine.stats()["h2d_bytes"] - st0["h2d_bytes"]) / len(stamps),
+                "d2h_bytes_per_step": (engine.stats()["d2h_bytes"] - st0["d2h_bytes"]) / len(stamps)})
         for i in ids:
             engine.release(i)
     clk = clocks.summary(first_mark)
@@ -344,7 +351,8 @@ def serve_workload(args, cfg, model, pk, clocks):
         "e2e": {"value": best["aggregate_tok_s"], "unit": "tokens/s",
                 "note": "the whole workload runs through Engine.add_request / Engine.step: host "
                         "token lists in, host token ids out",
-                "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
+                "h2d_bytes_per_step": best["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": best["d2h_bytes_per_step"]},
         "gpu_launches": best["launches"], "clocks": clk, "runs": runs,
         "roofline": {"bound": "hbm", "achieved": roof["achieved"], "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": roof["frac"],
@@ -451,7 +459,7 @@ def decode_workload(args, cfg, full_layers, model, pk, clocks):
     clk = clocks.summary(mark)
     value = args.batch / (ms / 1e3)
     achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
-    e2e = e2e_bench(engine, args.batch, args.prompt_len, steps, warmup, rng)
+    e2e, copied = e2e_bench(engine, args.batch, args.prompt_len, steps, warmup, rng)
     points = {}
     point_detail = {}
     if not args.skip_points:
@@ -475,7 +483,7 @@ def decode_workload(args, cfg, full_layers, model, pk, clocks):
         p2 = prefill_record(model, prefill_bench(eng2.runner, model, T, rng), T, pk)
         d_ms, _, _ = decode_bench(eng2.runner, model, args.batch, args.prompt_len, steps, warmup,
                                   rng)
-        e2 = e2e_bench(eng2, args.batch, args.prompt_len, steps, warmup, rng)
+        e2, _ = e2e_bench(eng2, args.batch, args.prompt_len, steps, warmup, rng)
         engine_page = {"page_size": own, "value": args.batch / (d_ms / 1e3), "ms_per_step": d_ms,
                        "e2e": e2, "prefill_value": p2["value"], "prefill_ms": p2["ms"],
                        "prefill_frac": p2["frac"], "prefill_runs_ms": p2["runs_ms"]}
@@ -498,11 +506,11 @@ def decode_workload(args, cfg, full_layers, model, pk, clocks):
                    "peaks": pk["source"]},
         # per step the engine copies one int32 array (header, token id, position, request slot,
         # wanted row and the index of the token drawn on the device per request, block-table
-        # changes) and the sampler's options (10 float32 words per row capacity of 64), and reads
-        # back four status words and one token id per request
-        "e2e": {"value": e2e, "unit": "tokens/s",
-                "h2d_bytes_per_step": 4 * (16 + 5 * ((args.batch + 3) // 4 * 4)) + 4 * 10 * 64,
-                "d2h_bytes_per_step": 4 * (4 + args.batch)},
+        # changes) and, when the set of requests or a random draw changes them, the sampler's
+        # options; it reads back four status words and one token id per request.  Counted where
+        # the engine copies them.
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": copied[0],
+                "d2h_bytes_per_step": copied[1]},
         "gpu_launches": launches, "clocks": clk, "clocks_whole_run": all_clk, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},

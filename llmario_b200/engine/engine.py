@@ -233,6 +233,8 @@ class Engine:
         """Counters in the spirit of the reference's ``Stats`` (engine.rs:59-159)."""
         c = self.runner.cache
         return {**self.runner.counters, **self.scheduler.counters, **self.counters,
+                "h2d_bytes": self.runner.counters["h2d_bytes"] + self.sampler.h2d_bytes,
+                "d2h_bytes": self.sampler.d2h_bytes,
                 "cache": dict(c.counters), "free_pages": c.free_pages(),
                 "pages": [g.n_pages for g in c.groups], "running": len(self.scheduler.running),
                 "waiting": len(self.scheduler.waiting), **self.timers}

@@ -97,7 +97,8 @@ class ModelRunner:
         self._graphs: Dict[Any, Any] = {}
         self._graph_seen: Dict[Any, Any] = {}
         self.counters = {"steps": 0, "rows": 0, "max_entries_in_step": 0, "refused_steps": 0,
-                         "graphs_recorded": 0, "graph_replays": 0, "failed_launches": 0}
+                         "graphs_recorded": 0, "graph_replays": 0, "failed_launches": 0,
+                         "h2d_bytes": 0}
         self._carried_updates: Optional[List[np.ndarray]] = None   # of a step that failed
 
     # ------------------------------------------------------------------ requests
@@ -258,6 +259,7 @@ class ModelRunner:
         if device_tokens is not None:
             h[o_src:o_src + rows] = np.asarray(device_tokens[1], dtype=np.int32)
         dev[:off].copy_(host[:off], non_blocking=True)
+        self.counters["h2d_bytes"] += 4 * off     # (work items of mixed steps go by the driver)
         if device_tokens is not None:
             kernels.patch_tokens(dev[o_tok:o_tok + rows], device_tokens[0],
                                  dev[o_src:o_src + rows])

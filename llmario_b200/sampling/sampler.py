@@ -81,6 +81,8 @@ class DeviceSampler:
     def __init__(self, device):
         self.device = torch.device(device)
         self._cap = 0
+        self.h2d_bytes = 0       # bytes copied to and from the device so far
+        self.d2h_bytes = 0
 
     def _buffers(self, rows: int, triples: int):
         need = max(rows, 1)
@@ -159,6 +161,7 @@ class DeviceSampler:
             for r, s in enumerate(samplers):
                 u[r] = s.next_uniform()
             self._dev.copy_(self._host[i], non_blocking=True)
+            self.h2d_bytes += self._host[i].numel() * 4
             self._host_event[i] = torch.cuda.Event()
             self._host_event[i].record()
             self._dev_key = key
@@ -169,6 +172,7 @@ class DeviceSampler:
                 self._tri_event.synchronize()       # the copy of the draw before has left
             self._tri_host[:3 * n] = torch.tensor(tri, dtype=torch.int32)
             self._tri_dev[:3 * n].copy_(self._tri_host[:3 * n], non_blocking=True)
+            self.h2d_bytes += 12 * n
             self._tri_event = torch.cuda.Event()
             self._tri_event.record()
             kernels.apply_penalties(logits, self._tri_dev, n, d[3 * c:4 * c], d[4 * c:5 * c],
@@ -180,6 +184,7 @@ class DeviceSampler:
         self._flip ^= 1
         n = STATUS_WORDS + rows
         host[:n].copy_(self._out[:n], non_blocking=True)
+        self.d2h_bytes += 4 * n
         event = torch.cuda.Event()
         event.record()
         return PendingTokens(event, host, rows)
