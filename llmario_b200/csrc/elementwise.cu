@@ -218,6 +218,32 @@ LLM_EXPORT int llm_silu_mul(const float* gate_up, void* out, int out_dtype, int 
   return launch_status();
 }
 
+// out[t][j] += bias[j], in 32-bit, rounded once to the type of out: the bias of a projection
+// (the reference adds it after the product, crates/engine/model/src/forward.rs:810-830).
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, long long total,
+                                int width) {
+  pdl_trigger();
+  pdl_wait();
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) out[idx] = from_f32<T>(to_f32(out[idx]) + bias[idx % width]);
+}
+
+LLM_EXPORT int llm_add_bias(void* out, int dtype, const float* bias, int rows, int width,
+                            cudaStream_t stream) {
+  const long long total = (long long)rows * width;
+  if (total <= 0) return 0;
+  const int threads = 256;
+  const long long want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  if (dtype == LLM_F32)
+    return launch_pdl(add_bias_kernel<float>, blocks, threads, 0, stream, (float*)out, bias, total, width);
+  if (dtype == LLM_BF16)
+    return launch_pdl(add_bias_kernel<bf16>, blocks, threads, 0, stream, (bf16*)out, bias, total, width);
+  return LLM_ERR_UNSUPPORTED;
+}
+
 // Scatter (row, column, value) triples into a table of block ids kept on the device.
 __global__ void table_update_kernel(int* __restrict__ table, int row_stride,
                                     const int* __restrict__ updates, int n) {

@@ -23,7 +23,7 @@ from ..parts.attention import Attention
 from ..parts.block import PreNormResidualBlock
 from ..parts.feed_forward import SwiGLU
 from ..parts.norm import RmsNorm
-from ..parts.position import RotaryHalfSplit
+from ..parts.position import RotaryAdjacentPairs, RotaryHalfSplit
 
 
 def describe_block(block, shared_tables: Dict[Tuple, torch.Tensor]) -> Optional[LayerDesc]:
@@ -37,8 +37,10 @@ def describe_block(block, shared_tables: Dict[Tuple, torch.Tensor]) -> Optional[
         return None
     if type(block.mixer_norm) is not RmsNorm or type(block.ffn_norm) is not RmsNorm:
         return None
-    if m.position is not None and type(m.position) is not RotaryHalfSplit:
-        return None
+    if m.position is not None and type(m.position) not in (RotaryHalfSplit, RotaryAdjacentPairs):
+        return None         # (adjacent pairs: the mixer has ordered its rows for the kernels' pairs)
+    if any(lin.bias is not None for lin in (m.qkv_proj, m.o_proj, f.gate_up, f.down)):
+        return None         # a bias is a launch of its own behind the product: the part's forward
     if m.q_norm is not None and (type(m.q_norm) is not RmsNorm or type(m.k_norm) is not RmsNorm):
         return None
     d = LayerDesc()

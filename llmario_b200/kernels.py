@@ -42,6 +42,7 @@ def _signatures():
         "llm_rms_norm": [P, P, P, I, P, I, I, F, P],
         "llm_patch_tokens": [P, P, P, I, P],
         "llm_silu_mul": [P, P, I, I, I, P],
+        "llm_add_bias": [P, I, P, I, I, P],
         "llm_table_update": [P, I, P, I, P],
         "llm_table_update_counted": [P, I, P, P, I, P],
         "llm_zero_slots": [P, L, P, P, I, P],
@@ -162,6 +163,14 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     assert gate_up.shape == (rows, 2 * ff)
     _check(lib().llm_silu_mul(_ptr(gate_up), _ptr(out), _dt(out), rows, ff, _stream()),
            "silu_mul")
+
+
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
+    """out[t][j] += bias[j] (bias float32; the sum is made in 32-bit and rounded once)."""
+    _cuda(out, bias)
+    rows, width = out.shape
+    assert out.is_contiguous() and bias.dtype == torch.float32 and bias.shape == (width,)
+    _check(lib().llm_add_bias(_ptr(out), _dt(out), _ptr(bias), rows, width, _stream()), "add_bias")
 
 
 def table_update(table: torch.Tensor, updates: torch.Tensor, n: int) -> None:

@@ -15,7 +15,8 @@ import torch
 from .. import driver, kernels
 from ..cache import PagedKV
 from ..config.spec import ConfigError, PartSpec
-from .base import BoundCall, StepContext, build_part, register_part, tensor_of
+from .base import (BoundCall, StepContext, build_part, optional_tensor_of, register_part,
+                   tensor_of)
 from .linear import Linear
 
 
@@ -43,9 +44,29 @@ class Attention:
             raise ValueError("q_norm and k_norm come together")
         if self.q_norm is not None and self.q_norm.eps != self.k_norm.eps:
             raise ValueError("q_norm and k_norm must share eps")
-        self.qkv_proj = Linear.stacked([tensor_of(spec, r, weights) for r in ("q", "k", "v")])
-        self.q_proj = Linear(self.qkv_proj.weight[:self.q_width])   # the first rows, no copy
-        self.o_proj = Linear(tensor_of(spec, "o", weights))
+        w = {r: tensor_of(spec, r, weights) for r in ("q", "k", "v")}
+        # biases exist for the families that store them (forward.rs:399-425); tensor roles
+        # "q_bias", "k_bias", "v_bias", "o_bias", each optional
+        b = {r: optional_tensor_of(spec, r + "_bias", weights) for r in ("q", "k", "v", "o")}
+        perm = self.position.head_permutation(self.head_dim) \
+            if hasattr(self.position, "head_permutation") else None
+        if perm is not None:
+            # The position encoding rotates other pairs of a head than the kernels do.  A head's
+            # scores do not change when queries and keys are permuted alike, so the rows of the
+            # q and k projections (and what follows them per head: bias, norm gain) are permuted
+            # once here and the kernels rotate their own pairs.
+            perm = perm.to(device)
+            for r, heads in (("q", self.num_heads), ("k", self.num_kv_heads)):
+                w[r] = w[r].view(heads, self.head_dim, -1)[:, perm].reshape(w[r].shape)
+                if b[r] is not None:
+                    b[r] = b[r].view(heads, self.head_dim)[:, perm].reshape(-1)
+            for norm in (self.q_norm, self.k_norm):
+                if norm is not None:
+                    norm.weight = norm.weight[perm].contiguous()
+        self.qkv_proj = Linear.stacked([w["q"], w["k"], w["v"]], [b["q"], b["k"], b["v"]])
+        self.q_proj = Linear(self.qkv_proj.weight[:self.q_width],      # the first rows, no copy
+                             None if self.qkv_proj.bias is None else self.qkv_proj.bias[:self.q_width])
+        self.o_proj = Linear(tensor_of(spec, "o", weights), b["o"])
 
     def cache_need(self):
         return PagedKV(self.num_kv_heads, self.head_dim, self.window)

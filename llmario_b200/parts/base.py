@@ -10,7 +10,9 @@ Interfaces (``ctx`` is the :class:`StepContext` of the running step):
 
 * norm          ``apply(ctx, x_f32[rows, width], out[rows, width], rows_index=None)``
 * position      ``rotary_tables()`` -> (inv_freq, rot_dim, attn_factor) for a rotation that the
-                fused kernel applies, or ``None`` together with ``apply(ctx, heads_f32, n_heads)``
+                fused kernel applies, or ``None`` together with ``apply(ctx, heads_f32, n_heads)``;
+                optionally ``head_permutation(head_dim)`` -> the order in which a head's values
+                must stand for the kernels' pairs (i, i + rot_dim/2) to be this encoding's pairs
 * mixer         ``cache_need()`` -> PagedKV | FixedState | None;
                 ``forward(ctx, call, h[rows, hidden], x_f32[rows, hidden])`` adds its output to x
 * feed_forward  ``forward(ctx, h[rows, hidden], x_f32[rows, hidden])`` adds its output to x
@@ -60,6 +62,13 @@ def tensor_of(spec: PartSpec, role: str, weights: Dict[str, torch.Tensor]) -> to
     """The loaded tensor that ``spec`` names for ``role``."""
     name = spec["tensors"][role][0]
     return weights[name]
+
+
+def optional_tensor_of(spec: PartSpec, role: str, weights: Dict[str, torch.Tensor]
+                       ) -> Optional[torch.Tensor]:
+    """The loaded tensor for ``role``, or None when ``spec`` names none."""
+    entry = spec["tensors"].get(role)
+    return None if entry is None else weights[entry[0]]
 
 
 @dataclass

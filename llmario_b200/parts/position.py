@@ -1,7 +1,8 @@
-"""Rotary position encoding, half-split pairing (i, i + rot_dim/2):
-``freq_i = theta^(-2i/rot_dim)``, ``angle = pos * freq_scale * freq_i``, all in 32-bit
-(crates/engine/cpu/src/ops.rs:46-66, ``RopeKind::Neox``).  The rotation itself is applied by the
-kernel that also norms the heads and writes the cache; this part owns the constants."""
+"""Rotary position encoding: ``freq_i = theta^(-2i/rot_dim)``, ``angle = pos * freq_scale *
+freq_i``, all in 32-bit (crates/engine/cpu/src/ops.rs:46-66).  The pair that angle i turns is
+(i, i + rot_dim/2) for ``rope_neox`` (``RopeKind::Neox``) and (2i, 2i + 1) for ``rope_normal``
+(``RopeKind::Normal``, ops.rs:57-60).  The rotation itself is applied by the kernel that also
+norms the heads and writes the cache; this part owns the constants."""
 from __future__ import annotations
 
 from typing import Dict, Optional, Tuple
@@ -44,4 +45,21 @@ class RotaryHalfSplit:
         return table
 
 
+class RotaryAdjacentPairs(RotaryHalfSplit):
+    """Angle i turns the pair (2i, 2i + 1).  The kernels turn (i, i + rot_dim/2); the mixer
+    therefore orders each head of its query and key projections by :meth:`head_permutation`
+    when it is built (scores do not depend on the order in which a head's values stand, as long
+    as queries and keys stand alike), and nothing else changes."""
+
+    def head_permutation(self, head_dim: int) -> torch.Tensor:
+        """``perm`` with ``stored[j] = original[perm[j]]``: the even members of the rotated
+        pairs first, then the odd ones, then what is not rotated."""
+        half = self.rot_dim // 2
+        perm = list(range(0, self.rot_dim, 2)) + list(range(1, self.rot_dim, 2)) \
+            + list(range(self.rot_dim, head_dim))
+        assert len(perm) == head_dim and perm[half] == 1
+        return torch.tensor(perm, dtype=torch.long)
+
+
 register_part("position", "rope_neox", RotaryHalfSplit, replace=True)
+register_part("position", "rope_normal", RotaryAdjacentPairs, replace=True)

@@ -83,9 +83,11 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return x * scale * w
 
 
-def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """y = W x with W stored [out][in], no bias (forward.rs:810-830)."""
-    return x @ w.t()
+def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = W x (+ b) with W stored [out][in] (forward.rs:810-830; this architecture has no
+    biases, a layer that has them adds them after the product: forward.rs:399-425)."""
+    y = x @ w.t()
+    return y if b is None else y + b
 
 
 def per_head_norm(x: torch.Tensor, w: torch.Tensor, eps: float, n_heads: int) -> torch.Tensor:
@@ -109,6 +111,25 @@ def rope_neox(x: torch.Tensor, positions: torch.Tensor, n_heads: int, head_dim: 
     xh = x.reshape(t, n_heads, head_dim)
     a, b = xh[..., :half], xh[..., half:]
     out = torch.cat([a * cos - b * sin, a * sin + b * cos], dim=-1)
+    return out.reshape(t, n_heads * head_dim)
+
+
+def rope_normal(x: torch.Tensor, positions: torch.Tensor, n_heads: int, head_dim: int,
+                rot_dim: int, theta: float, freq_scale: float = 1.0,
+                attn_factor: float = 1.0) -> torch.Tensor:
+    """Adjacent-pair rotation: angle i turns the pair (2i, 2i+1) of the first ``rot_dim`` values
+    of a head; freq = theta^(-2i/rot_dim), angle = pos * freq_scale * freq, cosine and sine
+    times ``attn_factor`` (ops.rs:46-66 with RopeKind::Normal, :57-60).  Not used by this
+    architecture: it checks the position part of that kind."""
+    t = x.shape[0]
+    out = x.reshape(t, n_heads, head_dim).clone()
+    for i in range(rot_dim // 2):
+        freq = theta ** (-(2.0 * i) / rot_dim)
+        angle = positions.to(x.dtype) * freq_scale * freq
+        cos, sin = torch.cos(angle)[:, None] * attn_factor, torch.sin(angle)[:, None] * attn_factor
+        x0, x1 = out[:, :, 2 * i].clone(), out[:, :, 2 * i + 1].clone()
+        out[:, :, 2 * i] = x0 * cos - x1 * sin
+        out[:, :, 2 * i + 1] = x0 * sin + x1 * cos
     return out.reshape(t, n_heads * head_dim)
 
 

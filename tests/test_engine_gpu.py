@@ -707,3 +707,87 @@ def test_a_toy_feed_forward_with_routing_and_a_toy_position_encoding():
     finally:
         unregister_part("feed_forward", "top_one_of_two")
         unregister_part("position", "interpolated_partial")
+
+
+# ------------------------------------------- options of the standard parts this architecture leaves off
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_projection_biases_and_adjacent_pair_rotation(dtype):
+    """Two options that the standard parts take as data although this architecture uses
+    neither: biases of the q, k, v and output projections (added after the product,
+    forward.rs:399-425) and the rotation of adjacent pairs (2i, 2i+1) (``RopeKind::Normal``,
+    ops.rs:57-60), here on part of a head, with scaled positions and a factor on cosine and
+    sine.  Layer 0 has the other rotation only and runs through the native step driver; layer
+    1 has both and runs through the parts' own forward.  Compared with the formulas in float64,
+    in portions, in a mixed step and token by token."""
+    from llmario_b200.config import PartSpec, load_spec
+    from llmario_b200.engine import Model, ModelRunner, StepEntry
+    from llmario_b200.weights import expected_tensors, random_tensors
+
+    name = "D"
+    base = load_spec(model_dir(name, dtype))
+    cfg = P.read_config(model_dir(name, dtype))
+    hq, hkv, hd, eps = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["eps"]
+    rotation = [dict(rot_dim=hd, theta=cfg["theta"], freq_scale=1.0, attn_factor=1.0),
+                dict(rot_dim=hd // 2, theta=3000.0, freq_scale=0.5, attn_factor=1.125)]
+    layers = list(base.layers)
+    for l in range(2):
+        params = dict(layers[l].mixer.params)
+        params["position"] = PartSpec("rope_normal", rotation[l])
+        if l == 1:
+            a = "model.layers.1.self_attn."
+            tensors = dict(params["tensors"])
+            for r, width in (("q", hq * hd), ("k", hkv * hd), ("v", hkv * hd), ("o", base.hidden_size)):
+                tensors[r + "_bias"] = (a + r + "_proj.bias", (width,))
+            params["tensors"] = tensors
+        layers[l] = dataclasses.replace(layers[l], mixer=dataclasses.replace(layers[l].mixer,
+                                                                             params=params))
+    spec = dataclasses.replace(base, layers=tuple(layers))
+    assert "model.layers.1.self_attn.k_proj.bias" in expected_tensors(spec)
+    tdtype = getattr(torch, dtype)
+    weights = random_tensors(spec, 21, tdtype, DEV)
+    gen = torch.Generator().manual_seed(5)
+    for n in list(weights):
+        if n.endswith(".bias"):      # (the seeded generator makes gains near one for 1-D tensors)
+            weights[n] = (0.4 * torch.randn(weights[n].shape, generator=gen)).to(DEV)
+    host = {k: v.double().cpu() for k, v in weights.items()}
+    runner = ModelRunner(Model(spec, weights, tdtype, DEV), page_size=16, n_pages=24,
+                         max_requests=3, max_context=128)
+    assert runner.native is not None and runner.native.native_layer == [True, False]
+
+    def reference(tokens):
+        xx = P.embed(host["model.embed_tokens.weight"], tokens)
+        pos = torch.arange(len(tokens))
+        for l in range(2):
+            p = f"model.layers.{l}."
+            a, rot = p + "self_attn.", rotation[l]
+            h = P.rms_norm(xx, host[p + "input_layernorm.weight"], eps)
+            proj = {r: P.linear(h, host[a + r + "_proj.weight"], host.get(a + r + "_proj.bias"))
+                    for r in ("q", "k", "v")}
+            q = P.per_head_norm(proj["q"], host[a + "q_norm.weight"], eps, hq)
+            k = P.per_head_norm(proj["k"], host[a + "k_norm.weight"], eps, hkv)
+            turn = lambda t, heads: P.rope_normal(t, pos, heads, hd, rot["rot_dim"], rot["theta"],
+                                                  rot["freq_scale"], rot["attn_factor"])
+            att = P.attention(turn(q, hq), turn(k, hkv), proj["v"], hq, hkv, hd,
+                              cfg["windows"][l], pos)
+            xx = xx + P.linear(att, host[a + "o_proj.weight"], host.get(a + "o_proj.bias"))
+            h = P.rms_norm(xx, host[p + "post_attention_layernorm.weight"], eps)
+            xx = xx + P.swiglu_ffn(h, host[p + "mlp.gate_proj.weight"],
+                                   host[p + "mlp.up_proj.weight"], host[p + "mlp.down_proj.weight"])
+        return P.linear(P.rms_norm(xx, host["model.norm.weight"], eps),
+                        host["lm_head.weight"]).numpy()
+
+    a, b = random_tokens(name, 45, 31), random_tokens(name, 27, 32)
+    toks, got = {"a": a, "b": b}, {"a": [], "b": []}
+    plan = [[("a", 0, 19)], [("a", 19, 14), ("b", 0, 17)], [("a", 33, 2), ("b", 17, 1)]]
+    plan += [[("a", 35 + i, 1), ("b", 18 + i, 1)] for i in range(9)]       # recorded decode steps
+    plan += [[("a", 44, 1)]]
+    for step in plan:
+        entries = [StepEntry(r, toks[r][s:s + n], list(range(n))) for r, s, n in step]
+        out = runner.step(entries).cpu().numpy()
+        at = 0
+        for r, s, n in step:
+            got[r].append(out[at:at + n])
+            at += n
+    assert runner.counters["graph_replays"] >= 5
+    assert_close(np.concatenate(got["a"]), reference(a), dtype, "biases, adjacent pairs a", name)
+    assert_close(np.concatenate(got["b"]), reference(b), dtype, "biases, adjacent pairs b", name)

@@ -35,6 +35,16 @@ def test_rms_norm(rows, width, out_dtype):
     assert torch.equal(out2, out.flip(0))
 
 
+@pytest.mark.parametrize("rows,width", [(1, 24), (9, 1000), (700, 4097)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_bias(rows, width, dtype):
+    from llmario_b200 import kernels
+    out, bias = rnd(rows, width, dtype=dtype, scale=2.0), rnd(width, seed=3)
+    want = (out.float() + bias).to(dtype)      # the sum in 32-bit, rounded once
+    kernels.add_bias(out, bias)
+    assert torch.equal(out, want)
+
+
 @pytest.mark.parametrize("vocab,width", [(50, 24), (1000, 520)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_embed(vocab, width, dtype):

@@ -32,6 +32,33 @@ def test_rope_identity_at_zero_and_norm_kept():
     assert r[[1, 2, 3, 4, 5, 6, 7, 9]].abs().max() == 0
 
 
+def test_adjacent_pairs_are_half_split_pairs_of_a_permuted_head():
+    """The position part for adjacent pairs gives the order in which a head's values must stand
+    for the half-split rotation to turn its pairs: rotating the permuted head and undoing the
+    permutation is the adjacent-pair rotation (ops.rs:57-60), also with part of a head rotated."""
+    from llmario_b200.config import PartSpec
+    from llmario_b200.parts.position import RotaryAdjacentPairs
+    heads, hd, theta = 3, 16, 500.0
+    x = torch.randn(5, heads * hd, dtype=torch.float64, generator=torch.Generator().manual_seed(1))
+    pos = torch.tensor([0, 1, 7, 30, 31])
+    for rot in (hd, 8):
+        part = RotaryAdjacentPairs(PartSpec("rope_normal", {"rot_dim": rot, "theta": theta}), {},
+                                   torch.float32, "cpu")
+        perm = part.head_permutation(hd)
+        assert sorted(perm.tolist()) == list(range(hd))
+        xp = x.reshape(5, heads, hd)[:, :, perm]
+        turned = xp.clone()
+        turned[:, :, :rot] = P.rope_neox(xp[:, :, :rot].reshape(5, heads * rot), pos, heads, rot,
+                                         theta).reshape(5, heads, rot)
+        back = torch.empty_like(turned)
+        back[:, :, perm] = turned
+        want = P.rope_normal(x, pos, heads, hd, rot, theta)
+        assert (back.reshape(5, heads * hd) - want).abs().max() < 1e-12
+        # the frequencies the kernels get are the formula's, in 32-bit
+        i = torch.arange(rot // 2, dtype=torch.float64)
+        assert torch.allclose(part.inv_freq.double(), theta ** (-(2.0 * i) / rot), rtol=1e-6)
+
+
 def test_attention_is_causal_grouped_and_windowed():
     T, Hq, Hkv, hd = 9, 4, 2, 8
     q, k, v = (torch.randn(T, n * hd, dtype=torch.float64) for n in (Hq, Hkv, Hkv))
