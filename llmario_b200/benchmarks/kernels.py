@@ -54,6 +54,7 @@ def timed(fn, reps: int, flush, chain: int = 1) -> float:
 def cmd_gemm(a) -> None:
     T, N, K = a.rows, a.out, getattr(a, "in")
     kernels.use_cta_pairs(not a.one_cta)
+    kernels.force_pair_k_ranges(a.k_ranges)
     x = torch.randn(T, K, device=DEV).bfloat16()
     w = (0.02 * torch.randn(N, K, device=DEV)).bfloat16()
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
@@ -173,6 +174,7 @@ def cmd_step(a) -> None:
 
     from .. import driver
     driver.use_persistent_decode(a.persistent)
+    kernels.use_dependent_launch(not a.no_dependent_launch)
     model = Model.random(preset_config(a.model, a.layers), 0, "bfloat16", DEV)
     runner = ModelRunner(model, page_size=a.page_size, cache_tokens=a.batch * (a.context + 256),
                          max_requests=max(a.batch, 8), max_context=8192, use_graphs=not a.eager)
@@ -245,6 +247,9 @@ def main(argv=None) -> int:
     g.add_argument("--splits", type=int, default=1)
     g.add_argument("--one-cta", action="store_true",
                    help="many rows: the one-CTA persistent kernel instead of CTA pairs")
+    g.add_argument("--k-ranges", type=int, default=0,
+                   help="ranges of K in the CTA-pair product that adds into its output "
+                        "(0: its own cost model chooses)")
     g.add_argument("--f32", action="store_true")
     g.add_argument("--interleaved", action="store_true",
                    help="gated mode: the matrix holds alternating blocks of 16 gate and 16 up rows")
@@ -284,6 +289,8 @@ def main(argv=None) -> int:
     st.add_argument("--steps", type=int, default=4)
     st.add_argument("--page-size", type=int, default=16)
     st.add_argument("--eager", action="store_true", help="no CUDA graphs")
+    st.add_argument("--no-dependent-launch", action="store_true",
+                    help="every kernel waits for the end of the one before it")
     st.add_argument("--persistent", action="store_true",
                     help="decode attention by the persistent kernel where its CTAs make one to five waves")
     st.set_defaults(fn=cmd_step)

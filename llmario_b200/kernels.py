@@ -431,6 +431,24 @@ def use_cta_pairs(on: bool) -> None:
     l.llm_set_pair(int(on))
 
 
+def force_pair_k_ranges(n: int) -> None:
+    """Cut K into ``n`` ranges in the CTA-pair product that adds into its output, whatever its
+    own cost model would choose; 0 gives the choice back to the model.  For measurements."""
+    l = lib()
+    l.llm_set_pair_ksplits.argtypes = [c_int]
+    l.llm_set_pair_ksplits.restype = None
+    l.llm_set_pair_ksplits(int(n))
+
+
+def use_dependent_launch(on: bool) -> None:
+    """Whether kernels are launched as programmatic dependents of the one before them (the
+    default) or wait for its end.  For measurements."""
+    l = lib()
+    l.llm_set_pdl.argtypes = [c_int]
+    l.llm_set_pdl.restype = None
+    l.llm_set_pdl(int(on))
+
+
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, half: int = 0,
                  bn: Optional[int] = None, splits: int = 1, out_is_zero: bool = False) -> None:
     """Tensor-core product of bfloat16 operands.  mode 0: out = a w^T (bfloat16 or float32);
