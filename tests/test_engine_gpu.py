@@ -261,6 +261,58 @@ def test_many_requests_with_few_pages_give_the_same_tokens_either_way():
     assert st1.get("steps_planned_ahead", 0) > 10 and st0["preemptions"] > 0 and st1["preemptions"] > 0
 
 
+@pytest.mark.parametrize("every,cache_tokens", [(2, 400), (8, 400), (12, 2048)])
+def test_requests_arrive_and_are_aborted_while_others_run(every, cache_tokens):
+    """Requests arrive over time (one in ``every`` iterations), a few are aborted at random
+    moments (also while a step that was queued ahead is in flight), the sampling options are
+    mixed, and with the small cache requests are preempted.  Every request that was not aborted
+    gets the tokens it gets alone in an engine of its own; no page is lost on the way."""
+    from llmario_b200 import Engine, SamplingParams
+    name, dtype, n = "D", "float32", 90
+    rng = random.Random(every * 1000 + cache_tokens)
+    prompts = [random_tokens(name, rng.randint(1, 140), 5000 + i) for i in range(n)]
+    params = [SamplingParams(temperature=0.0 if rng.random() < 0.6 else rng.choice([0.5, 1.0, 1.3]),
+                             top_k=rng.choice([0, 5, 40]), top_p=rng.choice([1.0, 0.9]),
+                             min_p=rng.choice([0.0, 0.05]), seed=900 + i,
+                             repeat_penalty=rng.choice([1.0, 1.1]),
+                             frequency_penalty=rng.choice([0.0, 0.2]),
+                             max_tokens=rng.randint(1, 70)) for i in range(n)]
+    eng = Engine(model_dir(name, dtype), dtype=dtype, page_size=16, cache_tokens=cache_tokens,
+                 max_requests=6, context=256, token_budget=48, lookahead=True)
+    ids, aborted, nxt, steps = {}, set(), 0, 0
+    while nxt < n or eng.has_work():
+        if nxt < n and rng.random() < 1.0 / every:
+            ids[nxt] = eng.add_request(prompts[nxt], params[nxt])
+            nxt += 1
+        if eng.has_work():
+            eng.step()
+            steps += 1
+        if ids and rng.random() < 0.04:
+            k = rng.choice(list(ids))
+            if eng.request(ids[k]).finish_reason is None:
+                eng.abort(ids[k])
+                aborted.add(k)
+        if steps % 64 == 0:
+            eng.runner.cache.check_invariants()
+    cache, st = eng.runner.cache, eng.stats()
+    cache.check_invariants()
+    assert min(cache.free_pages()) == cache.groups[0].n_pages and not cache.live_requests()
+    assert st["failed_steps"] == 0 and aborted and len(aborted) < n // 2
+    if cache_tokens < 1000:
+        assert st["preemptions"] > 0
+    if every >= 8:
+        assert st["steps_planned_ahead"] > 0
+    alone = Engine(model_dir(name, dtype), dtype=dtype, page_size=16, cache_tokens=1024,
+                   max_requests=2, context=256, token_budget=256, lookahead=False)
+    for k in range(n):
+        r = eng.request(ids[k])
+        if k in aborted:
+            assert r.finish_reason == "aborted"
+            continue
+        assert r.finish_reason == "length" and len(r.output) == params[k].max_tokens
+        assert list(r.output) == alone.generate([prompts[k]], [params[k]])[0], f"request {k}"
+
+
 @pytest.mark.parametrize("lookahead", [False, True])
 def test_preemption_by_recompute_in_bfloat16(lookahead):
     """Thirty greedy requests in bfloat16 through a cache that holds a fraction of them (head
