@@ -44,7 +44,9 @@ struct alignas(1024) AttnStorage {
   uint64_t q_empty;                            // persistent form: the last scores of a work item are done
   uint64_t o_free;                             // persistent form: the softmax warps have read the output
   uint32_t tmem_base;
-  int dead;
+  int dead;                                    // a bounded wait gave up somewhere in the CTA
+  int stop[2];                                 // the copy of `dead` that the softmax warps act on, per tile parity
+  float xmax[2][ROWS];                         // two threads per row: the maxima of their halves of a tile
 };
 
 // SPLIT: two threads per row, each with 64 of a tile's 128 score columns (warps 2-5 the first
@@ -276,7 +278,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
     const int rpos = it.pos_start + tok;
     const int rlo = (window > 0 && rpos + 1 > window) ? rpos + 1 - window : 0;
     const uint32_t pair_bar = 2 + q4;                    // named barrier of the two warps of a quarter
-    const uint32_t x_addr = tmem + lane_base + O_COL + HD;   // spare columns: maxima and sums exchanged
+    const uint32_t x_addr = tmem + lane_base + O_COL + HD;   // spare columns: the sums of the two halves of a row meet here
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     pdl_wait();
@@ -284,9 +286,14 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
       const int b = j & 1;
       ok = mbar_wait(&sm.s_full[b], (uint32_t)((j >> 1) & 1));
       if (!ok) { if (lane == 0) atomicExch(status, 7); sm.dead = 1; }
+      // All softmax warps go on or all stop: one thread copies the flag before the barrier and
+      // all read the copy behind it (a warp that read the flag itself could see another value
+      // than its neighbour and leave it alone at the next barrier).  A wait that gives up after
+      // the copy was made stops the CTA one tile later.
+      if (threadIdx.x == 64) *(volatile int*)&sm.stop[b] = *(volatile int*)&sm.dead;
       if (SPLIT) asm volatile("bar.sync 1, 256;" ::: "memory");
       else asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (sm.dead) { ok = false; break; }
+      if (*(volatile int*)&sm.stop[b]) { ok = false; break; }
       tc_fence_after();
       const uint32_t s_addr = tmem + lane_base + (uint32_t)b * S_COLS;
       const int base = (tile_first + j) * KT;
@@ -317,17 +324,12 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
       }
       float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       if (SPLIT) {
-        // The two threads of a row share a TMEM lane: they pass their maxima through spare
-        // columns behind the output.  (The column of parity b is written again two tiles on,
-        // after the barrier of the tile between, by which time the partner has read it.)
-        tmem_st1(x_addr + (uint32_t)(b * 2 + half), __float_as_uint(m_tile));
-        tmem_st_wait();
-        tc_fence_before();
+        // The two threads of a row pass the maxima of their halves through shared memory.  (A
+        // thread writes its word again in the next tile, behind that tile's barrier of all
+        // softmax warps, which its partner reaches only after this read.)
+        sm.xmax[half][row] = m_tile;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-        tc_fence_after();
-        const uint32_t other = tmem_ld1(x_addr + (uint32_t)(b * 2 + (half ^ 1)));
-        tmem_ld_wait();
-        m_tile = fmaxf(m_tile, __uint_as_float(other));
+        m_tile = fmaxf(m_tile, sm.xmax[half ^ 1][row]);
       }
       m_tile *= scale_log2;
       // the scale in use is replaced only when the maximum has grown by more than 2^8
@@ -634,7 +636,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
     const int q4 = warp & 3;
     const int row = q4 * 32 + lane;
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
-    const uint32_t x_addr = tmem + lane_base + O_COL + HD;   // spare columns: maxima and sums exchanged
+    const uint32_t x_addr = tmem + lane_base + O_COL + HD;   // spare columns: the sums of the two halves of a row meet here
     auto pair_sync = [&]() {      // the two warps of a quarter (immediate ids: six barriers in all)
       if (q4 == 0) asm volatile("bar.sync 2, 64;" ::: "memory");
       else if (q4 == 1) asm volatile("bar.sync 3, 64;" ::: "memory");
@@ -656,18 +658,10 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
         const int b = (int)(T & 1);
         ok = mbar_wait(&sm.s_full[b], (T >> 1) & 1);
         if (!ok) { if (lane == 0) atomicExch(status, 7); sm.dead = 1; }
-        // the eight warps decide together whether to go on (a barrier that also combines their
-        // votes: all see the same answer, so none is left waiting at the next one)
-        uint32_t stop;
-        asm volatile(
-            "{\n\t.reg .pred p, q;\n\t"
-            "setp.ne.u32 q, %1, 0;\n\t"
-            "barrier.cta.red.or.pred p, 1, 256, q;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(stop)
-            : "r"((uint32_t)(!ok || sm.dead))
-            : "memory");
-        if (stop) { ok = false; break; }
+        // all eight warps go on or all stop (see the kernel above)
+        if (threadIdx.x == 64) *(volatile int*)&sm.stop[b] = *(volatile int*)&sm.dead;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (*(volatile int*)&sm.stop[b]) { ok = false; break; }
         tc_fence_after();
         const uint32_t s_addr = tmem + lane_base + (uint32_t)b * S_COLS;
         const int base = (w.tile_first + j) * KT;
@@ -693,14 +687,9 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
           mx[3] = fmaxf(mx[3], __uint_as_float(v[i + 3]));
         }
         float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        tmem_st1(x_addr + (uint32_t)(b * 2 + half), __float_as_uint(m_tile));
-        tmem_st_wait();
-        tc_fence_before();
+        sm.xmax[half][row] = m_tile;             // the partner's half of the row: through shared memory
         pair_sync();
-        tc_fence_after();
-        const uint32_t other = tmem_ld1(x_addr + (uint32_t)(b * 2 + (half ^ 1)));
-        tmem_ld_wait();
-        m_tile = fmaxf(m_tile, __uint_as_float(other)) * scale_log2;
+        m_tile = fmaxf(m_tile, sm.xmax[half ^ 1][row]) * scale_log2;
         const bool grow = m_tile > m_used + 8.0f;
         float factor = 1.f;
         if (grow) {
