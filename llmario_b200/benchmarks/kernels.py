@@ -96,7 +96,7 @@ def cmd_attention(a) -> None:
     slot = torch.arange(B, dtype=torch.int32, device=DEV)
     pos = torch.full((B,), S - 1, dtype=torch.int32, device=DEV)
     tma = not (a.row_major or a.cp_async)
-    splits = a.splits or kernels.decode_splits(B, Hkv, S, (3 if tma else 6) * kernels.sm_count(),
+    splits = a.splits or kernels.decode_splits(B, Hkv, S, (kernels.DECODE_TMA_CTAS_PER_SM if tma else 6) * kernels.sm_count(),
                                                kernels.DECODE_TMA_TILE if tma else 32)
     po = torch.empty(B * Hq * splits * hd, dtype=torch.float32, device=DEV)
     pml = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=DEV)

@@ -9,13 +9,15 @@
 // tile load brings the keys and the values of a page and KV head: up to 64 positions, 8 KB for a
 // page of 16 at head size 128.  The TMA unit spends about the same time on a load whatever its
 // size, so few large loads are what lets a warp stream at the memory's speed.  The bytes are
-// counted on an mbarrier per stage of a ring of two tiles of 64 keys; the warp spends its
+// counted on an mbarrier per stage of a ring of three tiles of 32 keys (four such CTAs to an SM
+// at head size 128: the same bytes in flight as three CTAs with two tiles of 64 keys, but a
+// fourth warp to work on them, which streams a tenth to a sixth faster); the warp spends its
 // instructions on the products and not on addresses.  Head sizes 64 and 128; other sizes use attention_decode.cu.
 #include "attention_common.cuh"
 #include "tcgen05.cuh"
 
 namespace {
-constexpr int DECODE_KT = 64, DECODE_STAGES = 2;   // keys of a tile, tiles in flight per warp
+constexpr int DECODE_KT = 32, DECODE_STAGES = 3;   // keys of a tile, tiles in flight per warp
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
   uint32_t r;
@@ -49,7 +51,7 @@ struct Fused {
 };                          // split keys several CTAs read it and the merge clears it)
 
 template <int HD, int KT, int STAGES, bool FUSED>
-__global__ void __launch_bounds__(32, 3) flash_decode_tma_kernel(
+__global__ void __launch_bounds__(32, 4) flash_decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, bf16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ items, const int* __restrict__ row_slot,
@@ -447,7 +449,7 @@ struct Cursor {       // a tile of the CTA's run and the unit it belongs to
 };
 
 template <int HD, int KT, int STAGES>
-__global__ void __launch_bounds__(32, 3) flash_decode_persistent_kernel(
+__global__ void __launch_bounds__(32, 4) flash_decode_persistent_kernel(
     const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, float* __restrict__ part_o,
     float* __restrict__ part_ml, const int* __restrict__ block_table, int table_stride,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, int rows, int Hq, int Hkv, int page_size,

@@ -101,7 +101,8 @@ namespace {
 // policies (the same numbers as llmario_b200/kernels.py)
 // ------------------------------------------------------------------------------------------------
 constexpr int SPLIT_K_MAX_ROWS = 256;       // up to here the q/k/v destination is kept at zero
-constexpr int DECODE_TMA_TILE = 64;         // keys of a tile of attention_decode_tma.cu
+constexpr int DECODE_TMA_TILE = 32;         // keys of a tile of attention_decode_tma.cu
+constexpr int DECODE_TMA_CTAS_PER_SM = 4;   // its one-warp CTAs that fit an SM at head size 128 (three tiles of 16 KB each)
 constexpr int PERSISTENT_ATTENTION_MAX_KEYS = 6144;
 // Prompt portions over a cache with small pages: the request's keys and values are first
 // gathered into scratch pages of GATHER_PAGE positions when the portion has at least
@@ -470,7 +471,7 @@ struct Run {
                     L.num_heads / L.num_kv_heads <= 8 && decode_tma_ok(c, L.head_dim) && st.all_single;
     if (!ok || g_fuse_mode == 1) return ok;
     const int reach = L.window ? (st.max_pos + 1 < L.window ? st.max_pos + 1 : L.window) : st.max_pos + 1;
-    const int resident = 3 * sm_count();
+    const int resident = DECODE_TMA_CTAS_PER_SM * sm_count();
     return (long long)st.rows * L.num_kv_heads *
                llm_decode_splits(st.rows, L.num_kv_heads, reach, resident, DECODE_TMA_TILE) <=
            2LL * resident;
@@ -508,11 +509,11 @@ struct Run {
     if (plan->n_small) {
       const bool tma = group <= 8 && decode_tma_ok(c, hd);
       const int splits = plan->small_single
-                             ? llm_decode_splits(plan->n_small, Hkv, reach, (tma ? 3 : 6) * sm_count(),
+                             ? llm_decode_splits(plan->n_small, Hkv, reach, (tma ? DECODE_TMA_CTAS_PER_SM : 6) * sm_count(),
                                                  tma ? DECODE_TMA_TILE : 32)
                              : 1;
       float *part_o, *part_ml;
-      const int resident = 3 * sm_count();
+      const int resident = DECODE_TMA_CTAS_PER_SM * sm_count();
       if (g_persistent_decode && tma && plan->small == nullptr && st.rows <= PERSISTENT_MAX_ROWS &&
           (long long)plan->n_small * Hkv * splits > resident &&
           (long long)plan->n_small * Hkv * splits <= (long long)PERSISTENT_MAX_WAVES * resident) {
@@ -621,7 +622,7 @@ struct Run {
     const bool use_norm = L.q_norm_w != nullptr;
     if (fusion_ok(L, c, cos_sin)) {
       const int reach = L.window ? (st.max_pos + 1 < L.window ? st.max_pos + 1 : L.window) : st.max_pos + 1;
-      const int splits = llm_decode_splits(rows, Hkv, reach, 3 * sm_count(), DECODE_TMA_TILE);
+      const int splits = llm_decode_splits(rows, Hkv, reach, DECODE_TMA_CTAS_PER_SM * sm_count(), DECODE_TMA_TILE);
       float *part_o, *part_ml;
       rc = parts(splits, L, &part_o, &part_ml);
       if (rc) return rc;

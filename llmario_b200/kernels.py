@@ -631,7 +631,7 @@ def attention_decode_persistent(q: torch.Tensor, part_o: torch.Tensor, part_ml: 
         _ptr(q), _ptr(part_o), _ptr(part_ml), _ptr(storage), storage.shape[0], storage.shape[1],
         slot, _ptr(block_table), block_table.stride(0), _ptr(row_slot), _ptr(row_pos), rows,
         num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0), parts,
-        int(ctas or 3 * sm_count()), _ptr(tc_status(q.device)), _stream()),
+        int(ctas or DECODE_TMA_CTAS_PER_SM * sm_count()), _ptr(tc_status(q.device)), _stream()),
         f"attention_decode_persistent (head_dim {head_dim})")
 
 
@@ -721,7 +721,7 @@ def decode_fusion_ok(ctx, view, num_heads: int, num_kv_heads: int, head_dim: int
     if not ok or FUSE_DECODE == "always":
         return ok
     reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
-    resident = 3 * sm_count()
+    resident = DECODE_TMA_CTAS_PER_SM * sm_count()
     return (ctx.rows * num_kv_heads * decode_splits(ctx.rows, num_kv_heads, reach, resident,
                                                    DECODE_TMA_TILE) <= 2 * resident)
 
@@ -742,7 +742,8 @@ def attention_decode_fused(ctx, proj: torch.Tensor, out: torch.Tensor, view, wri
     rows = ctx.rows
     reach = min(ctx.max_pos + 1, window) if window else ctx.max_pos + 1
     if splits is None:
-        splits = decode_splits(rows, num_kv_heads, reach, 3 * sm_count(), DECODE_TMA_TILE)
+        splits = decode_splits(rows, num_kv_heads, reach, DECODE_TMA_CTAS_PER_SM * sm_count(),
+                               DECODE_TMA_TILE)
     part_o = part_ml = None
     if splits > 1:
         part_o = ctx.buffer("attn.part_o", (rows * num_heads * splits * head_dim,), torch.float32)
@@ -761,7 +762,7 @@ def attention_decode_fused(ctx, proj: torch.Tensor, out: torch.Tensor, view, wri
                         clear=proj if clear else None)
 
 
-def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int = 444,
+def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int = 592,
                   tile: int = 32) -> int:
     """Parts into which the keys of a one-token item are cut.  ``resident``: how many CTAs of
     the kernel the GPU holds at once; ``tile``: keys of the kernel's tiles (parts are whole
@@ -780,5 +781,6 @@ def decode_splits(n_items: int, num_kv_heads: int, max_len: int, resident: int =
     return best
 
 
-DECODE_TMA_TILE = 64      # keys of a tile of attention_decode_tma.cu
+DECODE_TMA_TILE = 32      # keys of a tile of attention_decode_tma.cu
+DECODE_TMA_CTAS_PER_SM = 4    # its one-warp CTAs that fit an SM at head size 128
 PERSISTENT_ATTENTION_MAX_KEYS = 6144

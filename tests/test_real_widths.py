@@ -39,26 +39,30 @@ def test_every_cut_at_benchmark_widths(dtype, page):
     assert runner.cache.counters["pages_allocated"] > runner.cache.groups[0].n_pages
 
 
-@pytest.mark.parametrize("dtype,live,persistent", [("float32", 72, False), ("bfloat16", 72, False),
-                                                   ("bfloat16", 72, True), ("float32", 8, False),
-                                                   ("bfloat16", 8, False)])
-def test_many_live_requests_decode_through_recorded_steps(dtype, live, persistent):
+@pytest.mark.parametrize("dtype,live,mode", [("float32", 72, "default"), ("bfloat16", 72, "default"),
+                                             ("bfloat16", 80, "separate"),
+                                             ("bfloat16", 80, "persistent"),
+                                             ("float32", 8, "default"), ("bfloat16", 8, "default")])
+def test_many_live_requests_decode_through_recorded_steps(dtype, live, mode):
     """``live`` requests with prompts of unequal length, then 44 steps of one token each.  Many
     requests share a length modulo the page size, so their block tables change in the same
     step; the context bucket of the recorded step changes on the way (positions cross 128).
-    With 72 live rows bfloat16 decode attention splits the keys and merges once the contexts
-    have grown; with 8 it is the fused kernel.  Every row of every step against the plain implementation."""
+    In bfloat16 the rows of a step fit two waves of the fused decode kernel (norm, rotation,
+    cache write and attention in one); ``separate`` keeps the rotation kernel and the decode
+    attention apart, as steps of more rows run, and ``persistent`` takes the persistent decode
+    kernel with its merge there.  Every row of every step against the plain implementation."""
     from llmario_b200 import driver, kernels
-    from llmario_b200.engine import Model, ModelRunner, StepEntry
 
-    driver.use_persistent_decode(persistent)
+    driver.use_persistent_decode(mode == "persistent")
+    kernels.fuse_decode("few waves" if mode == "default" else "never")
     try:
-        _many_live(dtype, live, persistent)
+        _many_live(dtype, live, mode)
     finally:
         driver.use_persistent_decode(False)
+        kernels.fuse_decode("few waves")
 
 
-def _many_live(dtype, live, persistent):
+def _many_live(dtype, live, mode):
     from llmario_b200 import kernels
     from llmario_b200.engine import Model, ModelRunner, StepEntry
 
@@ -107,11 +111,13 @@ def _many_live(dtype, live, persistent):
         fused = after["decode_fused"] - before["decode_fused"]
         split = after["decode_tma"] + after["decode_persistent"] - before["decode_tma"] - \
             before["decode_persistent"]
-        if live >= 64:      # (while every context is short the 72 rows still fit the fused kernel)
-            assert split > 0 and after["merge"] > before["merge"]
-            assert (after["decode_persistent"] > before["decode_persistent"]) == persistent
-        else:
+        if mode == "default":
             assert fused > 0 and split == 0
+        else:
+            assert fused == 0 and split > 0 and after["rope_store"] > before["rope_store"]
+            assert (after["decode_persistent"] > before["decode_persistent"]) == (mode == "persistent")
+            if mode == "persistent":
+                assert after["merge"] > before["merge"]
         assert after["gemm_tcgen05"] > before["gemm_tcgen05"] and after["gemm_simt"] == before["gemm_simt"]
     for r in ids:
         ref = plain_logits(NAME, dtype, prompts[r] + tails[r])
