@@ -175,6 +175,7 @@ def cmd_step(a) -> None:
     from .. import driver
     driver.use_persistent_decode(a.persistent)
     kernels.use_dependent_launch(not a.no_dependent_launch)
+    kernels.fuse_decode(a.fuse)
     model = Model.random(preset_config(a.model, a.layers), 0, "bfloat16", DEV)
     runner = ModelRunner(model, page_size=a.page_size, cache_tokens=a.batch * (a.context + 256),
                          max_requests=max(a.batch, 8), max_context=8192, use_graphs=not a.eager)
@@ -289,6 +290,8 @@ def main(argv=None) -> int:
     st.add_argument("--steps", type=int, default=4)
     st.add_argument("--page-size", type=int, default=16)
     st.add_argument("--eager", action="store_true", help="no CUDA graphs")
+    st.add_argument("--fuse", default="few waves", choices=["few waves", "always", "never"],
+                    help="when decode attention runs fused with the rotation and the cache write")
     st.add_argument("--no-dependent-launch", action="store_true",
                     help="every kernel waits for the end of the one before it")
     st.add_argument("--persistent", action="store_true",
