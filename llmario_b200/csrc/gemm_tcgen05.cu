@@ -392,8 +392,8 @@ template <int EPI, typename TC>
 int dispatch(int bn, const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int ldc, int T, int N, int K,
              int half, int splits, int interleaved, int* status, cudaStream_t stream) {
   switch (bn) {
-    case 16: return launch<16, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
-    case 32: return launch<32, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
+    case 16: return launch<16, 6, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
+    case 32: return launch<32, 5, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
     case 64: return launch<64, 4, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
     case 128: return launch<128, 3, EPI, TC>(mw, mx, C, ldc, T, N, K, half, splits, interleaved, status, stream);
   }
