@@ -12,7 +12,6 @@ given.  Prints the median time, the bytes or flops it stands for, and the rate.
 from __future__ import annotations
 
 import argparse
-import math
 import sys
 
 import torch

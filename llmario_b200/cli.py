@@ -17,7 +17,7 @@ import os
 import random
 import sys
 import time
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 PRESETS = {
     # layer sizes of the benchmark configurations; weights are random

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import List, Any, Dict, Optional, Type
+from typing import List, Any, Dict, Optional
 
 from .spec import ConfigError, ModelSpec
 

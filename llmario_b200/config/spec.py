@@ -8,7 +8,7 @@ them knows which architecture produced it.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, Optional, Tuple
 
 
 class ConfigError(ValueError):

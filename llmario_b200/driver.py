@@ -13,7 +13,7 @@ from __future__ import annotations
 import ctypes
 import itertools
 from ctypes import POINTER, Structure, c_float, c_int, c_longlong, c_void_p
-from typing import Dict, Optional, Tuple
+from typing import Dict, Optional
 
 import numpy as np
 import torch

@@ -10,14 +10,13 @@ from __future__ import annotations
 
 import itertools
 import time
-from typing import Any, Dict, Iterable, List, Optional, Sequence, Union
+from typing import Any, Dict, List, Optional, Sequence, Union
 
 import torch
 
 from .. import kernels
-from ..cache import CacheFull
 from ..sampling import DeviceSampler, RequestSampler, SamplingParams
-from .model import Model, parse_dtype
+from .model import Model
 from .scheduler import FINISHED, Request, Scheduler, StepPlan
 from .step import ModelRunner, StepEntry
 

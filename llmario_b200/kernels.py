@@ -12,7 +12,7 @@ from typing import Optional
 
 import torch
 
-from .csrc.build import BuildError, load_library
+from .csrc.build import load_library
 
 F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}

@@ -8,7 +8,7 @@ residual stream.  A call that reads another call's cache projects only q.
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 

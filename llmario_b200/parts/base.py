@@ -23,7 +23,7 @@ Interfaces (``ctx`` is the :class:`StepContext` of the running step):
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 

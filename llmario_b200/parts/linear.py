@@ -4,7 +4,7 @@ after the product when the layer has one: forward.rs:399-425).  Chooses among th
 matrix kernels by dtype and size; there is no library product behind it."""
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 

@@ -18,7 +18,7 @@ from typing import Dict, Iterator, List, Optional, Tuple
 import torch
 
 from ..config.spec import ModelSpec, PartSpec
-from .safetensors_io import SafetensorsError, SafetensorsFolder, write_safetensors
+from .safetensors_io import SafetensorsFolder, write_safetensors
 
 
 class WeightError(ValueError):

@@ -1,7 +1,6 @@
 """The engine through its entry point, the sampler on the device, the parts alone, and parts
 defined by a test."""
 import dataclasses
-import math
 import random
 
 import numpy as np
@@ -9,7 +8,7 @@ import pytest
 import torch
 
 from plain import qwen3_plain as P
-from util import (TINY, assert_close, check_greedy_against_plain, config_json, model_dir,
+from util import (TINY, assert_close, check_greedy_against_plain, model_dir,
                   plain_logits, random_tokens)
 
 pytestmark = pytest.mark.gpu
@@ -455,7 +454,7 @@ class RunningMeanMixer:
 
 def toy_spec(spec):
     """Config A with the mixer of layer 1 replaced by the running-mean mixer."""
-    from llmario_b200.config import LayerSpec, PartSpec
+    from llmario_b200.config import PartSpec
     hidden = spec.hidden_size
     toy = PartSpec("running_mean", {"hidden_size": hidden,
                                     "tensors": {"mix": ("toy.mix.weight", (hidden, hidden))}})

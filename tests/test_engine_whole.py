@@ -1,8 +1,6 @@
 """Each request alone and whole: the engine's logits at every position against the plain
 implementation, in 32-bit and in bfloat16."""
-import numpy as np
 import pytest
-import torch
 
 from util import TINY, assert_close, model_dir, plain_logits, random_tokens
 

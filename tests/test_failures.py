@@ -6,7 +6,6 @@ The words travel to the host with every step's drawn tokens.  These tests make b
 without a kernel that misbehaves: a self-test kernel whose only job is to wait a few
 microseconds on a barrier at which nothing arrives, give up and return; and a token id patched
 in on the device."""
-import numpy as np
 import pytest
 import torch
 

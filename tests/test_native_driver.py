@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import traces
-from util import TINY, model_dir, random_tokens
+from util import model_dir, random_tokens
 
 
 def test_native_policies_equal_the_python_ones():

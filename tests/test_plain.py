@@ -1,7 +1,6 @@
 """The plain implementation itself, and the host-side pieces it is compared with (no GPU)."""
 import math
 
-import numpy as np
 import pytest
 import torch
 

@@ -13,11 +13,10 @@ import random
 
 import numpy as np
 import pytest
-import torch
 
 import traces
 from test_replay import requests_for, run_in_process
-from util import TINY, assert_close, model_dir, plain_logits, random_tokens
+from util import assert_close, model_dir, plain_logits, random_tokens
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
