@@ -240,8 +240,9 @@ def serve_workload(args, cfg, model, pk, clocks):
     lengths = [rng.randint(args.min_prompt, args.max_prompt) for _ in range(n)]
     page = args.page_size
     cache_tokens = sum(-(-(l + new + 1) // page) * page for l in lengths) + 4 * page
+    slots = min(n, args.max_requests or n)
     engine = Engine(model, page_size=page, cache_tokens=cache_tokens,
-                    token_budget=args.token_budget, max_requests=n, context=args.context)
+                    token_budget=args.token_budget, max_requests=slots, context=args.context)
     vocab = model.vocab_size
     weight_bytes = model.weight_bytes()
     kv_tok = kv_bytes_per_token(engine.runner)
@@ -315,6 +316,8 @@ def serve_workload(args, cfg, model, pk, clocks):
                 "ttft_ms_median": statistics.median((t_first[i] - t0) * 1e3 for i in ids),
                 "ttft_ms_max": max((t_first[i] - t0) * 1e3 for i in ids),
                 "engine_steps": len(stamps), "mixed_steps": host["mixed_steps"],
+                "steps_queued_ahead": engine.stats()["steps_planned_ahead"] - st0["steps_planned_ahead"],
+                "request_slots": slots,
                 "host_ms_per_mixed_step": host["mixed_s"] / max(1, host["mixed_steps"]) * 1e3,
                 "host_ms_per_decode_step": host["decode_s"] / max(1, host["decode_steps"]) * 1e3,
                 "mixed_wall_s": (stamps[last_mixed] - t0) if last_mixed >= 0 else 0.0,
@@ -393,6 +396,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     # the serve workload
     ap.add_argument("--requests", type=int, default=32)
+    ap.add_argument("--max-requests", type=int, default=None,
+                    help="serve: request slots of the engine (default: all requests at once); "
+                         "fewer make the rest wait for a slot")
     ap.add_argument("--min-prompt", type=int, default=16)
     ap.add_argument("--max-prompt", type=int, default=2048)
     ap.add_argument("--decode-len", type=int, default=128)

@@ -322,15 +322,20 @@ int llm_sched_plan(Sched* s, int cap, int64_t* keys, int* triples, int64_t* even
 // The step after `flying` (n entries: keys and (start, count, samples) triples; flying_events: how
 // many requests that plan preempted or failed), decided while it is still running and the tokens
 // it draws are unknown.  Returns the number of entries written, or -1 when that step cannot be
-// known yet.  It can when the flying step draws a token for every running request, nothing waits
-// for admission, and the pages suffice: then every request that does not end for certain
-// (max_tokens or the context reached) decodes one more token.  Changes nothing but a counter.
+// known yet.  It can when the flying step draws a token for every running request and the pages
+// suffice: then every request that does not end for certain (max_tokens or the context reached)
+// decodes one more token.  While requests wait for admission the step is known only if none of
+// them could be admitted into it: every request slot is taken, or the first in the queue finds
+// no pages, and no running request ends for certain (its slot and pages would come free).  A
+// request that ends on an end-of-sequence token drawn by the flying step then leaves its slot
+// one step before the queue sees it.  Changes nothing but a counter.
 int llm_sched_plan_ahead(Sched* s, int n, const int64_t* fkeys, const int* ftriples, int flying_events,
                          int64_t* keys, int* triples) {
-  if (!s->waiting.empty() || flying_events || n <= 0) return -1;
+  if (flying_events || n <= 0) return -1;
   if (n != (int)s->running.size()) return -1;
   for (int i = 0; i < n; ++i)
     if (!ftriples[3 * i + 2]) return -1;
+  const bool someone_waits = !s->waiting.empty();
   std::vector<int> free(s->n_groups);
   llm_cache_free_pages(s->cache, free.data());
   int m = 0;
@@ -339,7 +344,10 @@ int llm_sched_plan_ahead(Sched* s, int n, const int64_t* fkeys, const int* ftrip
     if (it == s->reqs.end()) return -1;
     const Req& r = it->second;
     if (r.state != RUNNING || r.penalties) return -1;
-    if (r.out_len + 1 >= r.max_tokens || r.seq() + 1 >= s->max_context) continue;   // its last token is in flight
+    if (r.out_len + 1 >= r.max_tokens || r.seq() + 1 >= s->max_context) {   // its last token is in flight
+      if (someone_waits) return -1;
+      continue;
+    }
     const std::vector<int> need = s->pages_for(r, 1, true);
     if (!Sched::fits(need, free)) return -1;      // someone has to go: decided with all facts known
     Sched::take(need, &free);
@@ -350,6 +358,13 @@ int llm_sched_plan_ahead(Sched* s, int n, const int64_t* fkeys, const int* ftrip
     ++m;
   }
   if (m == 0 || m > s->budget) return -1;
+  if (someone_waits && m < s->budget && llm_cache_free_slots(s->cache) > 0) {
+    // would the planner admit the first in the queue beside these decodes?  (make_plan, step 3)
+    Req& w = s->reqs[s->waiting.front()];
+    const int left = w.seq() - w.computed;
+    const bool whole_fits = !w.preemptions || Sched::fits(s->pages_for(w, left + 1, false), free);
+    if (whole_fits && s->fit(w, std::min(left, s->budget - m), free, false) > 0) return -1;
+  }
   ++s->counters[C_STEPS];
   ++s->counters[C_STEPS_AHEAD];
   return m;

@@ -259,11 +259,15 @@ class Scheduler:
     def plan_ahead(self, flying: StepPlan) -> Optional[StepPlan]:
         """The step after ``flying``, decided while ``flying`` is still running and the tokens it
         draws are unknown, or None when that step cannot be known yet.  It can when ``flying``
-        draws a token for every running request, nothing waits for admission, and the pages
-        suffice: then every request that does not end for certain (``max_tokens`` or the
-        context reached) decodes one more token.  A request that ends on an end-of-sequence
-        token drawn by ``flying`` has a row too many in the step ahead; :meth:`complete`
-        passes over it.  Changes nothing; the cache lengths already count ``flying``."""
+        draws a token for every running request and the pages suffice: then every request that
+        does not end for certain (``max_tokens`` or the context reached) decodes one more token.
+        While requests wait for admission the step is known only if none of them could be
+        admitted into it (every request slot is taken, or the first in the queue finds no pages)
+        and no running request ends for certain: a busy engine keeps its steps queued ahead, and a
+        request that ends on an end-of-sequence token leaves its slot to the queue one step
+        later than the queue could have had it.  Such a request has a row too many in the step
+        ahead; :meth:`complete` passes over it.  Changes nothing; the cache lengths already count
+        ``flying``."""
         n = len(flying.entries)
         if n == 0 or n > self._cap:
             return None

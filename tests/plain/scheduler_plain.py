@@ -214,12 +214,15 @@ class PlainScheduler:
     def plan_ahead(self, flying: StepPlan) -> Optional[StepPlan]:
         """The step after ``flying``, decided while ``flying`` is still running and the tokens it
         draws are unknown, or None when that step cannot be known yet.  It can when ``flying``
-        draws a token for every running request, nothing waits for admission, and the pages
-        suffice: then every request that does not end for certain (``max_tokens`` or the
-        context reached) decodes one more token.  A request that ends on an end-of-sequence
-        token drawn by ``flying`` has a row too many in the step ahead; :meth:`complete`
-        passes over it.  Changes nothing; the cache lengths already count ``flying``."""
-        if self.waiting or flying.preempted or flying.failed or not flying.entries:
+        draws a token for every running request and the pages suffice: then every request that
+        does not end for certain (``max_tokens`` or the context reached) decodes one more token.
+        While requests wait for admission the step is known only if none of them could be
+        admitted into it: every request slot is taken, or the first in the queue finds no
+        pages, and no running request ends for certain.  A request that ends on an
+        end-of-sequence token drawn by ``flying`` has a row too many in the step ahead;
+        :meth:`complete` passes over it.  Changes nothing; the cache lengths already count
+        ``flying``."""
+        if flying.preempted or flying.failed or not flying.entries:
             return None
         if len(flying.entries) != len(self.running) or not all(e.samples for e in flying.entries):
             return None
@@ -231,6 +234,8 @@ class PlainScheduler:
                 return None
             if len(r.output) + 1 >= r.params.max_tokens or \
                     r.sequence_len + 1 >= self.max_context:
+                if self.waiting:
+                    return None               # its slot and pages come free: admission is open
                 continue                      # its last token is the one in flight
             need = self._pages_for(r, 1, True)
             if any(n > f for n, f in zip(need, free)):
@@ -239,6 +244,14 @@ class PlainScheduler:
             entries.append(PlanEntry(r, e.start + e.count, 1, True))
         if not entries or len(entries) > self.token_budget:
             return None
+        if self.waiting and len(entries) < self.token_budget and self.cache.free_slots() > 0:
+            w = self.waiting[0]               # would plan() admit it beside these decodes?
+            left = w.sequence_len - w.computed
+            whole_fits = not w.preemptions or not any(
+                k > f for k, f in zip(self._pages_for(w, left + 1, False), free))
+            if whole_fits and self._fit(w, min(left, self.token_budget - len(entries)), free,
+                                        False) > 0:
+                return None
         self.counters["steps_planned"] += 1
         self.counters["steps_planned_ahead"] = self.counters.get("steps_planned_ahead", 0) + 1
         return StepPlan(entries=entries)

@@ -382,19 +382,48 @@ def test_a_step_is_planned_ahead_only_when_it_is_certain():
     s.cache.check_invariants()
 
 
-def test_no_step_ahead_when_someone_waits_or_pages_are_short():
+def test_no_step_ahead_when_someone_can_be_admitted_or_pages_are_short():
     m = manager(n_pages=4, page=4, max_requests=2, ctx=64)
     s = Scheduler(m, token_budget=64)
     a, b, c = req("a", 7, 50), req("b", 7, 50), req("c", 3, 50)
     s.add(a), s.add(b), s.add(c)        # two request slots: c waits
     p = s.plan()
     launch(s, p)
-    assert [e.request.id for e in p.entries] == ["a", "b"] and s.plan_ahead(p) is None
+    assert [e.request.id for e in p.entries] == ["a", "b"]
+    # c cannot be admitted while a and b hold both slots: the next step is known
+    ahead = s.plan_ahead(p)
+    assert [(e.request.id, e.start, e.count) for e in ahead.entries] == [("a", 7, 1), ("b", 7, 1)]
     finish(s, p)
     s.abort(c)
     p = s.plan()                        # a and b at 8 tokens each: all four pages are full
     launch(s, p)
     assert s.plan_ahead(p) is None      # the next token of each needs a page that is not there
+    # a free slot and free pages: the request that waits belongs into the next step
+    s3 = Scheduler(manager(n_pages=64, max_requests=3, ctx=64), token_budget=64)
+    d, e = req("d", 5, 50), req("e", 5, 50)
+    s3.add(d), s3.add(e)
+    p = s3.plan()
+    launch(s3, p)
+    s3.add(req("f", 4, 50))
+    assert s3.plan_ahead(p) is None
+    finish(s3, p)
+    p = s3.plan()
+    assert [x.request.id for x in p.entries] == ["d", "e", "f"]
+    # all slots taken, but one request ends for certain with the token in flight: its slot
+    # comes free, so the step after is planned with the queue in view
+    s4 = Scheduler(manager(n_pages=64, max_requests=2, ctx=64), token_budget=64)
+    g, h = req("g", 5, 2), req("h", 5, 50)
+    s4.add(g), s4.add(h), s4.add(req("i", 4, 50))
+    p = s4.plan()
+    launch(s4, p)
+    ahead = s4.plan_ahead(p)            # g's first token is in flight: it has one more to draw
+    assert [x.request.id for x in ahead.entries] == ["g", "h"]
+    launch(s4, ahead)
+    finish(s4, p)
+    assert s4.plan_ahead(ahead) is None      # g's last token is in flight and i waits
+    assert [r.id for r in finish(s4, ahead)] == ["g"]
+    p = s4.plan()
+    assert [x.request.id for x in p.entries] == ["h", "i"]
     pen = req("p", 3, 50)
     pen.params.repeat_penalty = 1.3     # penalties need the tokens on the host
     s2 = Scheduler(manager(n_pages=64, ctx=64), token_budget=8)
