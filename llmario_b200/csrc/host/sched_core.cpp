@@ -48,7 +48,12 @@ struct Req {
   int max_tokens = 0;
   bool ignore_eos = false, penalties = false;
   int state = WAITING, reason = R_NONE, preemptions = 0;
-  int seq() const { return prompt_len + out_len; }
+  // What a step that is still running will have added when it ends (no end-of-sequence token
+  // assumed); non-zero only while the step after it is being planned.
+  int fly_count = 0, fly_samples = 0;
+  int done() const { return computed + fly_count; }         // tokens in the cache, the running step's included
+  int outs() const { return out_len + fly_samples; }
+  int seq() const { return prompt_len + out_len + fly_samples; }
 };
 
 struct Entry { int64_t key; int start, count, samples; };
@@ -130,7 +135,11 @@ struct Plan {
   std::vector<int64_t> preempted, failed, admitted;
 };
 
-void make_plan(Sched& s, Plan* plan) {
+// ahead: the plan is made while a step is still running (its contribution stands in the
+// requests' fly_* fields).  Then nothing may be decided that needs the tokens it draws: where a
+// request would have to give way, or the step would be empty, the answer is false and nothing
+// has changed.
+bool make_plan(Sched& s, Plan* plan, bool ahead = false) {
   for (;;) {
     std::vector<int> free(s.n_groups);
     llm_cache_free_pages(s.cache, free.data());
@@ -140,15 +149,22 @@ void make_plan(Sched& s, Plan* plan) {
     // 1. decoding requests, one token each
     for (int64_t key : s.running) {
       Req& r = s.reqs[key];
-      if (r.computed == r.seq() - 1 && r.out_len > 0) {
+      if (r.done() == r.seq() - 1 && r.outs() > 0) {
+        if (ahead) {
+          // its last token is the one in flight: it ends with the running step
+          if (r.outs() >= r.max_tokens || r.seq() >= s.max_context) continue;
+          // its next input is the token in flight; penalties need that token on the host
+          if (r.fly_samples && r.penalties) return false;
+        }
         const std::vector<int> need = s.pages_for(r, 1, true);
         if (used >= s.budget) break;
         if (!Sched::fits(need, free)) {
+          if (ahead) return false;      // someone has to go: decided with all facts known
           ok = false;
           break;
         }
         Sched::take(need, &free);
-        entries.push_back({key, r.computed, 1, 1});
+        entries.push_back({key, r.done(), 1, 1});
         ++used;
       }
     }
@@ -167,12 +183,12 @@ void make_plan(Sched& s, Plan* plan) {
     for (int64_t key : s.running) {
       if (used >= s.budget) break;
       Req& r = s.reqs[key];
-      if (r.out_len > 0 && r.computed == r.seq() - 1) continue;
-      const int left = r.seq() - r.computed;
+      if (r.outs() > 0 && r.done() == r.seq() - 1) continue;
+      const int left = r.seq() - r.done();
       const int n = s.fit(r, std::min(left, s.budget - used), free, true);
       if (n <= 0) continue;
       Sched::take(s.pages_for(r, n, true), &free);
-      entries.push_back({key, r.computed, n, r.computed + n == r.seq() ? 1 : 0});
+      entries.push_back({key, r.done(), n, r.done() + n == r.seq() ? 1 : 0});
       used += n;
     }
     // 3. admission
@@ -199,6 +215,7 @@ void make_plan(Sched& s, Plan* plan) {
       entries.push_back({r.key, r.computed, n, r.computed + n == r.seq() ? 1 : 0});
       used += n;
     }
+    if (entries.empty() && ahead) return false;
     if (entries.empty() && !s.running.empty()) {
       // nothing fits although requests are running: a prompt portion is stuck for want of pages
       Req& victim = s.reqs[s.running.back()];
@@ -222,6 +239,7 @@ void make_plan(Sched& s, Plan* plan) {
     break;
   }
   ++s.counters[C_STEPS];
+  return true;
 }
 
 }  // namespace
@@ -321,53 +339,44 @@ int llm_sched_plan(Sched* s, int cap, int64_t* keys, int* triples, int64_t* even
 
 // The step after `flying` (n entries: keys and (start, count, samples) triples; flying_events: how
 // many requests that plan preempted or failed), decided while it is still running and the tokens
-// it draws are unknown.  Returns the number of entries written, or -1 when that step cannot be
-// known yet.  It can when the flying step draws a token for every running request and the pages
-// suffice: then every request that does not end for certain (max_tokens or the context reached)
-// decodes one more token.  While requests wait for admission the step is known only if none of
-// them could be admitted into it: every request slot is taken, or the first in the queue finds
-// no pages, and no running request ends for certain (its slot and pages would come free).  A
-// request that ends on an end-of-sequence token drawn by the flying step then leaves its slot
-// one step before the queue sees it.  Changes nothing but a counter.
+// it draws are unknown.  The planner runs as for any step, on the requests as they will stand
+// when the flying step ends without an end-of-sequence token: decoding requests get one more
+// token (the one in flight is their input), prompts their next portions, waiting requests are
+// admitted into free slots.  A request whose last token is in flight (max_tokens or the context
+// reached) is left out; it keeps its slot and pages until the flying step is reported.  Returns
+// the number of entries, with the admitted requests in events / n_events[2], or -1 when the step
+// cannot be known yet: the flying plan preempted or failed someone, pages are short so that a
+// request would have to give way, nothing could run, or a request with penalties would need the
+// token in flight.  A request that does end on an end-of-sequence token drawn by the flying
+// step has a row too many in this one; llm_sched_complete passes over it.
 int llm_sched_plan_ahead(Sched* s, int n, const int64_t* fkeys, const int* ftriples, int flying_events,
-                         int64_t* keys, int* triples) {
+                         int cap, int64_t* keys, int* triples, int64_t* events, int* n_events) {
   if (flying_events || n <= 0) return -1;
-  if (n != (int)s->running.size()) return -1;
-  for (int i = 0; i < n; ++i)
-    if (!ftriples[3 * i + 2]) return -1;
-  const bool someone_waits = !s->waiting.empty();
-  std::vector<int> free(s->n_groups);
-  llm_cache_free_pages(s->cache, free.data());
-  int m = 0;
+  if (cap < (int)(s->waiting.size() + s->running.size())) return S_ARGUMENT;
+  std::vector<Req*> touched;
   for (int i = 0; i < n; ++i) {
     auto it = s->reqs.find(fkeys[i]);
-    if (it == s->reqs.end()) return -1;
-    const Req& r = it->second;
-    if (r.state != RUNNING || r.penalties) return -1;
-    if (r.out_len + 1 >= r.max_tokens || r.seq() + 1 >= s->max_context) {   // its last token is in flight
-      if (someone_waits) return -1;
-      continue;
-    }
-    const std::vector<int> need = s->pages_for(r, 1, true);
-    if (!Sched::fits(need, free)) return -1;      // someone has to go: decided with all facts known
-    Sched::take(need, &free);
-    keys[m] = r.key;
-    triples[3 * m] = ftriples[3 * i] + ftriples[3 * i + 1];
-    triples[3 * m + 1] = 1;
-    triples[3 * m + 2] = 1;
-    ++m;
+    if (it == s->reqs.end() || it->second.state != RUNNING) continue;     // gone meanwhile (aborted)
+    it->second.fly_count = ftriples[3 * i + 1];
+    it->second.fly_samples = ftriples[3 * i + 2] ? 1 : 0;
+    touched.push_back(&it->second);
   }
-  if (m == 0 || m > s->budget) return -1;
-  if (someone_waits && m < s->budget && llm_cache_free_slots(s->cache) > 0) {
-    // would the planner admit the first in the queue beside these decodes?  (make_plan, step 3)
-    Req& w = s->reqs[s->waiting.front()];
-    const int left = w.seq() - w.computed;
-    const bool whole_fits = !w.preemptions || Sched::fits(s->pages_for(w, left + 1, false), free);
-    if (whole_fits && s->fit(w, std::min(left, s->budget - m), free, false) > 0) return -1;
-  }
-  ++s->counters[C_STEPS];
+  Plan plan;
+  const bool known = make_plan(*s, &plan, true);
+  for (Req* r : touched) r->fly_count = r->fly_samples = 0;
+  if (!known) return -1;
   ++s->counters[C_STEPS_AHEAD];
-  return m;
+  for (size_t i = 0; i < plan.entries.size(); ++i) {
+    keys[i] = plan.entries[i].key;
+    triples[3 * i] = plan.entries[i].start;
+    triples[3 * i + 1] = plan.entries[i].count;
+    triples[3 * i + 2] = plan.entries[i].samples;
+  }
+  int at = 0;
+  for (int64_t k : plan.admitted) events[at++] = k;
+  n_events[0] = n_events[1] = 0;
+  n_events[2] = (int)plan.admitted.size();
+  return (int)plan.entries.size();
 }
 
 // The step ran.  tokens[i]: the token drawn for entry i (read only where the entry samples).

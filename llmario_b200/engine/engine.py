@@ -139,19 +139,28 @@ class Engine:
         still running and whose drawn tokens are this step's input."""
         entries = []
         source = None
-        if after is None:
-            for e in plan.entries:
-                toks = e.request.tokens(e.start, e.count)
-                entries.append(StepEntry(e.request.id, toks, [e.count - 1] if e.samples else []))
-        else:
-            row_of = {}
-            i = 0
+        row_of = {}        # request id -> its row among the tokens that ``after`` draws
+        if after is not None:
             for e in after.plan.entries:
                 if e.samples:
-                    row_of[e.request.id] = i
-                    i += 1
-            entries = [StepEntry(e.request.id, [0], [0]) for e in plan.entries]
-            source = (self.sampler.device_tokens, [row_of[e.request.id] for e in plan.entries])
+                    row_of[e.request.id] = len(row_of)
+        rows: List[int] = []        # per token row: where on the device its token comes from, or -1
+        for e in plan.entries:
+            r = e.request
+            want = [e.count - 1] if e.samples else []
+            # the position of the token ``after`` is drawing for this request
+            unknown = len(r.prompt) + len(r.output) if r.id in row_of else None
+            if unknown is not None and e.start + e.count - 1 >= unknown:
+                if e.count != 1 or e.start != unknown:
+                    raise RuntimeError(f"request {r.id!r}: a portion planned ahead reaches past "
+                                       "the token in flight")
+                entries.append(StepEntry(r.id, [0], want))
+                rows.append(row_of[r.id])
+            else:
+                entries.append(StepEntry(r.id, r.tokens(e.start, e.count), want))
+                rows += [-1] * e.count
+        if any(x >= 0 for x in rows):
+            source = (self.sampler.device_tokens, rows)
         t0 = time.perf_counter()
         logits = self.runner.step(entries, source)
         samplers = [e.request.sampler for e in plan.entries if e.samples]

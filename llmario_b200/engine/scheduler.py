@@ -108,7 +108,7 @@ def _native():
             "llm_sched_has_work": ([P], I),
             "llm_sched_request": ([P, L, P], I),
             "llm_sched_plan": ([P, I, P, P, P, P], I),
-            "llm_sched_plan_ahead": ([P, I, P, P, I, P, P], I),
+            "llm_sched_plan_ahead": ([P, I, P, P, I, I, P, P, P, P], I),
             "llm_sched_complete": ([P, I, P, P, P, P, P], I),
             "llm_sched_abort": ([P, L], I),
             "llm_sched_fail": ([P, L], I),
@@ -258,16 +258,17 @@ class Scheduler:
 
     def plan_ahead(self, flying: StepPlan) -> Optional[StepPlan]:
         """The step after ``flying``, decided while ``flying`` is still running and the tokens it
-        draws are unknown, or None when that step cannot be known yet.  It can when ``flying``
-        draws a token for every running request and the pages suffice: then every request that
-        does not end for certain (``max_tokens`` or the context reached) decodes one more token.
-        While requests wait for admission the step is known only if none of them could be
-        admitted into it (every request slot is taken, or the first in the queue finds no pages)
-        and no running request ends for certain: a busy engine keeps its steps queued ahead, and a
-        request that ends on an end-of-sequence token leaves its slot to the queue one step
-        later than the queue could have had it.  Such a request has a row too many in the step
-        ahead; :meth:`complete` passes over it.  Changes nothing; the cache lengths already count
-        ``flying``."""
+        draws are unknown, or None when that step cannot be known yet.  The planner runs as for
+        any step, on the requests as they will stand when ``flying`` ends without an
+        end-of-sequence token: decoding requests get one more token (the one in flight is their
+        input), prompts their next portions, waiting requests are admitted into free slots.  A
+        request whose last token is in flight (``max_tokens`` or the context reached) is left
+        out; it keeps its slot and pages until ``flying`` is reported.  None when ``flying``
+        preempted or failed someone, when pages are so short that a request would have to give
+        way (that is decided with all facts known), when nothing could run, or when a request
+        with penalties would need the token in flight.  A request that does end on an
+        end-of-sequence token drawn by ``flying`` has a row too many in the step ahead;
+        :meth:`complete` passes over it.  The cache lengths already count ``flying``."""
         n = len(flying.entries)
         if n == 0 or n > self._cap:
             return None
@@ -277,13 +278,21 @@ class Scheduler:
             self._in_triples[3 * i + 1] = e.count
             self._in_triples[3 * i + 2] = int(e.samples)
         m = self._lib.llm_sched_plan_ahead(self._s, n, self._in_keys, self._in_triples,
-                                           len(flying.preempted) + len(flying.failed), self._keys,
-                                           self._triples)
-        if m < 0:
+                                           len(flying.preempted) + len(flying.failed), self._cap,
+                                           self._keys, self._triples, self._events, self._n_events)
+        if m == -1:
             return None
+        if m < 0:
+            raise RuntimeError(f"the native scheduler answered {m}")
+        plan = StepPlan()
+        for i in range(self._n_events[2]):
+            self._by_key[self._events[i]].state = RUNNING
         t = self._triples
-        return StepPlan(entries=[PlanEntry(self._by_key[self._keys[i]], t[3 * i], 1, True)
-                                 for i in range(m)])
+        plan.entries = [PlanEntry(self._by_key[self._keys[i]], t[3 * i], t[3 * i + 1],
+                                  bool(t[3 * i + 2])) for i in range(m)]
+        if self._n_events[2]:
+            self._mirror_queues()
+        return plan
 
     # ------------------------------------------------------------------ after the step
     def complete(self, plan: StepPlan, sampled: Dict[Any, int]) -> List[Request]:

@@ -95,6 +95,7 @@ class PlainScheduler:
         self._arrivals = itertools.count()
         self.counters = {"admitted": 0, "finished": 0, "preemptions": 0, "failed": 0,
                          "steps_planned": 0, "prompt_tokens": 0, "decode_tokens": 0}
+        self._fly: dict = {}
 
     # ------------------------------------------------------------------ queue
     def add(self, request: Request) -> None:
@@ -119,9 +120,23 @@ class PlainScheduler:
         ps = self.cache.page_size
         return [-(-count // ps)] * len(self.cache.groups)
 
-    def plan(self) -> StepPlan:
+    # A request as it will stand when the step that is still running ends without an
+    # end-of-sequence token (``_fly``: request id -> (tokens, draws a token) of that step; empty
+    # except while the step after it is being planned).
+    def _done(self, r: Request) -> int:
+        return r.computed + self._fly.get(r.id, (0, 0))[0]
+
+    def _outs(self, r: Request) -> int:
+        return len(r.output) + self._fly.get(r.id, (0, 0))[1]
+
+    def _seq(self, r: Request) -> int:
+        return len(r.prompt) + self._outs(r)
+
+    def plan(self, ahead: bool = False) -> Optional[StepPlan]:
         """Decide the next step.  Changes the queues (admission, preemption, failure) but feeds
-        nothing: the caller runs the step and reports back with :meth:`complete`."""
+        nothing: the caller runs the step and reports back with :meth:`complete`.  ``ahead``:
+        the plan is made while a step is still running; where a request would have to give way
+        or nothing could run the answer is None and nothing has changed."""
         plan = StepPlan()
         cache = self.cache
         while True:
@@ -131,15 +146,23 @@ class PlainScheduler:
             ok = True
             # 1. decoding requests, one token each
             for r in self.running:
-                if r.computed == r.sequence_len - 1 and r.output:
+                if self._done(r) == self._seq(r) - 1 and self._outs(r) > 0:
+                    if ahead:
+                        if self._outs(r) >= r.params.max_tokens or \
+                                self._seq(r) >= self.max_context:
+                            continue          # its last token is the one in flight
+                        if self._fly.get(r.id, (0, 0))[1] and r.params.penalties_active:
+                            return None       # penalties need the token in flight on the host
                     need = self._pages_for(r, 1, True)
                     if used >= self.token_budget:
                         break
                     if any(n > f for n, f in zip(need, free)):
+                        if ahead:
+                            return None       # someone has to go: decided with all facts known
                         ok = False
                         break
                     free = [f - n for f, n in zip(free, need)]
-                    entries.append(PlanEntry(r, r.computed, 1, True))
+                    entries.append(PlanEntry(r, self._done(r), 1, True))
                     used += 1
             if not ok:
                 victim = self.running[-1]
@@ -155,16 +178,16 @@ class PlainScheduler:
             for r in self.running:
                 if used >= self.token_budget:
                     break
-                if r.output and r.computed == r.sequence_len - 1:
+                if self._outs(r) > 0 and self._done(r) == self._seq(r) - 1:
                     continue
-                left = r.sequence_len - r.computed
+                left = self._seq(r) - self._done(r)
                 n = min(left, self.token_budget - used)
                 n = self._fit(r, n, free, True)
                 if n <= 0:
                     continue
                 need = self._pages_for(r, n, True)
                 free = [f - k for f, k in zip(free, need)]
-                entries.append(PlanEntry(r, r.computed, n, r.computed + n == r.sequence_len))
+                entries.append(PlanEntry(r, self._done(r), n, self._done(r) + n == self._seq(r)))
                 used += n
             # 3. admission
             while self.waiting and used < self.token_budget and \
@@ -189,6 +212,8 @@ class PlainScheduler:
                 free = [f - k for f, k in zip(free, need)]
                 entries.append(PlanEntry(r, r.computed, n, r.computed + n == r.sequence_len))
                 used += n
+            if not entries and ahead:
+                return None
             if not entries and self.running:
                 # nothing fits although requests are running: a prompt portion is stuck for
                 # want of pages.  Make room by preempting the newest, or fail a lone request.
@@ -213,48 +238,21 @@ class PlainScheduler:
 
     def plan_ahead(self, flying: StepPlan) -> Optional[StepPlan]:
         """The step after ``flying``, decided while ``flying`` is still running and the tokens it
-        draws are unknown, or None when that step cannot be known yet.  It can when ``flying``
-        draws a token for every running request and the pages suffice: then every request that
-        does not end for certain (``max_tokens`` or the context reached) decodes one more token.
-        While requests wait for admission the step is known only if none of them could be
-        admitted into it: every request slot is taken, or the first in the queue finds no
-        pages, and no running request ends for certain.  A request that ends on an
-        end-of-sequence token drawn by ``flying`` has a row too many in the step ahead;
-        :meth:`complete` passes over it.  Changes nothing; the cache lengths already count
-        ``flying``."""
+        draws are unknown, or None when that step cannot be known yet: the planner runs on the
+        requests as they will stand when ``flying`` ends without an end-of-sequence token.  A
+        request that does end on such a token has a row too many in the step ahead;
+        :meth:`complete` passes over it.  The cache lengths already count ``flying``."""
         if flying.preempted or flying.failed or not flying.entries:
             return None
-        if len(flying.entries) != len(self.running) or not all(e.samples for e in flying.entries):
-            return None
-        free = list(self.cache.free_pages())
-        entries: List[PlanEntry] = []
-        for e in flying.entries:
-            r = e.request
-            if r.state != RUNNING or r.params.penalties_active:
-                return None
-            if len(r.output) + 1 >= r.params.max_tokens or \
-                    r.sequence_len + 1 >= self.max_context:
-                if self.waiting:
-                    return None               # its slot and pages come free: admission is open
-                continue                      # its last token is the one in flight
-            need = self._pages_for(r, 1, True)
-            if any(n > f for n, f in zip(need, free)):
-                return None                   # someone has to go: decided with all facts known
-            free = [f - n for f, n in zip(free, need)]
-            entries.append(PlanEntry(r, e.start + e.count, 1, True))
-        if not entries or len(entries) > self.token_budget:
-            return None
-        if self.waiting and len(entries) < self.token_budget and self.cache.free_slots() > 0:
-            w = self.waiting[0]               # would plan() admit it beside these decodes?
-            left = w.sequence_len - w.computed
-            whole_fits = not w.preemptions or not any(
-                k > f for k, f in zip(self._pages_for(w, left + 1, False), free))
-            if whole_fits and self._fit(w, min(left, self.token_budget - len(entries)), free,
-                                        False) > 0:
-                return None
-        self.counters["steps_planned"] += 1
-        self.counters["steps_planned_ahead"] = self.counters.get("steps_planned_ahead", 0) + 1
-        return StepPlan(entries=entries)
+        self._fly = {e.request.id: (e.count, int(e.samples)) for e in flying.entries
+                     if e.request.state == RUNNING}
+        try:
+            plan = self.plan(ahead=True)
+        finally:
+            self._fly = {}
+        if plan is not None:
+            self.counters["steps_planned_ahead"] = self.counters.get("steps_planned_ahead", 0) + 1
+        return plan
 
     def _planned_new(self, entries: List[PlanEntry]) -> int:
         return sum(1 for e in entries if not self.cache.has(e.request.id))

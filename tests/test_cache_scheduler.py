@@ -349,17 +349,23 @@ def finish(s, plan, token=7):
     return s.complete(plan, {e.request.id: token for e in plan.entries if e.samples})
 
 
-def test_a_step_is_planned_ahead_only_when_it_is_certain():
+def test_a_step_is_planned_ahead_on_what_is_certain():
+    """While a step runs, the step after it is planned on the requests as they will stand when it
+    ends without an end-of-sequence token: the rest of a prompt, the admission of a request that
+    waits, one more token for every request that decodes (its input is the token in flight)."""
     s = Scheduler(manager(n_pages=64, ctx=64), token_budget=8, eos_token_ids=[99])
     a, b = req("a", 10, max_tokens=3), req("b", 3, max_tokens=50)
     s.add(a), s.add(b)
-    p1 = s.plan()                       # a's first portion: nothing is drawn for b
+    p1 = s.plan()                       # a's first portion fills the budget: b still waits
+    assert [(e.request.id, e.start, e.count, e.samples) for e in p1.entries] == [("a", 0, 8, False)]
     launch(s, p1)
-    assert s.plan_ahead(p1) is None
-    finish(s, p1)
-    p2 = s.plan()                       # the rest of a and all of b: both draw a token
+    p2 = s.plan_ahead(p1)               # the rest of a, and b is admitted: both draw a token
+    assert [(e.request.id, e.start, e.count, e.samples) for e in p2.entries] == \
+        [("a", 8, 2, True), ("b", 0, 3, True)]
+    assert b.state == "running" and not s.waiting
     launch(s, p2)
-    p3 = s.plan_ahead(p2)
+    assert finish(s, p1) == []
+    p3 = s.plan_ahead(p2)               # the tokens p2 draws are the inputs of p3
     assert [(e.request.id, e.start, e.count, e.samples) for e in p3.entries] == \
         [("a", 10, 1, True), ("b", 3, 1, True)]
     launch(s, p3)
@@ -380,9 +386,10 @@ def test_a_step_is_planned_ahead_only_when_it_is_certain():
     assert s.plan_ahead(p6) is None and not s.has_work()
     assert s.cache.free_pages() == [64]
     s.cache.check_invariants()
+    assert s.counters["steps_planned_ahead"] == 5 and s.counters["steps_planned"] == 6
 
 
-def test_no_step_ahead_when_someone_can_be_admitted_or_pages_are_short():
+def test_what_a_step_planned_ahead_leaves_to_the_next_plan():
     m = manager(n_pages=4, page=4, max_requests=2, ctx=64)
     s = Scheduler(m, token_budget=64)
     a, b, c = req("a", 7, 50), req("b", 7, 50), req("c", 3, 50)
@@ -390,42 +397,50 @@ def test_no_step_ahead_when_someone_can_be_admitted_or_pages_are_short():
     p = s.plan()
     launch(s, p)
     assert [e.request.id for e in p.entries] == ["a", "b"]
-    # c cannot be admitted while a and b hold both slots: the next step is known
+    # c cannot be admitted while a and b hold both slots: the next step is a and b alone
     ahead = s.plan_ahead(p)
     assert [(e.request.id, e.start, e.count) for e in ahead.entries] == [("a", 7, 1), ("b", 7, 1)]
+    assert [r.id for r in s.waiting] == ["c"]
     finish(s, p)
     s.abort(c)
-    p = s.plan()                        # a and b at 8 tokens each: all four pages are full
-    launch(s, p)
-    assert s.plan_ahead(p) is None      # the next token of each needs a page that is not there
-    # a free slot and free pages: the request that waits belongs into the next step
+    launch(s, ahead)                    # a and b at 8 tokens each: all four pages are full
+    assert s.plan_ahead(ahead) is None  # the next token of each needs a page that is not there:
+    finish(s, ahead)                    # who gives way is decided with all facts known
+    p = s.plan()
+    assert [r.id for r in p.preempted] == ["b"] and [e.request.id for e in p.entries] == ["a"]
+    # a request that arrives while a step runs is admitted into the step planned ahead
     s3 = Scheduler(manager(n_pages=64, max_requests=3, ctx=64), token_budget=64)
     d, e = req("d", 5, 50), req("e", 5, 50)
     s3.add(d), s3.add(e)
     p = s3.plan()
     launch(s3, p)
-    s3.add(req("f", 4, 50))
-    assert s3.plan_ahead(p) is None
-    finish(s3, p)
-    p = s3.plan()
-    assert [x.request.id for x in p.entries] == ["d", "e", "f"]
-    # all slots taken, but one request ends for certain with the token in flight: its slot
-    # comes free, so the step after is planned with the queue in view
+    f = req("f", 4, 50)
+    s3.add(f)
+    ahead = s3.plan_ahead(p)
+    assert [(x.request.id, x.start, x.count) for x in ahead.entries] == \
+        [("d", 5, 1), ("e", 5, 1), ("f", 0, 4)]
+    assert f.state == "running"
+    # all slots taken and one request ends for certain with the token in flight: it is left out
+    # of the step ahead but keeps its slot until the flying step is reported, so the request
+    # that waits comes in with the plan after that
     s4 = Scheduler(manager(n_pages=64, max_requests=2, ctx=64), token_budget=64)
-    g, h = req("g", 5, 2), req("h", 5, 50)
-    s4.add(g), s4.add(h), s4.add(req("i", 4, 50))
+    g, h, i = req("g", 5, 2), req("h", 5, 50), req("i", 4, 50)
+    s4.add(g), s4.add(h), s4.add(i)
     p = s4.plan()
     launch(s4, p)
-    ahead = s4.plan_ahead(p)            # g's first token is in flight: it has one more to draw
-    assert [x.request.id for x in ahead.entries] == ["g", "h"]
-    launch(s4, ahead)
+    p2 = s4.plan_ahead(p)               # g's first token is in flight: it has one more to draw
+    assert [x.request.id for x in p2.entries] == ["g", "h"]
+    launch(s4, p2)
     finish(s4, p)
-    assert s4.plan_ahead(ahead) is None      # g's last token is in flight and i waits
-    assert [r.id for r in finish(s4, ahead)] == ["g"]
-    p = s4.plan()
-    assert [x.request.id for x in p.entries] == ["h", "i"]
+    p3 = s4.plan_ahead(p2)              # g's last token is in flight
+    assert [x.request.id for x in p3.entries] == ["h"] and [r.id for r in s4.waiting] == ["i"]
+    launch(s4, p3)
+    assert [r.id for r in finish(s4, p2)] == ["g"]
+    p4 = s4.plan_ahead(p3)
+    assert [(x.request.id, x.start, x.count) for x in p4.entries] == [("h", 7, 1), ("i", 0, 4)]
+    # penalties need the drawn token on the host before the next step can be made
     pen = req("p", 3, 50)
-    pen.params.repeat_penalty = 1.3     # penalties need the tokens on the host
+    pen.params.repeat_penalty = 1.3
     s2 = Scheduler(manager(n_pages=64, ctx=64), token_budget=8)
     s2.add(pen)
     p = s2.plan()
@@ -586,6 +601,9 @@ def test_native_scheduler_agrees_with_the_plain_model(seed):
                 live_a = [e for e in aa.entries if e.request.state == RUNNING]
                 live_b = [e for e in ab.entries if e.request.state == RUNNING]
                 for s, live in ((native, live_a), (plain, live_b)):
+                    for e in live:                  # (a step planned ahead may admit a request)
+                        if not s.cache.has(e.request.id):
+                            s.cache.open(e.request.id)
                     s.cache.reserve([(e.request.id, e.count) for e in live])
                     for e in live:
                         s.cache.advance(e.request.id, e.count)
