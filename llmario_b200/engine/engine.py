@@ -41,9 +41,9 @@ class Engine:
         once; ``token_budget``: most tokens in one step; ``num_pages`` / ``cache_tokens``: size
         of the cache (default: room for every request slot at full context, or what nine tenths
         of the free device memory hold, whichever is less).  ``lookahead``:
-        while a step of decoding requests runs, the next one is already queued on the device
-        with its input tokens taken from the sampler's output there, so that the device does
-        not wait for the host between steps; the tokens a caller sees are the same.
+        while a step runs, the next one is already planned and queued on the device (rows whose
+        input is the token in flight take it from the sampler's output there), so that the
+        device does not wait for the host between steps; the tokens a caller sees are the same.
         ``native``: standard blocks are driven by the C++ step driver (one call per run of
         layers) instead of launch by launch from Python; the launches are the same."""
         if not torch.cuda.is_available():
