@@ -8,7 +8,9 @@ default run has the layer sizes of Qwen3-8B with seeded random bfloat16 weights,
 1,024-token prompts of uniform random ids, context 8,192, pages of 16 tokens (the named
 configuration).  ``value`` is decoded tokens per second timed on the device around K consecutive
 steps of the step function plus the sampling kernel; ``e2e`` is the same through ``Engine.step``
-with host token lists in and out; ``prefill`` is one prompt of 2,048 tokens (median of the runs,
+with host token lists in and out (prompts run as steps of thousands of tokens at the power cap
+and the SM clock stays low for some 60 ms after them, so at least 48 untimed decode steps,
+``config.untimed_steps``, come before the K timed ones, of both figures); ``prefill`` is one prompt of 2,048 tokens (median of the runs,
 all runs listed); ``points`` holds batch 1 and 64; ``engine_page`` repeats prefill, ``value`` and
 ``e2e`` with the engine's default page of 64 tokens.  ``--model qwen3-32b --prompt-len 4096
 --context 16384`` is the second named configuration.  The weights are larger than the L2 cache,
@@ -109,6 +111,13 @@ def reference_arm():
     return 0
 
 
+# Untimed decode steps between the prompts and the timed steps, at least: prompts run as steps of
+# thousands of tokens at the power cap, and the SM clock stays low for some 60 ms after them
+# (1,620 of 1,965 MHz; a decode step of Qwen3-8B sizes then takes 3.46 instead of 3.14 ms).  The
+# timed steps start when that has passed, whatever --warmup says beyond it.
+SETTLE_STEPS = 48
+
+
 def decode_bench(runner, model, batch, prompt_len, steps, warmup, rng, chunk=2048):
     """Prefill ``batch`` requests of ``prompt_len`` tokens, then time ``steps`` decode steps on
     the device.  Returns (ms per step, cache bytes read per step on average, launches)."""
@@ -119,6 +128,7 @@ def decode_bench(runner, model, batch, prompt_len, steps, warmup, rng, chunk=204
     from llmario_b200.engine import StepEntry
 
     vocab = model.vocab_size
+    warmup = max(warmup, SETTLE_STEPS)
     ids = [f"b{batch}-{i}" for i in range(batch)]
     for rid in ids:
         toks = [rng.randrange(vocab) for _ in range(prompt_len)]
@@ -168,7 +178,8 @@ def e2e_bench(engine, batch, prompt_len, steps, warmup, rng):
            for _ in range(batch)]
     while not all(engine.request(i).output for i in ids):
         engine.step()                      # prefill (chunked under the token budget)
-    for _ in range(warmup):
+    # (the untimed steps go on until the clocks have recovered from the prompts: SETTLE_STEPS)
+    for _ in range(max(warmup, SETTLE_STEPS)):
         engine.step()
     torch.cuda.synchronize()
     st0 = engine.stats()
@@ -448,7 +459,7 @@ def decode_workload(args, cfg, full_layers, model, pk, clocks):
     # room for the prompt, the decoded tokens and the tokens a request decodes while the prompts
     # of the others are still being prefilled
     ahead = args.batch * -(-args.prompt_len // budget) + 2
-    per_req = args.prompt_len + warmup + steps + ahead + args.page_size
+    per_req = args.prompt_len + max(warmup, SETTLE_STEPS) + steps + ahead + args.page_size
     cache_tokens = max(max_batch * per_req, args.prefill_tokens + args.page_size)
     engine = Engine(model, page_size=args.page_size, cache_tokens=cache_tokens,
                     token_budget=budget, max_requests=max_batch, context=context)
@@ -482,7 +493,7 @@ def decode_workload(args, cfg, full_layers, model, pk, clocks):
     if own != args.page_size and not args.skip_points:
         del engine, runner
         torch.cuda.empty_cache()
-        per_req = args.prompt_len + warmup + steps + ahead + own
+        per_req = args.prompt_len + max(warmup, SETTLE_STEPS) + steps + ahead + own
         eng2 = Engine(model, page_size=own,
                       cache_tokens=max(args.batch * per_req, T + own),
                       token_budget=budget, max_requests=args.batch, context=context)
@@ -509,7 +520,7 @@ def decode_workload(args, cfg, full_layers, model, pk, clocks):
                    "context": context, "page_size": args.page_size,
                    "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights %.1f GB)" % (weight_bytes / 1e9),
-                   "peaks": pk["source"]},
+                   "peaks": pk["source"], "untimed_steps": max(warmup, SETTLE_STEPS)},
         # per step the engine copies one int32 array (header, token id, position, request slot,
         # wanted row and the index of the token drawn on the device per request, block-table
         # changes) and, when the set of requests or a random draw changes them, the sampler's
