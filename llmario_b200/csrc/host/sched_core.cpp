@@ -153,8 +153,6 @@ bool make_plan(Sched& s, Plan* plan, bool ahead = false) {
         if (ahead) {
           // its last token is the one in flight: it ends with the running step
           if (r.outs() >= r.max_tokens || r.seq() >= s.max_context) continue;
-          // its next input is the token in flight; penalties need that token on the host
-          if (r.fly_samples && r.penalties) return false;
         }
         const std::vector<int> need = s.pages_for(r, 1, true);
         if (used >= s.budget) break;
@@ -346,8 +344,8 @@ int llm_sched_plan(Sched* s, int cap, int64_t* keys, int* triples, int64_t* even
 // reached) is left out; it keeps its slot and pages until the flying step is reported.  Returns
 // the number of entries, with the admitted requests in events / n_events[2], or -1 when the step
 // cannot be known yet: the flying plan preempted or failed someone, pages are short so that a
-// request would have to give way, nothing could run, or a request with penalties would need the
-// token in flight.  A request that does end on an end-of-sequence token drawn by the flying
+// request would have to give way, or nothing could run.  (Penalties do not stand in the way: the
+// sampler counts the token in flight on the device.)  A request that does end on an end-of-sequence token drawn by the flying
 // step has a row too many in this one; llm_sched_complete passes over it.
 int llm_sched_plan_ahead(Sched* s, int n, const int64_t* fkeys, const int* ftriples, int flying_events,
                          int cap, int64_t* keys, int* triples, int64_t* events, int* n_events) {

@@ -192,14 +192,39 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
 // (sampler.rs:486-507).
 __global__ void penalty_kernel(float* __restrict__ logits, long long ld, const int* __restrict__ triples,
                                int n, const float* __restrict__ repeat, const float* __restrict__ freq,
-                               const float* __restrict__ presence) {
+                               const float* __restrict__ presence, const int* __restrict__ inflight_src,
+                               const int* __restrict__ drawn) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const int r = triples[3 * i], tok = triples[3 * i + 1], count = triples[3 * i + 2];
+  const int r = triples[3 * i], tok = triples[3 * i + 1];
+  int count = triples[3 * i + 2];
+  // the token that the step before is still drawing for this row counts once more
+  if (inflight_src && inflight_src[r] >= 0 && drawn[inflight_src[r]] == tok) ++count;
   float* l = logits + (size_t)r * ld + tok;
   float v = *l;
   v = v <= 0.f ? v * repeat[r] : v / repeat[r];
   v -= (float)count * freq[r] + presence[r];
+  *l = v;
+}
+
+// Rows whose window gets a token that the host does not know yet (the step before is still
+// drawing it; drawn[inflight_src[row]] will hold it in stream order): when no triple of the row
+// names that token, it has been seen once.  One thread per row walks the triples.
+__global__ void penalty_inflight_kernel(float* __restrict__ logits, long long ld, int V,
+                                        const int* __restrict__ triples, int n, int rows,
+                                        const float* __restrict__ repeat, const float* __restrict__ freq,
+                                        const float* __restrict__ presence,
+                                        const int* __restrict__ inflight_src, const int* __restrict__ drawn) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows || inflight_src[r] < 0) return;
+  const int tok = drawn[inflight_src[r]];
+  if (tok < 0 || tok >= V) return;
+  for (int i = 0; i < n; ++i)
+    if (triples[3 * i] == r && triples[3 * i + 1] == tok) return;      // counted by its triple
+  float* l = logits + (size_t)r * ld + tok;
+  float v = *l;
+  v = v <= 0.f ? v * repeat[r] : v / repeat[r];
+  v -= 1.0f * freq[r] + presence[r];
   *l = v;
 }
 }  // namespace
@@ -215,10 +240,18 @@ LLM_EXPORT int llm_sample(const float* logits, long long ld, int rows, int V,
   return launch_status();
 }
 
-LLM_EXPORT int llm_apply_penalties(float* logits, long long ld, const int* triples, int n,
+// triples: n (row, token, count) of the tokens in the rows' penalty windows.  inflight_src (may be
+// null): per row of `rows`, the index in `drawn` of a token that enters the row's window but is
+// still being drawn by the step before (-1: none); rows with penalties switched off must have -1.
+LLM_EXPORT int llm_apply_penalties(float* logits, long long ld, int V, const int* triples, int n,
                                    const float* repeat, const float* freq, const float* presence,
+                                   const int* inflight_src, const int* drawn, int rows,
                                    cudaStream_t stream) {
-  if (n <= 0) return 0;
-  penalty_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits, ld, triples, n, repeat, freq, presence);
+  if (n > 0)
+    penalty_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits, ld, triples, n, repeat, freq, presence,
+                                                        inflight_src, drawn);
+  if (inflight_src && rows > 0)
+    penalty_inflight_kernel<<<(rows + 63) / 64, 64, 0, stream>>>(logits, ld, V, triples, n, rows, repeat, freq,
+                                                               presence, inflight_src, drawn);
   return launch_status();
 }

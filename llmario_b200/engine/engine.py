@@ -145,6 +145,7 @@ class Engine:
                 if e.samples:
                     row_of[e.request.id] = len(row_of)
         rows: List[int] = []        # per token row: where on the device its token comes from, or -1
+        inflight: List[int] = []    # per sampling row: the same for the token that enters its window
         for e in plan.entries:
             r = e.request
             want = [e.count - 1] if e.samples else []
@@ -156,16 +157,20 @@ class Engine:
                                        "the token in flight")
                 entries.append(StepEntry(r.id, [0], want))
                 rows.append(row_of[r.id])
+                if e.samples:
+                    inflight.append(row_of[r.id])
             else:
                 entries.append(StepEntry(r.id, r.tokens(e.start, e.count), want))
                 rows += [-1] * e.count
+                if e.samples:
+                    inflight.append(-1)
         if any(x >= 0 for x in rows):
             source = (self.sampler.device_tokens, rows)
         t0 = time.perf_counter()
         logits = self.runner.step(entries, source)
         samplers = [e.request.sampler for e in plan.entries if e.samples]
         t1 = time.perf_counter()
-        pending = self.sampler.launch(logits, samplers) if samplers else None
+        pending = self.sampler.launch(logits, samplers, inflight) if samplers else None
         t2 = time.perf_counter()
         self.timers["step_s"] += t1 - t0
         self.timers["sample_s"] += t2 - t1

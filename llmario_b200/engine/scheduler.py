@@ -265,10 +265,9 @@ class Scheduler:
         request whose last token is in flight (``max_tokens`` or the context reached) is left
         out; it keeps its slot and pages until ``flying`` is reported.  None when ``flying``
         preempted or failed someone, when pages are so short that a request would have to give
-        way (that is decided with all facts known), when nothing could run, or when a request
-        with penalties would need the token in flight.  A request that does end on an
-        end-of-sequence token drawn by ``flying`` has a row too many in the step ahead;
-        :meth:`complete` passes over it.  The cache lengths already count ``flying``."""
+        way (that is decided with all facts known), or when nothing could run.  A request that
+        does end on an end-of-sequence token drawn by ``flying`` has a row too many in the step
+        ahead; :meth:`complete` passes over it.  The cache lengths already count ``flying``."""
         n = len(flying.entries)
         if n == 0 or n > self._cap:
             return None

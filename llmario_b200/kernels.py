@@ -67,7 +67,7 @@ def _signatures():
                                             P, P],
         "llm_attention_tcgen05": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, I, P, P],
         "llm_attention_tcgen05_x2": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, P, P],
-        "llm_apply_penalties": [P, L, P, I, P, P, P, P],
+        "llm_apply_penalties": [P, L, I, P, I, P, P, P, P, P, I, P],
         "llm_random_normal": [P, I, L, ctypes.c_ulonglong, ctypes.c_double, ctypes.c_double, L,
                               P],
     }
@@ -310,11 +310,17 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 
 def apply_penalties(logits: torch.Tensor, triples: torch.Tensor, n: int, repeat: torch.Tensor,
-                    freq: torch.Tensor, presence: torch.Tensor) -> None:
-    """For the first n (row, token, count) triples adjust logits[row][token] in place."""
-    _cuda(logits, triples, repeat, freq, presence)
-    _check(lib().llm_apply_penalties(_ptr(logits), logits.stride(0), _ptr(triples), n,
-                                     _ptr(repeat), _ptr(freq), _ptr(presence), _stream()),
+                    freq: torch.Tensor, presence: torch.Tensor,
+                    inflight_src: Optional[torch.Tensor] = None,
+                    drawn: Optional[torch.Tensor] = None) -> None:
+    """For the first n (row, token, count) triples adjust logits[row][token] in place.
+    ``inflight_src`` (int32 per row, -1: none) names, by its index in ``drawn``, a token that
+    enters the row's window but is still being drawn by the step before: it counts once more."""
+    _cuda(logits, triples, repeat, freq, presence, inflight_src, drawn)
+    assert (inflight_src is None) == (drawn is None)
+    _check(lib().llm_apply_penalties(_ptr(logits), logits.stride(0), logits.shape[1], _ptr(triples),
+                                     n, _ptr(repeat), _ptr(freq), _ptr(presence),
+                                     _ptr(inflight_src), _ptr(drawn), logits.shape[0], _stream()),
            "apply_penalties")
 
 

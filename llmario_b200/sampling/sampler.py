@@ -51,6 +51,21 @@ class RequestSampler:
         self.window.append(token)
         self.counts[token] = self.counts.get(token, 0) + 1
 
+    def counts_before_unknown(self) -> Dict[int, int]:
+        """The counts of the window as they will stand when one more token, not known yet, has
+        entered it: without that token itself, but with the oldest token gone if the window
+        is full."""
+        n = self.params.repeat_last_n
+        if n <= 0 or len(self.window) < n:
+            return self.counts
+        out = dict(self.counts)
+        old = self.window[0]
+        if out[old] > 1:
+            out[old] -= 1
+        else:
+            del out[old]
+        return out
+
     def next_uniform(self) -> float:
         return 0.0 if self.params.greedy else self.rng.next_f64()
 
@@ -126,17 +141,28 @@ class DeviceSampler:
             return []
         return self.launch(logits, samplers).result()
 
-    def launch(self, logits: torch.Tensor, samplers: Sequence[RequestSampler]) -> PendingTokens:
+    def launch(self, logits: torch.Tensor, samplers: Sequence[RequestSampler],
+               inflight: Optional[Sequence[int]] = None) -> PendingTokens:
         """As :meth:`sample` without waiting: the draw and the copy of the tokens to the host
-        are queued on the stream; at most two draws may be unread at a time."""
+        are queued on the stream; at most two draws may be unread at a time.  ``inflight``: per
+        row, the row of the draw before this one (:attr:`device_tokens`) whose token enters this
+        row's penalty window although the host has not seen it yet, or -1: the step before is
+        still running and this row's input is the token it draws."""
         rows = logits.shape[0]
         assert rows == len(samplers) and logits.dtype == torch.float32 and rows > 0
         tri: List[int] = []
+        src: List[int] = [-1] * rows
         for r, s in enumerate(samplers):
             if s.params.penalties_active:
-                for tok, cnt in s.counts.items():
+                unknown = inflight is not None and inflight[r] >= 0
+                if unknown:
+                    src[r] = int(inflight[r])
+                for tok, cnt in (s.counts_before_unknown() if unknown else s.counts).items():
                     tri += (r, tok, cnt)
-        self._buffers(rows, len(tri) // 3)
+        any_unknown = any(x >= 0 for x in src)
+        # (the tokens of the draw before, taken before the buffers may be replaced by larger ones)
+        drawn = self.device_tokens if any_unknown else None
+        self._buffers(rows, len(tri) // 3 + (rows if any_unknown else 0))
         c = self._cap
         # the options of a row change only when the set of requests changes; the uniforms
         # change with every draw (greedy rows draw nothing)
@@ -166,17 +192,21 @@ class DeviceSampler:
             self._host_event[i].record()
             self._dev_key = key
         d = self._dev
-        if tri:
+        if tri or any_unknown:
             n = len(tri) // 3
+            # the rows' sources of tokens in flight travel behind the triples
+            words = tri + (src if any_unknown else [])
             if getattr(self, "_tri_event", None) is not None:
                 self._tri_event.synchronize()       # the copy of the draw before has left
-            self._tri_host[:3 * n] = torch.tensor(tri, dtype=torch.int32)
-            self._tri_dev[:3 * n].copy_(self._tri_host[:3 * n], non_blocking=True)
-            self.h2d_bytes += 12 * n
+            self._tri_host[:len(words)] = torch.tensor(words, dtype=torch.int32)
+            self._tri_dev[:len(words)].copy_(self._tri_host[:len(words)], non_blocking=True)
+            self.h2d_bytes += 4 * len(words)
             self._tri_event = torch.cuda.Event()
             self._tri_event.record()
             kernels.apply_penalties(logits, self._tri_dev, n, d[3 * c:4 * c], d[4 * c:5 * c],
-                                    d[5 * c:6 * c])
+                                    d[5 * c:6 * c],
+                                    self._tri_dev[3 * n:3 * n + rows] if any_unknown else None,
+                                    drawn)
         kernels.sample(logits, d[0:c], d[6 * c:7 * c].view(torch.int32), d[c:2 * c],
                        d[2 * c:3 * c], d[8 * c:10 * c].view(torch.float64),
                        self._out[STATUS_WORDS:], self._out[:STATUS_WORDS])

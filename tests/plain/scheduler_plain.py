@@ -151,8 +151,6 @@ class PlainScheduler:
                         if self._outs(r) >= r.params.max_tokens or \
                                 self._seq(r) >= self.max_context:
                             continue          # its last token is the one in flight
-                        if self._fly.get(r.id, (0, 0))[1] and r.params.penalties_active:
-                            return None       # penalties need the token in flight on the host
                     need = self._pages_for(r, 1, True)
                     if used >= self.token_budget:
                         break

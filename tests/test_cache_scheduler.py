@@ -438,14 +438,15 @@ def test_what_a_step_planned_ahead_leaves_to_the_next_plan():
     assert [r.id for r in finish(s4, p2)] == ["g"]
     p4 = s4.plan_ahead(p3)
     assert [(x.request.id, x.start, x.count) for x in p4.entries] == [("h", 7, 1), ("i", 0, 4)]
-    # penalties need the drawn token on the host before the next step can be made
+    # penalties do not stand in the way: the sampler counts the token in flight on the device
     pen = req("p", 3, 50)
     pen.params.repeat_penalty = 1.3
     s2 = Scheduler(manager(n_pages=64, ctx=64), token_budget=8)
     s2.add(pen)
     p = s2.plan()
     launch(s2, p)
-    assert pen.params.penalties_active and s2.plan_ahead(p) is None
+    ahead = s2.plan_ahead(p)
+    assert pen.params.penalties_active and [(x.request.id, x.start) for x in ahead.entries] == [("p", 3)]
 
 
 # ------------------------------------------------------------------------------ native core vs plain model

@@ -155,6 +155,58 @@ def test_device_sampler_penalties_and_streams():
     assert abs(freqs[0] - 0.5) < 0.09 and abs(freqs[1] - 0.3) < 0.09 and abs(freqs[2] - 0.2) < 0.08
 
 
+def test_penalties_count_a_token_in_flight():
+    """A step queued ahead draws with penalties while the token that just entered the window is
+    still on the device: the sampler gets the counts without that token and the row of the draw
+    before that holds it.  The penalised logits and the drawn tokens must be, bit for bit, those
+    of a draw that had the token on the host: when the token is already in the window, when it
+    is new to it, and when the window is full and its oldest token leaves as the new one comes."""
+    from llmario_b200 import SamplingParams
+    from llmario_b200.sampling import DeviceSampler, RequestSampler
+
+    vocab, rows = 257, 5
+    gen = torch.Generator().manual_seed(3)
+    base = (3.0 * torch.randn(rows, vocab, generator=gen)).to(DEV)
+    params = [SamplingParams(temperature=0.0, repeat_penalty=1.3, frequency_penalty=0.4,
+                             presence_penalty=0.2, repeat_last_n=6),
+              SamplingParams(temperature=0.8, top_k=0, top_p=1.0, min_p=0.0, seed=5,
+                             repeat_penalty=1.2, frequency_penalty=0.3, repeat_last_n=6),
+              SamplingParams(temperature=0.0),                       # no penalties on this row
+              SamplingParams(temperature=0.0, repeat_penalty=1.5, repeat_last_n=4),
+              SamplingParams(temperature=0.0, frequency_penalty=0.7, repeat_last_n=64)]
+    histories = [[7, 9, 7], [1, 2, 3, 4, 5, 6], [4, 4], [8, 9, 10, 11], [20, 21]]
+    new = [7, 99, 4, 8, 21]           # in the window / new to it / (no penalties) / the one that leaves / in it
+
+    def samplers():
+        out = []
+        for p, h in zip(params, histories):
+            s = RequestSampler(p, vocab)
+            for t in h:
+                s.accept(t)
+            out.append(s)
+        return out
+
+    # the draw before: its tokens lie in the sampler's device buffer (rows in another order)
+    order = [3, 0, 4, 1, 2]
+    dev = DeviceSampler(DEV)
+    want_rows = torch.full((rows, vocab), -50.0, device=DEV)
+    for j, r in enumerate(order):
+        want_rows[j, new[r]] = 50.0
+    assert dev.sample(want_rows, [RequestSampler(SamplingParams(temperature=0.0), vocab)
+                                  for _ in range(rows)]) == [new[r] for r in order]
+    ahead = samplers()
+    la = base.clone()
+    got_ahead = dev.launch(la, ahead, inflight=[order.index(r) for r in range(rows)]).result()
+    # the same draw with the tokens known on the host
+    known = samplers()
+    for s, t in zip(known, new):
+        s.accept(t)
+    lk = base.clone()
+    got_known = DeviceSampler(DEV).sample(lk, known)
+    assert torch.equal(la, lk) and got_ahead == got_known
+    assert not torch.equal(la, base) and torch.equal(la[2], base[2])
+
+
 def test_temperature_generation_is_reproducible_and_batch_independent():
     """Config B's workload: four requests of 1/7/23/40 tokens, prompts cut at 16 beside
     running decodes, 12 tokens at temperature 0.7 with a seed."""
