@@ -92,7 +92,10 @@ def cmd_run(args) -> int:
     n = args.max_tokens if args.max_tokens is not None else args.n
     temp = 0.0 if args.temperature is None else args.temperature
     params = SamplingParams(temperature=temp, seed=args.seed, max_tokens=n,
-                            top_k=args.top_k, top_p=args.top_p, min_p=args.min_p)
+                            top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
+                            repeat_penalty=args.repeat_penalty, repeat_last_n=args.repeat_last_n,
+                            presence_penalty=args.presence_penalty,
+                            frequency_penalty=args.frequency_penalty)
     import torch
 
     rid = eng.add_request(prompt, params)
@@ -228,6 +231,11 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     run.add_argument("--top-k", type=int, default=40)
     run.add_argument("--top-p", type=float, default=0.95)
     run.add_argument("--min-p", type=float, default=0.05)
+    run.add_argument("--repeat-penalty", type=float, default=1.0,
+                     help="over the last --repeat-last-n tokens, prompt included; 1 disables")
+    run.add_argument("--repeat-last-n", type=int, default=64)
+    run.add_argument("--presence-penalty", type=float, default=0.0)
+    run.add_argument("--frequency-penalty", type=float, default=0.0)
     _common(run)
     run.set_defaults(fn=cmd_run)
     bench = sub.add_parser("bench", help="prefill and decode rates at given concurrency")
