@@ -45,6 +45,14 @@ def test_run_with_a_seed_is_reproducible():
     assert ids == b.stdout.strip().splitlines()[-1] and len(ids.split(",")) == 12
     other = cli(*args[:5], 2, *args[6:])
     assert other.stdout.strip().splitlines()[-1] != ids          # another seed, other tokens
+    # the penalties of the chain are options too (steps queued ahead count the token in flight)
+    greedy = ("run", "tiny-a", "--prompt-len", 5, "--n", 24, "--dtype", "float32", "--page-size", 4,
+              "--context", 64)
+    plain_ids = cli(*greedy).stdout.strip().splitlines()[-1].split(",")
+    pen = cli(*greedy, "--repeat-penalty", 1.5, "--frequency-penalty", 1.0, "--repeat-last-n", 8)
+    pen_ids = pen.stdout.strip().splitlines()[-1].split(",")
+    assert len(pen_ids) == 24 and pen_ids != plain_ids
+    assert max(pen_ids.count(t) for t in pen_ids) <= max(plain_ids.count(t) for t in plain_ids)
 
 
 def test_bench_writes_json_and_markdown_with_the_roofline_fraction():
